@@ -1,0 +1,332 @@
+#!/usr/bin/env python3
+"""Benchmark of the fused NVFP4 MoE expert layer (decode, large-MoE shape).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens M] [--impl ours|reference]
+
+One "step" is one pass of the layer over one batch of M synthetic tokens (hidden 4096, 512 routed
+experts top-10 + 1 shared expert, intermediate 1024, NVFP4 weights from seed 0).  Prints ONE JSON
+line (rank 0).  ``value`` is tokens/s with inputs resident in HBM, timed with CUDA events;
+``e2e`` is the same metric through the operator class with host (pinned) buffers, host<->device
+copies inside the timed region; ``roofline`` is the gate_up kernel's algorithmic bytes over its
+own event-timed launch duration against the measured HBM copy bandwidth; ``cpu_baseline`` is the
+CPU oracle (torch dequantise-then-matmul, all host threads) timed on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+os.environ.setdefault("VMOE_NO_VLLM", "1")   # the operator classes do not need the framework to run
+
+METRIC = "moe_layer_decode_tokens_per_s"
+UNIT = "tokens/s"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--tokens", type=int, default=64, help="decode batch per GPU")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rotate", type=int, default=4, help="distinct input sets cycled through")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-sample-tokens", type=int, default=2)
+    return ap.parse_args()
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:  # noqa: BLE001
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:  # noqa: BLE001
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:  # noqa: BLE001
+            self.proc.kill()
+        sm = sorted(float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit())
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 9 for n, v in zip(names, r[5:9]) if v.lower().startswith("active")})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx[0] if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the oracle (torch dequantise-then-matmul restatement of the reference's check,
+# fused-moe/test_verdict_moe_ext.py:196-218) on a bounded sample of the workload.
+# ---------------------------------------------------------------------------------------------
+def cpu_sample_problem(tokens: int, seed: int):
+    """A bounded sample of the decode workload, built on the CPU: ``tokens`` tokens of the batch with
+    only the experts they touch materialised (ids remapped to a dense range)."""
+    import numpy as np
+    import torch
+    from oracle import moe as omoe
+    from sm120_moe_bench_b200 import synth
+    cfg = synth.CONFIG_LARGE
+    hidden, logits = synth.make_inputs(cfg, tokens, seed=seed)
+    ids, w = omoe.route(logits.numpy(), cfg.topk)
+    used, dense = np.unique(ids, return_inverse=True)
+    gen = torch.Generator().manual_seed(seed)
+    routed = synth.make_expert_weights(len(used), cfg.hidden, cfg.inter, gen, "cpu")
+    shared = synth.make_expert_weights(1, cfg.hidden, cfg.inter, gen, "cpu")
+    conv = lambda six: omoe.ExpertWeights(*[t.numpy() for t in six])
+    return hidden.float().numpy(), dense.reshape(ids.shape).astype(np.int32), w, conv(routed), conv(shared), len(used)
+
+
+def cpu_time_once(problem):
+    from oracle import moe as omoe
+    hidden, ids, w, routed, shared, _ = problem
+    t0 = time.perf_counter()
+    omoe.moe_layer(hidden, ids, w, routed, shared, accum="f32")
+    return time.perf_counter() - t0
+
+
+def run_reference_arm(args):
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    sample_tokens = 1
+    problem = cpu_sample_problem(sample_tokens, seed=0)
+    for _ in range(max(args.warmup, 0)):
+        cpu_time_once(problem)
+    times = [cpu_time_once(problem) for _ in range(max(args.steps, 1))]
+    total = sum(times)
+    value = sample_tokens * len(times) / total
+    sample = (f"{sample_tokens} token(s) of the {args.tokens}-token decode batch per step, "
+              f"{problem[5]} routed experts + 1 shared dequantised and multiplied per step")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": len(times), "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4(w4a4)->f32",
+        "data": "synthetic",
+        "config": workload_config(args.tokens, args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(tokens, gpus):
+    return {"workload": "single-GPU decode MoE layer, large-MoE shape (BASELINE config 2)",
+            "hidden": 4096, "inter": 1024, "experts": 512, "topk": 10, "shared_experts": 1,
+            "tokens_per_gpu": tokens, "weights": "NVFP4 (E2M1 + E4M3 per-16 + fp32 global), N(0,0.02), seed 0",
+            "parallelism": "single GPU" if gpus == 1 else f"{gpus} independent replicas",
+            "l2": "inputs larger than L2: every step streams > 126 MB of expert weights; input sets rotate"}
+
+
+# ---------------------------------------------------------------------------------------------
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    import sm120_moe_bench_b200 as vm
+    from sm120_moe_bench_b200 import ops, synth
+    from sm120_moe_bench_b200.verdict_moe import VerdictMoEMonolithic
+
+    cfg = synth.CONFIG_LARGE
+    M = args.tokens
+    layer = synth.make_layer(cfg, seed=0, device=dev)
+    routed = ops.MoEWeights(*layer["routed"])
+    shared = ops.MoEWeights(*layer["shared"])
+    shape = vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, max(M, 1), has_shared=True)
+    ws = vm.Workspace(shape, dev)
+    sets = [synth.make_inputs(cfg, M, seed=100 * rank + i, device=dev) for i in range(max(args.rotate, 1))]
+    out = torch.empty(M, cfg.hidden, dtype=torch.bfloat16, device=dev)
+
+    def step(i):
+        h, l = sets[i % len(sets)]
+        vm.fused_moe(h, routed, ws, router_logits=l, shared=shared, out=out)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    status = ws.status()
+
+    # ---- per-kernel durations, same inputs, each stage bracketed by its own events ---------
+    stage_ms = {"gate_up": 0.0, "down": 0.0}
+    distinct = []
+    for i in range(args.steps):
+        h, l = sets[i % len(sets)]
+        ids, w = vm.route(l, cfg.topk)
+        vm.build_tables(ws, ids, w)
+        pk, sf = vm.quantize(h)
+        ws.view("act_q", torch.uint8, pk.numel()).copy_(pk.view(-1))
+        ws.view("act_sf", torch.uint8, sf.numel()).copy_(sf.view(-1))
+        for name in ("gate_up", "down"):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            ops.run_stage(name, ws, routed, shared, M)
+            b.record()
+            b.synchronize()
+            stage_ms[name] += a.elapsed_time(b)
+        distinct.append(int(torch.unique(ids).numel()) + 1)
+    clocks = sampler.stop() if rank == 0 else None
+    U = float(np.mean(distinct))
+    K, N = cfg.hidden, cfg.inter
+    gate_up_bytes = U * (2 * N * K // 2 + 2 * N * K // 16) + M * (K // 2 + K // 16)
+    down_bytes = U * (K * N // 2 + K * N // 16)
+    layer_bytes = U * routed.nbytes_per_expert() + M * (K * 2 * 2 + cfg.num_experts * 4)
+    peak, peak_kind = measured_peak_gbs()
+    gu_s = stage_ms["gate_up"] / args.steps * 1e-3
+    dn_s = stage_ms["down"] / args.steps * 1e-3
+    roof = {"bound": "hbm", "kernel": "gate_up_kernel", "achieved": gate_up_bytes / gu_s / 1e9, "peak": peak,
+            "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s",
+            "unit": "GB/s", "frac": gate_up_bytes / gu_s / 1e9 / peak, "traffic": None,
+            "algorithmic_bytes_per_launch": gate_up_bytes, "us_per_launch": gu_s * 1e6,
+            "distinct_experts_per_step": U,
+            "down_kernel": {"achieved": down_bytes / dn_s / 1e9, "frac": down_bytes / dn_s / 1e9 / peak,
+                            "us_per_launch": dn_s * 1e6, "algorithmic_bytes_per_launch": down_bytes},
+            "layer": {"achieved": layer_bytes / (ms / args.steps * 1e-3) / 1e9,
+                      "frac": layer_bytes / (ms / args.steps * 1e-3) / 1e9 / peak,
+                      "algorithmic_bytes_per_step": layer_bytes}}
+
+    # ---- end to end through the operator class with host buffers -----------------------------
+    class _Q:  # quant-config attributes the class reads (fused-moe/verdict_moe.py:499-503,519-520)
+        g1_alphas, g2_alphas = routed.w13_gs, routed.w2_gs
+        a1_gscale = torch.ones_like(routed.w13_gs); a2_gscale = torch.ones_like(routed.w2_gs)
+        w1_scale, w2_scale = routed.w13_sf, routed.w2_sf
+
+    class _C:
+        experts_per_token = cfg.topk
+    op = VerdictMoEMonolithic(_C(), _Q())
+    op.set_shared_expert(shared)
+    host_sets = [(h.cpu().pin_memory(), l.cpu().pin_memory()) for h, l in sets]
+    host_out = torch.empty(M, cfg.hidden, dtype=torch.bfloat16).pin_memory()
+    h_dev = torch.empty(M, cfg.hidden, dtype=torch.bfloat16, device=dev)
+    l_dev = torch.empty(M, cfg.num_experts, dtype=torch.float32, device=dev)
+
+    def e2e_step(i):
+        hh, lh = host_sets[i % len(host_sets)]
+        h_dev.copy_(hh, non_blocking=True)
+        l_dev.copy_(lh, non_blocking=True)
+        o = op.apply(h_dev, routed.w13, routed.w2, l_dev, "SILU", cfg.num_experts, None, None, False)
+        host_out.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()     # the caller reads the result every step
+
+    for i in range(args.warmup):
+        e2e_step(i)
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for i in range(args.steps):
+        e2e_step(i)
+    f1.record()
+    barrier()
+    e2e_ms = f0.elapsed_time(f1)
+
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = t.tolist()
+
+    line = None
+    if rank == 0:
+        tokens_total = M * world * args.steps
+        launches_per_step = 6 if M * cfg.topk <= 16384 else 9
+        line = {
+            "metric": METRIC, "value": tokens_total / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4(w4a4)->f32",
+            "data": "synthetic", "config": workload_config(M, world),
+            "roofline": roof, "clocks": clocks,
+            "e2e": {"value": tokens_total / (e2e_ms * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": M * (cfg.hidden * 2 + cfg.num_experts * 4),
+                    "d2h_bytes_per_step": M * cfg.hidden * 2, "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": launches_per_step * args.steps,
+            "device_status": status,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            cores = os.cpu_count() or 1
+            torch.set_num_threads(cores)
+            problem = cpu_sample_problem(args.cpu_sample_tokens, seed=0)
+            dt = cpu_time_once(problem)
+            line["cpu_baseline"] = {
+                "value": args.cpu_sample_tokens / dt, "unit": UNIT, "cores": cores, "kind": "port",
+                "sample": f"{args.cpu_sample_tokens} tokens of the batch, {problem[5]} routed experts + 1 shared, "
+                          f"one pass of the CPU oracle ({dt:.1f} s)"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,166 @@
+/*
+ * vmoe.h -- C ABI of the B200 (sm_100a) fused NVFP4 MoE expert layer.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle
+ * (a cudaStream_t passed as void*), returns an int status (VMOE_OK == 0) and
+ * neither allocates nor synchronises; the caller owns every buffer, including the
+ * workspace blob whose size vmoe_workspace_bytes() reports.  This is the surface a
+ * binding of the reference's operator would call in place of its pybind11
+ * extension functions (reference: fused-moe/csrc/verdict_fused_cooperative_tma_ext.cu
+ * :574-656 `verdict_cooperative_tma_forward`, :1022-1031 the pybind module; and
+ * fused-moe/csrc/verdict_moe_ext.cu:358-433, :578-582 for the scalar pipeline).
+ *
+ * Tensor layouts are the reference's (fused-moe/verdict_moe.py:571-575, :519-520):
+ *   hidden   [M, K]        bf16
+ *   w13      [E, 2N, K/2]  u8, two E2M1 codes per byte, even k in the low nibble;
+ *                          rows 0..N-1 = gate, N..2N-1 = up
+ *   w13_sf   [E, 2N, K/16] u8, E4M3 block scales, linear (not swizzled)
+ *   w13_gs   [E]           f32 per-expert global scale (the reference's alpha1)
+ *   w2       [E, K, N/2]   u8;  w2_sf [E, K, N/16] u8;  w2_gs [E] f32 (alpha2)
+ *   out      [M, K]        bf16
+ * K = hidden size, N = expert intermediate size, E = experts held by this GPU,
+ * T = experts per token.
+ */
+#ifndef VMOE_H_
+#define VMOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VMOE_ABI_VERSION 1
+
+enum vmoe_status {
+    VMOE_OK = 0,
+    VMOE_ERR_NULL = 1,       /* a required pointer is NULL */
+    VMOE_ERR_SHAPE = 2,      /* unsupported K / N / E / T / M */
+    VMOE_ERR_ALIGN = 3,      /* a pointer is not 16-byte aligned */
+    VMOE_ERR_WORKSPACE = 4,  /* workspace too small */
+    VMOE_ERR_CUDA = 5,       /* a CUDA call failed; cudaGetLastError has details */
+    VMOE_ERR_TIMEOUT = 6,    /* a bounded device-side wait ran out (read from the status word) */
+    VMOE_ERR_SCALE = 7,      /* a block-scale byte has its sign bit set (NVFP4 scales are unsigned) */
+    VMOE_ERR_LIMIT = 8       /* size beyond a stated fixed maximum */
+};
+
+/* Problem shape.  Replaces the reference's compile-time HIDDEN = 4096 and the
+ * (K, N_half, num_pairs) integer arguments of its forward functions
+ * (fused-moe/csrc/verdict_fused_cooperative_tma_ext.cu:32, :594-596). */
+typedef struct vmoe_shape {
+    int32_t hidden;       /* K: multiple of 128, <= 8192 */
+    int32_t inter;        /* N: multiple of 128, <= 2048 */
+    int32_t num_experts;  /* E: routed experts whose weights this GPU holds */
+    int32_t topk;         /* T: 1..16 */
+    int32_t max_tokens;   /* largest M the workspace must serve */
+    int32_t has_shared;   /* 1: an always-on shared expert is applied to every token */
+    int32_t num_global_experts; /* width of router logits / range of topk ids (== E without expert parallelism) */
+    int32_t reserved;
+} vmoe_shape;
+
+/* One set of NVFP4 expert weights (device pointers).  Replaces the (w1, w1_sf,
+ * w1_alpha, w2, w2_sf, w2_alpha) tensor arguments of the reference's forward
+ * (…tma_ext.cu:575-581); the per-pair alpha gather of fused-moe/verdict_moe.py
+ * :499-513 happens on the device from the per-expert arrays. */
+typedef struct vmoe_weights {
+    const uint8_t* w13;
+    const uint8_t* w13_sf;
+    const float*   w13_gs;
+    const uint8_t* w2;
+    const uint8_t* w2_sf;
+    const float*   w2_gs;
+} vmoe_weights;
+
+/* Byte offsets of the intermediate tables inside the workspace, so that a test or
+ * a profiler can read each stage.  Mirrors the scratch tensors the reference
+ * preallocates in fused-moe/verdict_moe.py:243-414 (input_fp4/input_sf,
+ * inter_fp4/inter_sf, pair_output_f32, expert id / weight / token tables). */
+typedef struct vmoe_ws_layout {
+    size_t total_bytes;
+    size_t topk_ids;        /* int32 [M, T] */
+    size_t topk_weights;    /* f32   [M, T] */
+    size_t expert_offsets;  /* int32 [E + 2]: exclusive scan of pairs per expert; entry E.. = shared expert */
+    size_t sorted_pair;     /* int32 [P + M]: flat pair index of each sorted slot */
+    size_t pair_slot;       /* int32 [P]: sorted slot of each pair, -1 when its expert is not local */
+    size_t gather_idx;      /* int32 [P + M]: source token of each sorted slot */
+    size_t scatter_weights; /* f32   [P + M]: router weight of each sorted slot (1.0 for the shared expert) */
+    size_t units;           /* int32 [max_units, 4]: (expert, first slot, tokens, 0) work units of the GEMV path */
+    size_t counters;        /* int32 [8]: 0 = number of units, 1 = number of slots, 2..3 = work queues, 4 = status word */
+    size_t act_q;           /* u8 [M, K/2] quantised activations */
+    size_t act_sf;          /* u8 [M, K/16] */
+    size_t inter_q;         /* u8 [P + M, N/2] quantised SwiGLU output per sorted slot */
+    size_t inter_sf;        /* u8 [P + M, N/16] */
+    size_t pair_out;        /* f32 [P + M, K] weighted down-projection rows per sorted slot */
+    size_t bitmap;          /* u32 [E, ceil(M/32)] scratch of the permutation */
+    size_t word_prefix;     /* int32 [E, ceil(M/32)] scratch of the permutation */
+} vmoe_ws_layout;
+
+int         vmoe_abi_version(void);
+const char* vmoe_status_string(int status);
+
+/* Workspace sizing.  Replaces VerdictMoEExperts.setup_buffers / workspace_shapes
+ * (fused-moe/verdict_moe.py:224-238, :243-414). */
+size_t vmoe_workspace_bytes(const vmoe_shape* shape);
+int    vmoe_workspace_layout(const vmoe_shape* shape, vmoe_ws_layout* out);
+
+/* Router: fp32 softmax over all experts, top-T by probability (lowest expert id
+ * wins ties, descending order), renormalised.  Replaces moe_topk_select
+ * (fused-moe/csrc/megakernel_v1.cu:491-537).  logits [M, E] f32. */
+int vmoe_route(const float* logits, int32_t M, int32_t E, int32_t T,
+               int32_t* topk_ids, float* topk_weights, void* stream);
+
+/* Permutation by expert: stable sort of the M*T pairs by (local) expert id,
+ * expert offsets, gather / scatter tables and the GEMV work-unit list, written into
+ * the workspace at the offsets of vmoe_workspace_layout().  Replaces
+ * build_group_tables (fused-moe/csrc/verdict_fused_grouped.cu:655-691) and the flat
+ * pair tables + expert_map remap of fused-moe/verdict_moe.py:473-477, :490-496.
+ * expert_map [num_global_experts] int32 (-1 = not local) or NULL. */
+int vmoe_build_tables(const vmoe_shape* shape, const int32_t* topk_ids,
+                      const float* topk_weights, const int32_t* expert_map,
+                      int32_t M, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Activation quantiser bf16 -> NVFP4 (per-16 E4M3 block scale, no global scale).
+ * Replaces the prologue of the fused kernel (…tma_ext.cu:249-279) and
+ * bf16_to_nvfp4_e4m3_kernel (fused-moe/csrc/verdict_fused_ext.cu:154-192). */
+int vmoe_quantize(const void* x_bf16, int32_t rows, int32_t K,
+                  uint8_t* packed, uint8_t* sf, void* stream);
+
+/* Decode NVFP4 to f32: value = e2m1(code) * e4m3(block scale) * global_scale[row_group].
+ * rows_per_scale rows share one entry of global_scale (NULL = 1.0).  Replaces
+ * read_nvfp4 / decode_fp4 / decode_e4m3fn (fused-moe/csrc/verdict_moe_ext.cu:86-116). */
+int vmoe_dequantize(const uint8_t* packed, const uint8_t* sf, const float* global_scale,
+                    int64_t rows, int32_t K, int64_t rows_per_scale, float* out, void* stream);
+
+/* The fused layer.  Replaces verdict_cooperative_tma_forward (…tma_ext.cu:574-656)
+ * plus the host glue of VerdictMoEExperts.apply (fused-moe/verdict_moe.py:421-553).
+ * Give either router logits [M, num_global_experts] f32 (routing runs on the
+ * device) or topk_ids / topk_weights [M, T] (pre-routed, the reference's slot);
+ * shared may be NULL when shape->has_shared == 0. */
+int vmoe_forward(const vmoe_shape* shape, const vmoe_weights* routed,
+                 const vmoe_weights* shared, const void* hidden_bf16,
+                 const float* router_logits, const int32_t* topk_ids,
+                 const float* topk_weights, const int32_t* expert_map,
+                 void* out_bf16, int32_t M, void* workspace, size_t workspace_bytes,
+                 void* stream);
+
+/* Individual stages of vmoe_forward over an already built workspace (tables and
+ * quantised activations present).  For stage-wise parity checks and per-kernel
+ * timing, as the reference's per_kernel_timing (fused-moe/csrc/verdict_moe_ext.cu
+ * :482-573). */
+int vmoe_stage_gate_up(const vmoe_shape* shape, const vmoe_weights* routed,
+                       const vmoe_weights* shared, int32_t M, void* workspace, void* stream);
+int vmoe_stage_down(const vmoe_shape* shape, const vmoe_weights* routed,
+                    const vmoe_weights* shared, int32_t M, void* workspace, void* stream);
+int vmoe_stage_combine(const vmoe_shape* shape, int32_t M, void* workspace,
+                       void* out_bf16, void* stream);
+
+/* Reads (and clears) the device status word of a workspace after the caller has
+ * synchronised the stream: VMOE_OK or VMOE_ERR_TIMEOUT.  The reference has no
+ * counterpart (its waits are unbounded: …tma_ext.cu:156-167). */
+int vmoe_read_status(void* workspace, const vmoe_shape* shape, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VMOE_H_ */

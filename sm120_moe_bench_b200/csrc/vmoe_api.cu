@@ -1,0 +1,246 @@
+// C ABI: argument validation, workspace layout, stage sequencing.  No allocation, no
+// synchronisation; every launch goes to the caller's stream.
+#include "vmoe_common.cuh"
+
+#include <string.h>
+
+namespace vmoe {
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+int max_units(const vmoe_shape* s) {
+    const long long P = (long long)s->max_tokens * s->topk + (s->has_shared ? s->max_tokens : 0);
+    return (int)(s->num_experts + 1 + (P + TOK_PER_UNIT - 1) / TOK_PER_UNIT);
+}
+
+static int check_shape(const vmoe_shape* s) {
+    if (!s) return VMOE_ERR_NULL;
+    if (s->hidden <= 0 || s->hidden % 128 || s->hidden > 4096) return VMOE_ERR_SHAPE;
+    if (s->inter <= 0 || s->inter % 128 || s->inter > 1024) return VMOE_ERR_SHAPE;
+    if (s->num_experts <= 0 || s->topk <= 0 || s->topk > MAX_TOPK) return VMOE_ERR_SHAPE;
+    if (s->max_tokens < 0) return VMOE_ERR_SHAPE;
+    if (s->num_global_experts < s->num_experts) return VMOE_ERR_SHAPE;
+    if (s->topk > s->num_global_experts) return VMOE_ERR_SHAPE;
+    return VMOE_OK;
+}
+
+int compute_layout(const vmoe_shape* s, vmoe_ws_layout* L) {
+    const int rc = check_shape(s);
+    if (rc) return rc;
+    const size_t M = (size_t)s->max_tokens, T = s->topk, E = s->num_experts, K = s->hidden, N = s->inter;
+    const size_t P = M * T, S = P + M;          // S: sorted slots incl. shared expert rows
+    const size_t words = (M + 31) / 32;
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
+    memset(L, 0, sizeof(*L));
+    L->counters        = take(CNT_N * 4);
+    L->topk_ids        = take(P * 4);
+    L->topk_weights    = take(P * 4);
+    L->expert_offsets  = take((E + 2) * 4);
+    L->sorted_pair     = take(S * 4);
+    L->pair_slot       = take(P * 4);
+    L->gather_idx      = take(S * 4);
+    L->scatter_weights = take(S * 4);
+    L->units           = take((size_t)max_units(s) * 16);
+    L->act_q           = take(M * K / 2);
+    L->act_sf          = take(M * K / 16);
+    L->inter_q         = take(S * N / 2);
+    L->inter_sf        = take(S * N / 16);
+    L->pair_out        = take(S * K * 4);
+    L->bitmap          = take(E * words * 4);
+    L->word_prefix     = take(E * words * 4);
+    L->total_bytes     = off;
+    return VMOE_OK;
+}
+
+int resolve_workspace(const vmoe_shape* s, void* base, Workspace* ws) {
+    vmoe_ws_layout L;
+    const int rc = compute_layout(s, &L);
+    if (rc) return rc;
+    uint8_t* b = static_cast<uint8_t*>(base);
+    ws->counters        = reinterpret_cast<int32_t*>(b + L.counters);
+    ws->topk_ids        = reinterpret_cast<int32_t*>(b + L.topk_ids);
+    ws->topk_weights    = reinterpret_cast<float*>(b + L.topk_weights);
+    ws->expert_offsets  = reinterpret_cast<int32_t*>(b + L.expert_offsets);
+    ws->sorted_pair     = reinterpret_cast<int32_t*>(b + L.sorted_pair);
+    ws->pair_slot       = reinterpret_cast<int32_t*>(b + L.pair_slot);
+    ws->gather_idx      = reinterpret_cast<int32_t*>(b + L.gather_idx);
+    ws->scatter_weights = reinterpret_cast<float*>(b + L.scatter_weights);
+    ws->units           = reinterpret_cast<int4*>(b + L.units);
+    ws->act_q           = b + L.act_q;
+    ws->act_sf          = b + L.act_sf;
+    ws->inter_q         = b + L.inter_q;
+    ws->inter_sf        = b + L.inter_sf;
+    ws->pair_out        = reinterpret_cast<float*>(b + L.pair_out);
+    ws->bitmap          = reinterpret_cast<uint32_t*>(b + L.bitmap);
+    ws->word_prefix     = reinterpret_cast<int32_t*>(b + L.word_prefix);
+    return VMOE_OK;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+static int check_weights(const vmoe_weights* w) {
+    if (!w || !w->w13 || !w->w13_sf || !w->w13_gs || !w->w2 || !w->w2_sf || !w->w2_gs) return VMOE_ERR_NULL;
+    if (!aligned16(w->w13) || !aligned16(w->w13_sf) || !aligned16(w->w2) || !aligned16(w->w2_sf)) return VMOE_ERR_ALIGN;
+    return VMOE_OK;
+}
+
+static WeightSet to_set(const vmoe_weights* w) {
+    WeightSet s{};
+    if (w) { s.w13 = w->w13; s.w13_sf = w->w13_sf; s.w13_gs = w->w13_gs; s.w2 = w->w2; s.w2_sf = w->w2_sf; s.w2_gs = w->w2_gs; }
+    return s;
+}
+
+static int check_call(const vmoe_shape* s, const vmoe_weights* routed, const vmoe_weights* shared, int M,
+                      void* workspace) {
+    int rc = check_shape(s);
+    if (rc) return rc;
+    if (M < 0 || M > s->max_tokens) return VMOE_ERR_SHAPE;
+    if (!workspace) return VMOE_ERR_NULL;
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0) return VMOE_ERR_ALIGN;
+    if ((rc = check_weights(routed))) return rc;
+    if (s->has_shared && (rc = check_weights(shared))) return rc;
+    return VMOE_OK;
+}
+
+}  // namespace vmoe
+
+using namespace vmoe;
+
+extern "C" {
+
+int vmoe_abi_version(void) { return VMOE_ABI_VERSION; }
+
+const char* vmoe_status_string(int status) {
+    switch (status) {
+        case VMOE_OK: return "ok";
+        case VMOE_ERR_NULL: return "a required pointer is NULL";
+        case VMOE_ERR_SHAPE: return "unsupported shape";
+        case VMOE_ERR_ALIGN: return "pointer not sufficiently aligned";
+        case VMOE_ERR_WORKSPACE: return "workspace too small";
+        case VMOE_ERR_CUDA: return "CUDA error";
+        case VMOE_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+        case VMOE_ERR_SCALE: return "block-scale byte with the sign bit set";
+        case VMOE_ERR_LIMIT: return "size beyond a fixed maximum";
+        default: return "unknown status";
+    }
+}
+
+size_t vmoe_workspace_bytes(const vmoe_shape* shape) {
+    vmoe_ws_layout L;
+    return compute_layout(shape, &L) == VMOE_OK ? L.total_bytes : 0;
+}
+
+int vmoe_workspace_layout(const vmoe_shape* shape, vmoe_ws_layout* out) {
+    if (!out) return VMOE_ERR_NULL;
+    return compute_layout(shape, out);
+}
+
+int vmoe_route(const float* logits, int32_t M, int32_t E, int32_t T, int32_t* topk_ids,
+               float* topk_weights, void* stream) {
+    if (!logits || !topk_ids || !topk_weights) return VMOE_ERR_NULL;
+    if (M < 0 || E <= 0 || T <= 0 || T > MAX_TOPK || T > E) return VMOE_ERR_SHAPE;
+    return launch_route(logits, M, E, T, topk_ids, topk_weights, static_cast<cudaStream_t>(stream));
+}
+
+int vmoe_build_tables(const vmoe_shape* shape, const int32_t* topk_ids, const float* topk_weights,
+                      const int32_t* expert_map, int32_t M, void* workspace, size_t workspace_bytes,
+                      void* stream) {
+    int rc = check_shape(shape);
+    if (rc) return rc;
+    if (!topk_ids || !topk_weights || !workspace) return VMOE_ERR_NULL;
+    if (M < 0 || M > shape->max_tokens) return VMOE_ERR_SHAPE;
+    if (workspace_bytes < vmoe_workspace_bytes(shape)) return VMOE_ERR_WORKSPACE;
+    Workspace ws;
+    if ((rc = resolve_workspace(shape, workspace, &ws))) return rc;
+    return launch_tables(*shape, topk_ids, topk_weights, expert_map, M, ws, static_cast<cudaStream_t>(stream));
+}
+
+int vmoe_quantize(const void* x_bf16, int32_t rows, int32_t K, uint8_t* packed, uint8_t* sf, void* stream) {
+    if (!x_bf16 || !packed || !sf) return VMOE_ERR_NULL;
+    if (rows < 0 || K <= 0 || K % SF_BLOCK) return VMOE_ERR_SHAPE;
+    if (!aligned16(x_bf16) || (reinterpret_cast<uintptr_t>(packed) & 7)) return VMOE_ERR_ALIGN;
+    return launch_quantize(static_cast<const __nv_bfloat16*>(x_bf16), rows, K, packed, sf,
+                           static_cast<cudaStream_t>(stream));
+}
+
+int vmoe_dequantize(const uint8_t* packed, const uint8_t* sf, const float* global_scale, int64_t rows,
+                    int32_t K, int64_t rows_per_scale, float* out, void* stream) {
+    if (!packed || !sf || !out) return VMOE_ERR_NULL;
+    if (rows < 0 || K <= 0 || K % SF_BLOCK) return VMOE_ERR_SHAPE;
+    if (reinterpret_cast<uintptr_t>(packed) & 7) return VMOE_ERR_ALIGN;
+    return launch_dequantize(packed, sf, global_scale, rows, K, rows_per_scale, out,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int vmoe_stage_gate_up(const vmoe_shape* shape, const vmoe_weights* routed, const vmoe_weights* shared,
+                       int32_t M, void* workspace, void* stream) {
+    int rc = check_call(shape, routed, shared, M, workspace);
+    if (rc) return rc;
+    Workspace ws;
+    if ((rc = resolve_workspace(shape, workspace, &ws))) return rc;
+    return launch_gate_up(*shape, to_set(routed), to_set(shape->has_shared ? shared : nullptr), M, ws,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int vmoe_stage_down(const vmoe_shape* shape, const vmoe_weights* routed, const vmoe_weights* shared,
+                    int32_t M, void* workspace, void* stream) {
+    int rc = check_call(shape, routed, shared, M, workspace);
+    if (rc) return rc;
+    Workspace ws;
+    if ((rc = resolve_workspace(shape, workspace, &ws))) return rc;
+    return launch_down(*shape, to_set(routed), to_set(shape->has_shared ? shared : nullptr), M, ws,
+                       static_cast<cudaStream_t>(stream));
+}
+
+int vmoe_stage_combine(const vmoe_shape* shape, int32_t M, void* workspace, void* out_bf16, void* stream) {
+    int rc = check_shape(shape);
+    if (rc) return rc;
+    if (!workspace || !out_bf16) return VMOE_ERR_NULL;
+    if (M < 0 || M > shape->max_tokens) return VMOE_ERR_SHAPE;
+    Workspace ws;
+    if ((rc = resolve_workspace(shape, workspace, &ws))) return rc;
+    return launch_combine(*shape, M, ws, static_cast<__nv_bfloat16*>(out_bf16), static_cast<cudaStream_t>(stream));
+}
+
+int vmoe_forward(const vmoe_shape* shape, const vmoe_weights* routed, const vmoe_weights* shared,
+                 const void* hidden_bf16, const float* router_logits, const int32_t* topk_ids,
+                 const float* topk_weights, const int32_t* expert_map, void* out_bf16, int32_t M,
+                 void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = check_call(shape, routed, shared, M, workspace);
+    if (rc) return rc;
+    if (!hidden_bf16 || !out_bf16) return VMOE_ERR_NULL;
+    if (!router_logits && !(topk_ids && topk_weights)) return VMOE_ERR_NULL;
+    if (!aligned16(hidden_bf16) || !aligned16(out_bf16)) return VMOE_ERR_ALIGN;
+    if (workspace_bytes < vmoe_workspace_bytes(shape)) return VMOE_ERR_WORKSPACE;
+    if (M == 0) return VMOE_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    Workspace ws;
+    if ((rc = resolve_workspace(shape, workspace, &ws))) return rc;
+    const WeightSet r = to_set(routed), sh = to_set(shape->has_shared ? shared : nullptr);
+    if (router_logits) {
+        if ((rc = launch_route(router_logits, M, shape->num_global_experts, shape->topk, ws.topk_ids,
+                               ws.topk_weights, st))) return rc;
+        topk_ids = ws.topk_ids; topk_weights = ws.topk_weights;
+    }
+    if ((rc = launch_tables(*shape, topk_ids, topk_weights, expert_map, M, ws, st))) return rc;
+    if ((rc = launch_quantize(static_cast<const __nv_bfloat16*>(hidden_bf16), M, shape->hidden, ws.act_q,
+                              ws.act_sf, st))) return rc;
+    if ((rc = launch_gate_up(*shape, r, sh, M, ws, st))) return rc;
+    if ((rc = launch_down(*shape, r, sh, M, ws, st))) return rc;
+    return launch_combine(*shape, M, ws, static_cast<__nv_bfloat16*>(out_bf16), st);
+}
+
+int vmoe_read_status(void* workspace, const vmoe_shape* shape, void* stream) {
+    Workspace ws;
+    int rc = resolve_workspace(shape, workspace, &ws);
+    if (rc) return rc;
+    int32_t v = 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cudaMemcpyAsync(&v, ws.counters + CNT_STATUS, 4, cudaMemcpyDeviceToHost, st) != cudaSuccess) return VMOE_ERR_CUDA;
+    if (cudaStreamSynchronize(st) != cudaSuccess) return VMOE_ERR_CUDA;
+    if (v != 0) cudaMemsetAsync(ws.counters + CNT_STATUS, 0, 4, st);
+    return v;
+}
+
+}  // extern "C"

@@ -1,0 +1,106 @@
+// bf16 -> NVFP4 activation quantiser, the NVFP4 -> f32 decoder and the deterministic combine.
+//
+// Quantiser arithmetic: fused-moe/csrc/verdict_fused_cooperative_tma_ext.cu:249-279 of the
+// reference (per 16 consecutive elements: amax / 6 floored at 1e-30 -> E4M3 RNE saturating ->
+// decoded scale floored at 1e-30 -> e2m1(x / scale), even element in the low nibble).
+// Combine: …tma_ext.cu:549-563 (fp32 sum over a token's pairs in ascending pair order -> bf16).
+#include "vmoe_common.cuh"
+
+namespace vmoe {
+
+// One thread per 16-element block: 32 bytes in, 8 + 1 bytes out.
+__global__ void __launch_bounds__(256)
+quantize_kernel(const __nv_bfloat16* __restrict__ x, long long nblocks, int blocks_per_row,
+                uint8_t* __restrict__ packed, uint8_t* __restrict__ sf) {
+    const long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= nblocks) return;
+    const uint4* src = reinterpret_cast<const uint4*>(x + b * SF_BLOCK);
+    uint4 raw[2] = {src[0], src[1]};
+    const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(raw);
+    float v[SF_BLOCK];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < SF_BLOCK; ++i) { v[i] = __bfloat162float(h[i]); amax = fmaxf(amax, fabsf(v[i])); }
+    const float target = fmaxf(amax / 6.0f, 1e-30f);
+    const uint8_t sb = e4m3_encode(target);
+    float scale = e4m3_decode(sb);
+    if (scale < 1e-30f) scale = 1e-30f;
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)  lo |= e2m1_encode(v[i] / scale) << (4 * i);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)  hi |= e2m1_encode(v[8 + i] / scale) << (4 * i);
+    reinterpret_cast<uint2*>(packed)[b] = make_uint2(lo, hi);
+    sf[b] = sb;
+    (void)blocks_per_row;
+}
+
+int launch_quantize(const __nv_bfloat16* x, int rows, int K, uint8_t* packed, uint8_t* sf, cudaStream_t st) {
+    const long long nblocks = (long long)rows * (K / SF_BLOCK);
+    if (nblocks == 0) return VMOE_OK;
+    quantize_kernel<<<(unsigned)((nblocks + 255) / 256), 256, 0, st>>>(x, nblocks, K / SF_BLOCK, packed, sf);
+    return cuda_status(cudaGetLastError());
+}
+
+__global__ void __launch_bounds__(256)
+dequantize_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ sf,
+                  const float* __restrict__ gs, long long nblocks, int blocks_per_row,
+                  long long rows_per_scale, float* __restrict__ out) {
+    const long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= nblocks) return;
+    const uint2 c = reinterpret_cast<const uint2*>(packed)[b];
+    const float s = e4m3_decode(sf[b]);
+    const float g = gs ? gs[(b / blocks_per_row) / rows_per_scale] : 1.0f;
+    float* o = out + b * SF_BLOCK;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = e2m1_decode((c.x >> (4 * i)) & 0xF) * s * g;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[8 + i] = e2m1_decode((c.y >> (4 * i)) & 0xF) * s * g;
+}
+
+int launch_dequantize(const uint8_t* packed, const uint8_t* sf, const float* gs, int64_t rows, int K,
+                      int64_t rows_per_scale, float* out, cudaStream_t st) {
+    const long long nblocks = (long long)rows * (K / SF_BLOCK);
+    if (nblocks == 0) return VMOE_OK;
+    dequantize_kernel<<<(unsigned)((nblocks + 255) / 256), 256, 0, st>>>(
+        packed, sf, gs, nblocks, K / SF_BLOCK, rows_per_scale > 0 ? rows_per_scale : 1, out);
+    return cuda_status(cudaGetLastError());
+}
+
+// out[m, :] = bf16( sum_j pair_out[slot(m, j), :]  (ascending j, fp32)  + shared row )
+// one thread per 4 consecutive columns.
+__global__ void __launch_bounds__(256)
+combine_kernel(const float* __restrict__ pair_out, const int32_t* __restrict__ pair_slot,
+               const int32_t* __restrict__ expert_offsets, int M, int K, int T, int E, int has_shared,
+               __nv_bfloat16* __restrict__ out) {
+    const int k4 = K / 4;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)M * k4) return;
+    const int m = (int)(i / k4), c = (int)(i % k4);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < T; ++j) {
+        const int slot = pair_slot[m * T + j];
+        if (slot >= 0) {
+            const float4 v = reinterpret_cast<const float4*>(pair_out + (size_t)slot * K)[c];
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+    }
+    if (has_shared) {
+        const int slot = expert_offsets[E] + m;
+        const float4 v = reinterpret_cast<const float4*>(pair_out + (size_t)slot * K)[c];
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+    uint2 o; o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
+    reinterpret_cast<uint2*>(out + (size_t)m * K)[c] = o;
+}
+
+int launch_combine(const vmoe_shape& s, int M, const Workspace& ws, __nv_bfloat16* out, cudaStream_t st) {
+    const long long n = (long long)M * (s.hidden / 4);
+    if (n == 0) return VMOE_OK;
+    combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
+        ws.pair_out, ws.pair_slot, ws.expert_offsets, M, s.hidden, s.topk, s.num_experts, s.has_shared, out);
+    return cuda_status(cudaGetLastError());
+}
+
+}  // namespace vmoe

@@ -1,0 +1,228 @@
+// Router (softmax + top-k + renormalise) and the permutation of pairs by expert.
+//
+// Router semantics: fused-moe/csrc/megakernel_v1.cu:491-537 of the reference (fp32 softmax,
+// strict '>' selection so the lowest expert id wins a tie, descending order, renormalise).
+// Permutation semantics: fused-moe/csrc/verdict_fused_grouped.cu:655-691 (stable sort of the
+// token-major pairs by expert id, expert offsets, gather indices, scatter weights).
+#include "vmoe_common.cuh"
+
+namespace vmoe {
+
+// ---------------------------------------------------------------------------------
+// Router: one warp per token.  Probabilities live in shared memory; each of the T
+// rounds takes the arg-max under the order (probability desc, expert id asc).
+// ---------------------------------------------------------------------------------
+constexpr int ROUTE_WARPS = 4;
+
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+route_kernel(const float* __restrict__ logits, int M, int E, int T,
+             int32_t* __restrict__ topk_ids, float* __restrict__ topk_w) {
+    extern __shared__ float s_prob[];            // [ROUTE_WARPS][E]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m = blockIdx.x * ROUTE_WARPS + warp;
+    if (m >= M) return;
+    float* p = s_prob + (size_t)warp * E;
+    const float* l = logits + (size_t)m * E;
+
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) { float v = l[e]; p[e] = v; mx = fmaxf(mx, v); }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) { float v = expf(p[e] - mx); p[e] = v; sum += v; }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = 1.0f / sum;
+    for (int e = lane; e < E; e += 32) p[e] *= inv;
+    __syncwarp();
+
+    float sel_w = 0.f; int sel_id = 0; float wsum = 0.f;   // lane j keeps the j-th selection
+    for (int j = 0; j < T; ++j) {
+        float bv = -1.0f; int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) { float v = p[e]; if (v > bv) { bv = v; bi = e; } }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            int   oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == j) { sel_w = bv; sel_id = bi; }
+        if (lane == 0) p[bi] = -2.0f;            // taken
+        wsum += bv;                              // same value in every lane, rank order
+        __syncwarp();
+    }
+    const float winv = 1.0f / wsum;
+    if (lane < T) {
+        topk_ids[(size_t)m * T + lane] = sel_id;
+        topk_w[(size_t)m * T + lane] = sel_w * winv;
+    }
+}
+
+int launch_route(const float* logits, int M, int E, int T, int32_t* ids, float* w, cudaStream_t st) {
+    if (M == 0) return VMOE_OK;
+    const size_t smem = (size_t)ROUTE_WARPS * E * sizeof(float);
+    if (smem > 200 * 1024) return VMOE_ERR_SHAPE;
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    route_kernel<<<(M + ROUTE_WARPS - 1) / ROUTE_WARPS, ROUTE_WARPS * 32, smem, st>>>(logits, M, E, T, ids, w);
+    return cuda_status(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------------
+// Permutation by expert.
+//
+// A token selects an expert at most once, so the stable rank of pair (m, j) inside
+// expert e is the number of tokens m' < m that selected e.  Phase A sets bit m of row e
+// of an [E, ceil(M/32)] bitmap; phase B gives every expert its pair count, the
+// exclusive scan over experts, a running popcount per bitmap word and its share of the
+// GEMV work-unit list; phase C places each pair at offset[e] + word_prefix + popc(bits
+// below m).  Deterministic, no sorting network, no atomics on the result.
+// The always-on shared expert is expert id E: slot range [offset[E], offset[E] + M),
+// pair index P + m, weight 1.0.
+// ---------------------------------------------------------------------------------
+struct TableArgs {
+    const int32_t* ids; const float* w; const int32_t* expert_map;
+    int M, T, E, has_shared, words;   // words = ceil(M / 32)
+    Workspace ws;
+};
+
+__device__ __forceinline__ int local_expert(const TableArgs& a, int p) {
+    int e = a.ids[p];
+    if (a.expert_map) e = a.expert_map[e];
+    return (e >= 0 && e < a.E) ? e : -1;
+}
+
+__device__ void phase_clear(const TableArgs& a, int tid, int nthr) {
+    const int n = a.E * a.words;
+    for (int i = tid; i < n; i += nthr) a.ws.bitmap[i] = 0u;
+    if (tid < CNT_N && tid != CNT_STATUS) a.ws.counters[tid] = 0;
+}
+__device__ void phase_mark(const TableArgs& a, int tid, int nthr) {
+    const int P = a.M * a.T;
+    for (int p = tid; p < P; p += nthr) {
+        const int e = local_expert(a, p);
+        if (e >= 0) { const int m = p / a.T; atomicOr(&a.ws.bitmap[(size_t)e * a.words + (m >> 5)], 1u << (m & 31)); }
+    }
+}
+// one warp per expert: running popcount per word; returns the expert's pair count to lane 0
+__device__ void phase_count(const TableArgs& a, int warp, int nwarps, int lane, int32_t* s_count) {
+    for (int e = warp; e < a.E; e += nwarps) {
+        int running = 0;
+        for (int w0 = 0; w0 < a.words; w0 += 32) {
+            const int w = w0 + lane;
+            const int c = (w < a.words) ? __popc(a.ws.bitmap[(size_t)e * a.words + w]) : 0;
+            int incl = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
+            if (w < a.words) a.ws.word_prefix[(size_t)e * a.words + w] = running + incl - c;
+            running += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) s_count[e] = running;
+    }
+}
+// single CTA: exclusive scan of counts -> expert_offsets, unit list
+__device__ void phase_scan(const TableArgs& a, int tid, int nthr, const int32_t* s_count, int32_t* s_scan) {
+    // chunked serial-per-thread scan: thread i owns experts [i*per, (i+1)*per)
+    const int n = a.E + (a.has_shared ? 1 : 0);
+    const int per = (n + nthr - 1) / nthr;
+    int csum = 0, usum = 0;
+    for (int k = 0; k < per; ++k) {
+        const int e = tid * per + k;
+        if (e < n) { const int c = (e < a.E) ? s_count[e] : a.M; csum += c; usum += (c + TOK_PER_UNIT - 1) / TOK_PER_UNIT; }
+    }
+    s_scan[tid] = csum; s_scan[nthr + tid] = usum;
+    __syncthreads();
+    if (tid == 0) {
+        int c = 0, u = 0;
+        for (int i = 0; i < nthr; ++i) { int tc = s_scan[i], tu = s_scan[nthr + i]; s_scan[i] = c; s_scan[nthr + i] = u; c += tc; u += tu; }
+        a.ws.counters[CNT_UNITS] = u; a.ws.counters[CNT_SLOTS] = c;
+        a.ws.expert_offsets[n] = c;
+        if (!a.has_shared) a.ws.expert_offsets[n + 1] = c;
+    }
+    __syncthreads();
+    int c = s_scan[tid], u = s_scan[nthr + tid];
+    for (int k = 0; k < per; ++k) {
+        const int e = tid * per + k;
+        if (e < n) {
+            const int cnt = (e < a.E) ? s_count[e] : a.M;
+            a.ws.expert_offsets[e] = c;
+            for (int s = 0; s < cnt; s += TOK_PER_UNIT)
+                a.ws.units[u++] = make_int4(e, c + s, min(TOK_PER_UNIT, cnt - s), 0);
+            c += cnt;
+        }
+    }
+}
+__device__ void phase_place(const TableArgs& a, int tid, int nthr) {
+    const int P = a.M * a.T;
+    for (int p = tid; p < P; p += nthr) {
+        const int e = local_expert(a, p);
+        int slot = -1;
+        if (e >= 0) {
+            const int m = p / a.T;
+            const size_t wi = (size_t)e * a.words + (m >> 5);
+            slot = a.ws.expert_offsets[e] + a.ws.word_prefix[wi] + __popc(a.ws.bitmap[wi] & ((1u << (m & 31)) - 1u));
+            a.ws.sorted_pair[slot] = p;
+            a.ws.gather_idx[slot] = m;
+            a.ws.scatter_weights[slot] = a.w[p];
+        }
+        a.ws.pair_slot[p] = slot;
+    }
+    if (a.has_shared) {
+        const int base = a.ws.expert_offsets[a.E];
+        for (int m = tid; m < a.M; m += nthr) {
+            a.ws.sorted_pair[base + m] = P + m;
+            a.ws.gather_idx[base + m] = m;
+            a.ws.scatter_weights[base + m] = 1.0f;
+        }
+    }
+}
+
+constexpr int TABLE_THREADS = 1024;
+
+// small problems: everything in one CTA
+__global__ void __launch_bounds__(TABLE_THREADS) tables_fused_kernel(TableArgs a) {
+    extern __shared__ int32_t s_mem[];          // [E] counts + [2 * nthr] scan
+    int32_t* s_count = s_mem; int32_t* s_scan = s_mem + a.E;
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    phase_clear(a, tid, nthr);       __syncthreads();
+    phase_mark(a, tid, nthr);        __syncthreads();
+    phase_count(a, tid >> 5, nthr >> 5, tid & 31, s_count); __syncthreads();
+    phase_scan(a, tid, nthr, s_count, s_scan); __syncthreads();
+    phase_place(a, tid, nthr);
+}
+// large problems: grid-wide phases as separate launches
+__global__ void tables_clear_kernel(TableArgs a) { phase_clear(a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x); }
+__global__ void tables_mark_kernel(TableArgs a)  { phase_mark(a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x); }
+__global__ void __launch_bounds__(TABLE_THREADS) tables_scan_kernel(TableArgs a) {
+    extern __shared__ int32_t s_mem[];
+    int32_t* s_count = s_mem; int32_t* s_scan = s_mem + a.E;
+    phase_count(a, threadIdx.x >> 5, blockDim.x >> 5, threadIdx.x & 31, s_count); __syncthreads();
+    phase_scan(a, threadIdx.x, blockDim.x, s_count, s_scan);
+}
+__global__ void tables_place_kernel(TableArgs a) { phase_place(a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x); }
+
+int launch_tables(const vmoe_shape& s, const int32_t* ids, const float* w, const int32_t* expert_map,
+                  int M, const Workspace& ws, cudaStream_t st) {
+    TableArgs a;
+    a.ids = ids; a.w = w; a.expert_map = expert_map;
+    a.M = M; a.T = s.topk; a.E = s.num_experts; a.has_shared = s.has_shared; a.words = (M + 31) / 32;
+    a.ws = ws;
+    const size_t smem = ((size_t)a.E + 2 * TABLE_THREADS) * sizeof(int32_t);
+    if (smem > 200 * 1024) return VMOE_ERR_SHAPE;
+    if (smem > 48 * 1024) {
+        cudaFuncSetAttribute(tables_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(tables_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
+    if ((long long)M * s.topk <= 16384) {
+        tables_fused_kernel<<<1, TABLE_THREADS, smem, st>>>(a);
+    } else {
+        const int blocks = 296;
+        tables_clear_kernel<<<blocks, 256, 0, st>>>(a);
+        tables_mark_kernel<<<blocks, 256, 0, st>>>(a);
+        tables_scan_kernel<<<1, TABLE_THREADS, smem, st>>>(a);
+        tables_place_kernel<<<blocks, 256, 0, st>>>(a);
+    }
+    return cuda_status(cudaGetLastError());
+}
+
+}  // namespace vmoe
