@@ -1,6 +1,7 @@
 """In-tree build of the CUDA library (``libvmoe.so``) for sm_100a with plain nvcc.
 
-``python -m sm120_moe_bench_b200.build`` (or ``build_library()``) compiles every ``csrc/*.cu``
+``python sm120_moe_bench_b200/build.py`` (or ``build_library()``; run it as a script, because
+importing the package needs the finished library) compiles every ``csrc/*.cu``
 into one shared object next to this file.  nvcc cross-compiles without a GPU.  No fast-math:
 the SwiGLU and the scale divisions need IEEE ``expf`` and division (the reference builds
 without it for the same reason, fused-moe/verdict_moe.py:67-76).
