@@ -160,6 +160,25 @@ int vmoe_stage_combine(const vmoe_shape* shape, int32_t M, void* workspace,
  * counterpart (its waits are unbounded: …tma_ext.cu:156-167). */
 int vmoe_read_status(void* workspace, const vmoe_shape* shape, void* stream);
 
+/* Permutation by expert for callers that cannot allocate device memory.  It has no
+ * counterpart in the reference.  Same tables as vmoe_build_tables, but written to arrays the
+ * caller passes (expert_offsets [E + 2], sorted_pair / gather_idx / scatter_weights
+ * [M*T + (has_shared ? M : 0)], pair_slot [M*T]) and with all scratch in a fixed array inside the
+ * library, so the call needs no workspace and performs no allocation of any kind.  It is meant
+ * for hosts that only own the buffers they were given at this point -- a serving worker whose
+ * memory pool already fills the GPU, or a thin FFI binding with no allocator.
+ * Limits: M <= 1024 tokens, E <= 1024 local experts, T <= 16 (VMOE_ERR_LIMIT beyond them); the
+ * scratch array is about 342 KiB per GPU that loads the library and is kept until the process
+ * exits.  The first call on each device looks up the array's device address (that device must
+ * be current); make that first call before any stream capture.  All calls share the one array,
+ * which is cleared at the start of each call: calls that overlap on the GPU (two streams, two
+ * threads) race and must be serialised by the caller. */
+int vmoe_permute_noalloc(const int32_t* topk_ids, const float* topk_weights,
+                         const int32_t* expert_map, int32_t M, int32_t T, int32_t E,
+                         int32_t has_shared, int32_t* expert_offsets, int32_t* sorted_pair,
+                         int32_t* pair_slot, int32_t* gather_idx, float* scatter_weights,
+                         void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -51,6 +51,8 @@ SIGNATURES = {
                                   C.c_int32, _P, _P]),
     "vmoe_stage_combine": (C.c_int, [C.POINTER(VmoeShape), C.c_int32, _P, _P, _P]),
     "vmoe_read_status": (C.c_int, [_P, C.POINTER(VmoeShape), _P]),
+    "vmoe_permute_noalloc": (C.c_int, [_P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                       _P, _P, _P, _P, _P, _P]),
 }
 
 
@@ -64,7 +66,7 @@ class VmoeError(RuntimeError):
 def _load() -> C.CDLL:
     if not LIB_PATH.exists():
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m sm120_moe_bench_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python sm120_moe_bench_b200/build.py` "
             "(there is no CPU or PyTorch fallback for this operator)")
     handle = C.CDLL(str(LIB_PATH))
     for name, (res, args) in SIGNATURES.items():

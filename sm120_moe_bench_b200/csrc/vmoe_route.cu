@@ -226,3 +226,89 @@ int launch_tables(const vmoe_shape& s, const int32_t* ids, const float* w, const
 }
 
 }  // namespace vmoe
+
+namespace vmoe {
+
+// ---------------------------------------------------------------------------------
+// vmoe_permute_noalloc: the permutation for callers that cannot obtain device memory.
+//
+// Some hosts of this library are handed a fixed set of input and output buffers and have
+// no way to get one more byte of device memory at the point of the call: a serving worker
+// whose memory pool was sized to fill the GPU (a cudaMalloc there fails or steals from the
+// KV cache), or a thin C / FFI binding that owns no allocator at all.  For them the scratch
+// of the permutation (the expert x token bitmap, its running popcounts, the work-unit list
+// and the counters) lives in the file-scope array below instead of a caller-owned workspace.
+// The array exists once per GPU that loads the library and stays until the process exits;
+// its size fixes the largest problem the entry point accepts.
+// ---------------------------------------------------------------------------------
+constexpr int NOALLOC_MAX_TOKENS  = 1024;   // M
+constexpr int NOALLOC_MAX_EXPERTS = 1024;   // local experts E
+constexpr int NOALLOC_WORDS       = NOALLOC_MAX_TOKENS / 32;
+constexpr size_t NOALLOC_BITMAP_BYTES = (size_t)NOALLOC_MAX_EXPERTS * NOALLOC_WORDS * 4;          // 128 KiB
+constexpr size_t NOALLOC_UNITS = NOALLOC_MAX_EXPERTS + 1 + ((size_t)NOALLOC_MAX_TOKENS * (MAX_TOPK + 1) + TOK_PER_UNIT - 1) / TOK_PER_UNIT;
+constexpr size_t NOALLOC_OFF_PREFIX   = NOALLOC_BITMAP_BYTES;
+constexpr size_t NOALLOC_OFF_UNITS    = 2 * NOALLOC_BITMAP_BYTES;
+constexpr size_t NOALLOC_OFF_COUNTERS = NOALLOC_OFF_UNITS + ((NOALLOC_UNITS * 16 + 255) / 256) * 256;
+constexpr size_t NOALLOC_SCRATCH_BYTES = NOALLOC_OFF_COUNTERS + 256;                                // ~ 342 KiB
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+// In host code the name g_noalloc_scratch is only a handle for the symbol; the device address
+// is looked up once per device (with that device current) and kept here.
+constexpr int NOALLOC_MAX_DEVICES = 64;
+static unsigned char* g_noalloc_addr[NOALLOC_MAX_DEVICES] = {nullptr};
+
+static int noalloc_scratch_address(unsigned char** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return VMOE_ERR_CUDA;
+    if (g_noalloc_addr[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) return VMOE_ERR_CUDA;
+        g_noalloc_addr[dev] = static_cast<unsigned char*>(p);
+    }
+    *out = g_noalloc_addr[dev];
+    return VMOE_OK;
+}
+
+// Same phases as tables_fused_kernel, over caller outputs + the static scratch.  The first
+// phase clears the bitmap and the counters, so nothing of an earlier call survives.
+__global__ void __launch_bounds__(TABLE_THREADS) tables_noalloc_kernel(TableArgs a) {
+    extern __shared__ int32_t s_mem[];
+    int32_t* s_count = s_mem; int32_t* s_scan = s_mem + a.E;
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    phase_clear(a, tid, nthr);       __syncthreads();
+    phase_mark(a, tid, nthr);        __syncthreads();
+    phase_count(a, tid >> 5, nthr >> 5, tid & 31, s_count); __syncthreads();
+    phase_scan(a, tid, nthr, s_count, s_scan); __syncthreads();
+    phase_place(a, tid, nthr);
+}
+
+}  // namespace vmoe
+
+extern "C" int vmoe_permute_noalloc(const int32_t* topk_ids, const float* topk_weights,
+                                    const int32_t* expert_map, int32_t M, int32_t T, int32_t E,
+                                    int32_t has_shared, int32_t* expert_offsets, int32_t* sorted_pair,
+                                    int32_t* pair_slot, int32_t* gather_idx, float* scatter_weights,
+                                    void* stream) {
+    using namespace vmoe;
+    if (!topk_ids || !topk_weights || !expert_offsets || !sorted_pair || !pair_slot || !gather_idx || !scatter_weights)
+        return VMOE_ERR_NULL;
+    if (M < 0 || T <= 0 || T > MAX_TOPK || E <= 0) return VMOE_ERR_SHAPE;
+    if (M > NOALLOC_MAX_TOKENS || E > NOALLOC_MAX_EXPERTS) return VMOE_ERR_LIMIT;
+    unsigned char* scratch = nullptr;
+    const int rc = noalloc_scratch_address(&scratch);
+    if (rc) return rc;
+    TableArgs a;
+    a.ids = topk_ids; a.w = topk_weights; a.expert_map = expert_map;
+    a.M = M; a.T = T; a.E = E; a.has_shared = has_shared ? 1 : 0; a.words = (M + 31) / 32;
+    a.ws = Workspace{};
+    a.ws.expert_offsets = expert_offsets; a.ws.sorted_pair = sorted_pair; a.ws.pair_slot = pair_slot;
+    a.ws.gather_idx = gather_idx; a.ws.scatter_weights = scatter_weights;
+    a.ws.bitmap      = reinterpret_cast<uint32_t*>(scratch);
+    a.ws.word_prefix = reinterpret_cast<int32_t*>(scratch + NOALLOC_OFF_PREFIX);
+    a.ws.units       = reinterpret_cast<int4*>(scratch + NOALLOC_OFF_UNITS);
+    a.ws.counters    = reinterpret_cast<int32_t*>(scratch + NOALLOC_OFF_COUNTERS);
+    const size_t smem = ((size_t)E + 2 * TABLE_THREADS) * sizeof(int32_t);   // <= 12 KiB at the maximum E
+    tables_noalloc_kernel<<<1, TABLE_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(a);
+    return cuda_status(cudaGetLastError());
+}
