@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define VMOE_ABI_VERSION 1
+#define VMOE_ABI_VERSION 2
 
 enum vmoe_status {
     VMOE_OK = 0,
@@ -49,15 +49,18 @@ enum vmoe_status {
  * (K, N_half, num_pairs) integer arguments of its forward functions
  * (fused-moe/csrc/verdict_fused_cooperative_tma_ext.cu:32, :594-596). */
 typedef struct vmoe_shape {
-    int32_t hidden;       /* K: multiple of 128, <= 8192 */
-    int32_t inter;        /* N: multiple of 128, <= 2048 */
+    int32_t hidden;       /* K: multiple of 128, <= 4096 (tensor-core path: multiple of 256) */
+    int32_t inter;        /* N: multiple of 128, <= 1024 (tensor-core path: multiple of 256) */
     int32_t num_experts;  /* E: routed experts whose weights this GPU holds */
     int32_t topk;         /* T: 1..16 */
     int32_t max_tokens;   /* largest M the workspace must serve */
     int32_t has_shared;   /* 1: an always-on shared expert is applied to every token */
     int32_t num_global_experts; /* width of router logits / range of topk ids (== E without expert parallelism) */
-    int32_t reserved;
+    int32_t path;         /* 0 = automatic (tensor-core path when the weights carry prepared scales, else the
+                             streaming GEMV path), 1 = streaming GEMV on CUDA cores, 2 = tcgen05 tensor-core path */
 } vmoe_shape;
+
+enum vmoe_path { VMOE_PATH_AUTO = 0, VMOE_PATH_GEMV = 1, VMOE_PATH_TC = 2 };
 
 /* One set of NVFP4 expert weights (device pointers).  Replaces the (w1, w1_sf,
  * w1_alpha, w2, w2_sf, w2_alpha) tensor arguments of the reference's forward
@@ -70,6 +73,11 @@ typedef struct vmoe_weights {
     const uint8_t* w2;
     const uint8_t* w2_sf;
     const float*   w2_gs;
+    /* Optional: the same block scales re-laid by vmoe_prepare_sf for the tensor-core path
+     * ([rows/128][K/64][512 bytes]); NULL = not prepared.  The reference has no such copy: it
+     * explicitly keeps scales linear (fused-moe/FINAL_SUMMARY.md:104-111). */
+    const uint8_t* w13_sf_atoms;
+    const uint8_t* w2_sf_atoms;
 } vmoe_weights;
 
 /* Byte offsets of the intermediate tables inside the workspace, so that a test or
@@ -94,6 +102,11 @@ typedef struct vmoe_ws_layout {
     size_t pair_out;        /* f32 [P + M, K] weighted down-projection rows per sorted slot */
     size_t bitmap;          /* u32 [E, ceil(M/32)] scratch of the permutation */
     size_t word_prefix;     /* int32 [E, ceil(M/32)] scratch of the permutation */
+    size_t tc_units;        /* int32 [max_tc_units, 4]: (expert, first slot, tokens, UMMA N) units of <= 64 tokens */
+    size_t tc_unit_base;    /* int32 [E + 1]: first tensor-core unit of each expert */
+    size_t act_q_sorted;    /* u8 [P + M, K/2] quantised activations in sorted-slot order (B operand of GEMM1) */
+    size_t act_sf_atoms;    /* u8 [max_tc_units, K/64, 512] activation scales, 128-row x 4-scale atoms per unit */
+    size_t inter_sf_atoms;  /* u8 [max_tc_units, N/64, 512] intermediate scales, same layout */
 } vmoe_ws_layout;
 
 int         vmoe_abi_version(void);
@@ -125,6 +138,16 @@ int vmoe_build_tables(const vmoe_shape* shape, const int32_t* topk_ids,
  * bf16_to_nvfp4_e4m3_kernel (fused-moe/csrc/verdict_fused_ext.cu:154-192). */
 int vmoe_quantize(const void* x_bf16, int32_t rows, int32_t K,
                   uint8_t* packed, uint8_t* sf, void* stream);
+
+/* One-time re-layout of linear E4M3 block scales [rows, K/16] into the 128-row x 4-scale atoms the
+ * tcgen05 block-scaled MMA reads ([rows/128][K/64][512 bytes], same size as the input); rows must
+ * be a multiple of 128, K of 64.  NaN patterns are stored as 0x00 (they decode to zero in the
+ * reference, …tma_ext.cu:48-55); *bad_count (device int32, caller zeroes it) is incremented for
+ * every byte with the sign bit set -- such weights must not be used with the tensor-core path.
+ * Done once per weight tensor at load time; the reference has no counterpart (its scales stay
+ * linear, fused-moe/verdict_moe.py:519-520). */
+int vmoe_prepare_sf(const uint8_t* sf, int64_t rows, int32_t K, uint8_t* atoms,
+                    int32_t* bad_count, void* stream);
 
 /* Decode NVFP4 to f32: value = e2m1(code) * e4m3(block scale) * global_scale[row_group].
  * rows_per_scale rows share one entry of global_scale (NULL = 1.0).  Replaces

@@ -15,17 +15,19 @@ LIB_PATH = PKG / "libvmoe.so"
 class VmoeShape(C.Structure):
     _fields_ = [("hidden", C.c_int32), ("inter", C.c_int32), ("num_experts", C.c_int32),
                 ("topk", C.c_int32), ("max_tokens", C.c_int32), ("has_shared", C.c_int32),
-                ("num_global_experts", C.c_int32), ("reserved", C.c_int32)]
+                ("num_global_experts", C.c_int32), ("path", C.c_int32)]
 
 
 class VmoeWeights(C.Structure):
     _fields_ = [("w13", C.c_void_p), ("w13_sf", C.c_void_p), ("w13_gs", C.c_void_p),
-                ("w2", C.c_void_p), ("w2_sf", C.c_void_p), ("w2_gs", C.c_void_p)]
+                ("w2", C.c_void_p), ("w2_sf", C.c_void_p), ("w2_gs", C.c_void_p),
+                ("w13_sf_atoms", C.c_void_p), ("w2_sf_atoms", C.c_void_p)]
 
 
 _LAYOUT_FIELDS = ["total_bytes", "topk_ids", "topk_weights", "expert_offsets", "sorted_pair",
                   "pair_slot", "gather_idx", "scatter_weights", "units", "counters", "act_q",
-                  "act_sf", "inter_q", "inter_sf", "pair_out", "bitmap", "word_prefix"]
+                  "act_sf", "inter_q", "inter_sf", "pair_out", "bitmap", "word_prefix", "tc_units",
+                  "tc_unit_base", "act_q_sorted", "act_sf_atoms", "inter_sf_atoms"]
 
 
 class VmoeWsLayout(C.Structure):
@@ -42,6 +44,7 @@ SIGNATURES = {
     "vmoe_route": (C.c_int, [_P, C.c_int32, C.c_int32, C.c_int32, _P, _P, _P]),
     "vmoe_build_tables": (C.c_int, [C.POINTER(VmoeShape), _P, _P, _P, C.c_int32, _P, C.c_size_t, _P]),
     "vmoe_quantize": (C.c_int, [_P, C.c_int32, C.c_int32, _P, _P, _P]),
+    "vmoe_prepare_sf": (C.c_int, [_P, C.c_int64, C.c_int32, _P, _P, _P]),
     "vmoe_dequantize": (C.c_int, [_P, _P, _P, C.c_int64, C.c_int32, C.c_int64, _P, _P]),
     "vmoe_forward": (C.c_int, [C.POINTER(VmoeShape), C.POINTER(VmoeWeights), C.POINTER(VmoeWeights),
                                _P, _P, _P, _P, _P, _P, C.c_int32, _P, C.c_size_t, _P]),

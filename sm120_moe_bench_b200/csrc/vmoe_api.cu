@@ -13,6 +13,11 @@ int max_units(const vmoe_shape* s) {
     return (int)(s->num_experts + 1 + (P + TOK_PER_UNIT - 1) / TOK_PER_UNIT);
 }
 
+int max_tc_units(const vmoe_shape* s) {
+    const long long P = (long long)s->max_tokens * s->topk + (s->has_shared ? s->max_tokens : 0);
+    return (int)(s->num_experts + 1 + (P + TC_UNIT_TOK - 1) / TC_UNIT_TOK);
+}
+
 static int check_shape(const vmoe_shape* s) {
     if (!s) return VMOE_ERR_NULL;
     if (s->hidden <= 0 || s->hidden % 128 || s->hidden > 4096) return VMOE_ERR_SHAPE;
@@ -21,6 +26,8 @@ static int check_shape(const vmoe_shape* s) {
     if (s->max_tokens < 0) return VMOE_ERR_SHAPE;
     if (s->num_global_experts < s->num_experts) return VMOE_ERR_SHAPE;
     if (s->topk > s->num_global_experts) return VMOE_ERR_SHAPE;
+    if (s->path < 0 || s->path > 2) return VMOE_ERR_SHAPE;
+    if (s->path == VMOE_PATH_TC && (s->hidden % 256 || s->inter % 256)) return VMOE_ERR_SHAPE;
     return VMOE_OK;
 }
 
@@ -49,6 +56,12 @@ int compute_layout(const vmoe_shape* s, vmoe_ws_layout* L) {
     L->pair_out        = take(S * K * 4);
     L->bitmap          = take(E * words * 4);
     L->word_prefix     = take(E * words * 4);
+    const size_t TU = (size_t)max_tc_units(s);
+    L->tc_units        = take(TU * 16);
+    L->tc_unit_base    = take((E + 1) * 4);
+    L->act_q_sorted    = take(S * K / 2);
+    L->act_sf_atoms    = take(TU * (K / 64) * 512);
+    L->inter_sf_atoms  = take(TU * ((N + 63) / 64) * 512);
     L->total_bytes     = off;
     return VMOE_OK;
 }
@@ -74,6 +87,11 @@ int resolve_workspace(const vmoe_shape* s, void* base, Workspace* ws) {
     ws->pair_out        = reinterpret_cast<float*>(b + L.pair_out);
     ws->bitmap          = reinterpret_cast<uint32_t*>(b + L.bitmap);
     ws->word_prefix     = reinterpret_cast<int32_t*>(b + L.word_prefix);
+    ws->tc_units        = reinterpret_cast<int4*>(b + L.tc_units);
+    ws->tc_unit_base    = reinterpret_cast<int32_t*>(b + L.tc_unit_base);
+    ws->act_q_sorted    = b + L.act_q_sorted;
+    ws->act_sf_atoms    = b + L.act_sf_atoms;
+    ws->inter_sf_atoms  = b + L.inter_sf_atoms;
     return VMOE_OK;
 }
 
@@ -89,6 +107,30 @@ static WeightSet to_set(const vmoe_weights* w) {
     WeightSet s{};
     if (w) { s.w13 = w->w13; s.w13_sf = w->w13_sf; s.w13_gs = w->w13_gs; s.w2 = w->w2; s.w2_sf = w->w2_sf; s.w2_gs = w->w2_gs; }
     return s;
+}
+
+static PreparedSet to_prep(const vmoe_weights* r, const vmoe_weights* sh) {
+    PreparedSet p{};
+    if (r) { p.w13_sf_atoms = r->w13_sf_atoms; p.w2_sf_atoms = r->w2_sf_atoms; }
+    if (sh) { p.shared_w13_sf_atoms = sh->w13_sf_atoms; p.shared_w2_sf_atoms = sh->w2_sf_atoms; }
+    return p;
+}
+
+// which path a call takes; VMOE_ERR_* (negative of nothing: plain status) when the request cannot be met
+static int pick_path(const vmoe_shape* s, const vmoe_weights* routed, const vmoe_weights* shared, int* path) {
+    const bool prepared = routed->w13_sf_atoms && routed->w2_sf_atoms &&
+                          (!s->has_shared || (shared->w13_sf_atoms && shared->w2_sf_atoms));
+    const bool shape_ok = (s->hidden % 256 == 0) && (s->inter % 256 == 0);
+    if (s->path == VMOE_PATH_TC) {
+        if (!prepared) return VMOE_ERR_NULL;
+        if (!shape_ok) return VMOE_ERR_SHAPE;
+        *path = VMOE_PATH_TC;
+    } else if (s->path == VMOE_PATH_GEMV) {
+        *path = VMOE_PATH_GEMV;
+    } else {
+        *path = (prepared && shape_ok) ? VMOE_PATH_TC : VMOE_PATH_GEMV;
+    }
+    return VMOE_OK;
 }
 
 static int check_call(const vmoe_shape* s, const vmoe_weights* routed, const vmoe_weights* shared, int M,
@@ -164,6 +206,12 @@ int vmoe_quantize(const void* x_bf16, int32_t rows, int32_t K, uint8_t* packed, 
                            static_cast<cudaStream_t>(stream));
 }
 
+int vmoe_prepare_sf(const uint8_t* sf, int64_t rows, int32_t K, uint8_t* atoms, int32_t* bad_count, void* stream) {
+    if (!sf || !atoms || !bad_count) return VMOE_ERR_NULL;
+    if (rows < 0 || rows % 128 || K <= 0 || K % 64) return VMOE_ERR_SHAPE;
+    return launch_prep_sf(sf, rows, K, atoms, bad_count, static_cast<cudaStream_t>(stream));
+}
+
 int vmoe_dequantize(const uint8_t* packed, const uint8_t* sf, const float* global_scale, int64_t rows,
                     int32_t K, int64_t rows_per_scale, float* out, void* stream) {
     if (!packed || !sf || !out) return VMOE_ERR_NULL;
@@ -179,8 +227,13 @@ int vmoe_stage_gate_up(const vmoe_shape* shape, const vmoe_weights* routed, cons
     if (rc) return rc;
     Workspace ws;
     if ((rc = resolve_workspace(shape, workspace, &ws))) return rc;
-    return launch_gate_up(*shape, to_set(routed), to_set(shape->has_shared ? shared : nullptr), M, ws,
-                          static_cast<cudaStream_t>(stream));
+    int path;
+    if ((rc = pick_path(shape, routed, shared, &path))) return rc;
+    const WeightSet r = to_set(routed), sh = to_set(shape->has_shared ? shared : nullptr);
+    if (path == VMOE_PATH_TC)
+        return launch_tc_gate_up(*shape, r, sh, to_prep(routed, shape->has_shared ? shared : nullptr), M, ws,
+                                 static_cast<cudaStream_t>(stream));
+    return launch_gate_up(*shape, r, sh, M, ws, static_cast<cudaStream_t>(stream));
 }
 
 int vmoe_stage_down(const vmoe_shape* shape, const vmoe_weights* routed, const vmoe_weights* shared,
@@ -189,8 +242,13 @@ int vmoe_stage_down(const vmoe_shape* shape, const vmoe_weights* routed, const v
     if (rc) return rc;
     Workspace ws;
     if ((rc = resolve_workspace(shape, workspace, &ws))) return rc;
-    return launch_down(*shape, to_set(routed), to_set(shape->has_shared ? shared : nullptr), M, ws,
-                       static_cast<cudaStream_t>(stream));
+    int path;
+    if ((rc = pick_path(shape, routed, shared, &path))) return rc;
+    const WeightSet r = to_set(routed), sh = to_set(shape->has_shared ? shared : nullptr);
+    if (path == VMOE_PATH_TC)
+        return launch_tc_down(*shape, r, sh, to_prep(routed, shape->has_shared ? shared : nullptr), M, ws,
+                              static_cast<cudaStream_t>(stream));
+    return launch_down(*shape, r, sh, M, ws, static_cast<cudaStream_t>(stream));
 }
 
 int vmoe_stage_combine(const vmoe_shape* shape, int32_t M, void* workspace, void* out_bf16, void* stream) {
@@ -223,11 +281,21 @@ int vmoe_forward(const vmoe_shape* shape, const vmoe_weights* routed, const vmoe
                                ws.topk_weights, st))) return rc;
         topk_ids = ws.topk_ids; topk_weights = ws.topk_weights;
     }
+    int path;
+    if ((rc = pick_path(shape, routed, shared, &path))) return rc;
     if ((rc = launch_tables(*shape, topk_ids, topk_weights, expert_map, M, ws, st))) return rc;
-    if ((rc = launch_quantize(static_cast<const __nv_bfloat16*>(hidden_bf16), M, shape->hidden, ws.act_q,
-                              ws.act_sf, st))) return rc;
-    if ((rc = launch_gate_up(*shape, r, sh, M, ws, st))) return rc;
-    if ((rc = launch_down(*shape, r, sh, M, ws, st))) return rc;
+    if (path == VMOE_PATH_TC) {
+        const PreparedSet prep = to_prep(routed, shape->has_shared ? shared : nullptr);
+        if ((rc = launch_permute_quantize(*shape, static_cast<const __nv_bfloat16*>(hidden_bf16), topk_ids,
+                                          expert_map, M, ws, st))) return rc;
+        if ((rc = launch_tc_gate_up(*shape, r, sh, prep, M, ws, st))) return rc;
+        if ((rc = launch_tc_down(*shape, r, sh, prep, M, ws, st))) return rc;
+    } else {
+        if ((rc = launch_quantize(static_cast<const __nv_bfloat16*>(hidden_bf16), M, shape->hidden, ws.act_q,
+                                  ws.act_sf, st))) return rc;
+        if ((rc = launch_gate_up(*shape, r, sh, M, ws, st))) return rc;
+        if ((rc = launch_down(*shape, r, sh, M, ws, st))) return rc;
+    }
     return launch_combine(*shape, M, ws, static_cast<__nv_bfloat16*>(out_bf16), st);
 }
 

@@ -120,27 +120,44 @@ __device__ void phase_count(const TableArgs& a, int warp, int nwarps, int lane, 
         if (lane == 0) s_count[e] = running;
     }
 }
-// single CTA: exclusive scan of counts -> expert_offsets, unit list
+// single CTA: exclusive scan of counts -> expert_offsets, GEMV unit list, tensor-core unit list
+__device__ __forceinline__ int tc_box(int n) { return n <= 8 ? 8 : n <= 16 ? 16 : n <= 32 ? 32 : 64; }
 __device__ void phase_scan(const TableArgs& a, int tid, int nthr, const int32_t* s_count, int32_t* s_scan) {
     // chunked serial-per-thread scan: thread i owns experts [i*per, (i+1)*per)
     const int n = a.E + (a.has_shared ? 1 : 0);
     const int per = (n + nthr - 1) / nthr;
-    int csum = 0, usum = 0;
+    int csum = 0, usum = 0, tsum = 0;
     for (int k = 0; k < per; ++k) {
         const int e = tid * per + k;
-        if (e < n) { const int c = (e < a.E) ? s_count[e] : a.M; csum += c; usum += (c + TOK_PER_UNIT - 1) / TOK_PER_UNIT; }
+        if (e < n) {
+            const int c = (e < a.E) ? s_count[e] : a.M;
+            csum += c; usum += (c + TOK_PER_UNIT - 1) / TOK_PER_UNIT; tsum += (c + TC_UNIT_TOK - 1) / TC_UNIT_TOK;
+        }
     }
-    s_scan[tid] = csum; s_scan[nthr + tid] = usum;
+    s_scan[tid] = csum; s_scan[nthr + tid] = usum; s_scan[2 * nthr + tid] = tsum;
     __syncthreads();
-    if (tid == 0) {
-        int c = 0, u = 0;
-        for (int i = 0; i < nthr; ++i) { int tc = s_scan[i], tu = s_scan[nthr + i]; s_scan[i] = c; s_scan[nthr + i] = u; c += tc; u += tu; }
-        a.ws.counters[CNT_UNITS] = u; a.ws.counters[CNT_SLOTS] = c;
-        a.ws.expert_offsets[n] = c;
-        if (!a.has_shared) a.ws.expert_offsets[n + 1] = c;
+    if (tid < 32) {   // warp 0: exclusive scan of the per-thread partial sums, 32 at a time
+        int cb = 0, ub = 0, tb = 0;
+        for (int i0 = 0; i0 < nthr; i0 += 32) {
+            const int i = i0 + tid;
+            const int c = i < nthr ? s_scan[i] : 0, u = i < nthr ? s_scan[nthr + i] : 0, t = i < nthr ? s_scan[2 * nthr + i] : 0;
+            int ci = c, ui = u, ti = t;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int c2 = __shfl_up_sync(0xffffffffu, ci, o), u2 = __shfl_up_sync(0xffffffffu, ui, o), t2 = __shfl_up_sync(0xffffffffu, ti, o);
+                if (tid >= o) { ci += c2; ui += u2; ti += t2; }
+            }
+            if (i < nthr) { s_scan[i] = cb + ci - c; s_scan[nthr + i] = ub + ui - u; s_scan[2 * nthr + i] = tb + ti - t; }
+            cb += __shfl_sync(0xffffffffu, ci, 31); ub += __shfl_sync(0xffffffffu, ui, 31); tb += __shfl_sync(0xffffffffu, ti, 31);
+        }
+        if (tid == 0) {
+            a.ws.counters[CNT_UNITS] = ub; a.ws.counters[CNT_SLOTS] = cb; a.ws.counters[CNT_TC_UNITS] = tb;
+            a.ws.expert_offsets[n] = cb;
+            if (!a.has_shared) a.ws.expert_offsets[n + 1] = cb;
+        }
     }
     __syncthreads();
-    int c = s_scan[tid], u = s_scan[nthr + tid];
+    int c = s_scan[tid], u = s_scan[nthr + tid], t = s_scan[2 * nthr + tid];
     for (int k = 0; k < per; ++k) {
         const int e = tid * per + k;
         if (e < n) {
@@ -148,6 +165,13 @@ __device__ void phase_scan(const TableArgs& a, int tid, int nthr, const int32_t*
             a.ws.expert_offsets[e] = c;
             for (int s = 0; s < cnt; s += TOK_PER_UNIT)
                 a.ws.units[u++] = make_int4(e, c + s, min(TOK_PER_UNIT, cnt - s), 0);
+            if (a.ws.tc_units) {
+                a.ws.tc_unit_base[e] = t;
+                for (int s = 0; s < cnt; s += TC_UNIT_TOK) {
+                    const int nt = min(TC_UNIT_TOK, cnt - s);
+                    a.ws.tc_units[t++] = make_int4(e, c + s, nt, tc_box(nt));
+                }
+            }
             c += cnt;
         }
     }
@@ -181,7 +205,7 @@ constexpr int TABLE_THREADS = 1024;
 
 // small problems: everything in one CTA
 __global__ void __launch_bounds__(TABLE_THREADS) tables_fused_kernel(TableArgs a) {
-    extern __shared__ int32_t s_mem[];          // [E] counts + [2 * nthr] scan
+    extern __shared__ int32_t s_mem[];          // [E] counts + [3 * nthr] scan
     int32_t* s_count = s_mem; int32_t* s_scan = s_mem + a.E;
     const int tid = threadIdx.x, nthr = blockDim.x;
     phase_clear(a, tid, nthr);       __syncthreads();
@@ -207,7 +231,7 @@ int launch_tables(const vmoe_shape& s, const int32_t* ids, const float* w, const
     a.ids = ids; a.w = w; a.expert_map = expert_map;
     a.M = M; a.T = s.topk; a.E = s.num_experts; a.has_shared = s.has_shared; a.words = (M + 31) / 32;
     a.ws = ws;
-    const size_t smem = ((size_t)a.E + 2 * TABLE_THREADS) * sizeof(int32_t);
+    const size_t smem = ((size_t)a.E + 3 * TABLE_THREADS) * sizeof(int32_t);
     if (smem > 200 * 1024) return VMOE_ERR_SHAPE;
     if (smem > 48 * 1024) {
         cudaFuncSetAttribute(tables_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -308,7 +332,7 @@ extern "C" int vmoe_permute_noalloc(const int32_t* topk_ids, const float* topk_w
     a.ws.word_prefix = reinterpret_cast<int32_t*>(scratch + NOALLOC_OFF_PREFIX);
     a.ws.units       = reinterpret_cast<int4*>(scratch + NOALLOC_OFF_UNITS);
     a.ws.counters    = reinterpret_cast<int32_t*>(scratch + NOALLOC_OFF_COUNTERS);
-    const size_t smem = ((size_t)E + 2 * TABLE_THREADS) * sizeof(int32_t);   // <= 12 KiB at the maximum E
+    const size_t smem = ((size_t)E + 3 * TABLE_THREADS) * sizeof(int32_t);   // 16 KiB at the maximum E
     tables_noalloc_kernel<<<1, TABLE_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(a);
     return cuda_status(cudaGetLastError());
 }

@@ -1,0 +1,501 @@
+// Tensor-core path: block-scaled tcgen05.mma (kind::mxf4nvf4, 16-element E4M3 scales) grouped
+// GEMM over the permutation tables, accumulators in TMEM.
+//
+//   tc_gemm_kernel<2> : gate_up projection (a8) + x alpha1 + SiLU*mul + FP4 re-quantisation (a9)
+//   tc_gemm_kernel<1> : down projection (a10) + (router weight x alpha2) scaling per sorted slot
+//
+// Operand roles are swapped with respect to the usual token-major GEMM: the 128 rows of the
+// UMMA tile are WEIGHT rows (A operand, streamed once from HBM by TMA with the 128-byte swizzle),
+// the N dimension (8..64) holds the tokens routed to the expert (B operand, rows of the slot-
+// ordered activation matrix).  With few tokens per expert this is a tensor-core GEMV: the FP4
+// decode happens inside the tensor core instead of on the conversion (XU) pipe, which a CUDA-core
+// GEMV saturates long before HBM does.  The same kernel serves prefill with more tokens per unit.
+//
+// Math follows fused-moe/csrc/verdict_fused_cooperative_tma_ext.cu:323-538 of the reference.
+// Warp roles per persistent CTA: warp 0 = TMA / bulk-copy producer, warp 1 = MMA issuer and TMEM
+// owner, warps 2-5 = epilogue (one TMEM lane quadrant each).  Every wait is bounded.
+#include "vmoe_common.cuh"
+
+#include <string.h>
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+namespace vmoe {
+
+constexpr int TC_THREADS = 192;
+constexpr int TC_ROWS = 128;                 // weight rows per tile (UMMA M)
+constexpr int TC_KB_BYTES = 128;             // bytes of K per row per stage = 256 E2M1 elements
+constexpr int TC_A_TILE = TC_ROWS * TC_KB_BYTES;            // 16 KiB
+constexpr int TC_B_TILE = TC_UNIT_TOK * TC_KB_BYTES;        // 8 KiB
+constexpr int TC_SF_TILE = 4 * 512;                         // four 128-row x 4-scale atoms
+constexpr int TC_TMEM_COLS = 512;
+constexpr int TC_ACC_STRIDE = 128;           // TMEM columns per accumulator buffer (gate | up)
+constexpr int TC_SF_COL0 = 256;              // first TMEM column of the scale-factor area
+constexpr int TC_SF_COLS = 48;               // per parity: 16 (A0) + 16 (A1) + 16 (B)
+
+template <int NA> struct TcCfg {
+    static constexpr int STAGE_BYTES = NA * TC_A_TILE + TC_B_TILE + NA * TC_SF_TILE + TC_SF_TILE;
+    static constexpr int STAGES = (NA == 2) ? 4 : 6;
+    static constexpr int OFF_B = NA * TC_A_TILE;
+    static constexpr int OFF_SFA = OFF_B + TC_B_TILE;
+    static constexpr int OFF_SFB = OFF_SFA + NA * TC_SF_TILE;
+};
+
+struct TcStageInfo { int expert, slot0, ntok, nbox, tile, unit, kb, last; };
+
+struct TcShared {
+    uint64_t full[8], empty[8];
+    uint64_t tmem_full[2], tmem_empty[2];
+    TcStageInfo info[8];
+    TcStageInfo epi[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+struct TcParams {
+    CUtensorMap map_a_routed, map_a_shared;    // weights [rows, K/2] bytes, box 128 x 128, swizzle 128B
+    CUtensorMap map_b[4];                      // activations [slots, K/2] bytes, box 128 x {8,16,32,64}
+    const uint8_t* sfa_routed; const uint8_t* sfa_shared;   // scale atoms [rows/128][K/64][512]
+    const uint8_t* sfb;                         // per-unit scale atoms [unit][K/64][512]
+    const float* gs_routed; const float* gs_shared;
+    Workspace ws;
+    int K;            // reduction length in elements
+    int rows;         // weight rows per expert matrix (2N for gate_up, hidden for down)
+    int N;            // intermediate size
+    int hidden;
+    int E;
+    int tiles;        // items per unit
+    int queue;        // counter index of the work queue
+};
+
+// ---------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                       uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n}\n"
+        ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
+}
+__device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// shared-memory matrix descriptors (sm_100 format: version 1 in bits 46-47)
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
+    // K-major, 128-byte swizzle: rows are 128 bytes apart, 8-row groups 1024 bytes apart
+    return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
+    // no swizzle: 32 rows of 16 bytes, 8-row groups 128 bytes apart
+    return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
+}
+__device__ __forceinline__ uint32_t idesc_nvf4(int n) {
+    // a/b format E2M1 (1), K-major both, N >> 3, scale format UE4M3 (0), M = 128 (>> 4), K = 64
+    return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24);
+}
+
+__device__ __forceinline__ void tc_timeout(const Workspace& ws, TcShared* sh) {
+    atomicExch(&ws.counters[CNT_STATUS], VMOE_ERR_TIMEOUT);
+    atomicExch(&sh->abort_flag, 1);
+}
+
+// ---------------------------------------------------------------------------------
+// The kernel.  NA = 2: gate_up (A0 = gate rows, A1 = up rows of the same 128-n tile);
+//              NA = 1: down.
+// ---------------------------------------------------------------------------------
+template <int NA>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+tc_gemm_kernel(const __grid_constant__ TcParams p) {
+    using Cfg = TcCfg<NA>;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    TcShared* sh = reinterpret_cast<TcShared*>(smem + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    if (tid == 0) {
+        for (int i = 0; i < Cfg::STAGES; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&sh->tmem_full[i], 2); mbar_init(&sh->tmem_empty[i], 4); }
+        sh->abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(TC_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sh->tmem_base;
+    pdl_wait();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------- producer
+        if (lane == 0) {
+            const int num_units = p.ws.counters[CNT_TC_UNITS];
+            const long long total = (long long)num_units * p.tiles;
+            const int kblocks = p.K / 256;
+            uint32_t g = 0;
+            bool ok = true;
+            while (ok) {
+                const long long item = atomicAdd(&p.ws.counters[p.queue], 1);
+                if (item >= total) break;
+                // unit-major order: consecutive items are the row tiles of one unit
+                const int unit = (int)(item / p.tiles), tile = (int)(item % p.tiles);
+                const int4 u = p.ws.tc_units[unit];
+                const bool shd = u.x >= p.E;
+                const int e = shd ? 0 : u.x;
+                const CUtensorMap* ma = shd ? &p.map_a_shared : &p.map_a_routed;
+                const uint8_t* sfa = shd ? p.sfa_shared : p.sfa_routed;
+                const int nbox = u.w;
+                const CUtensorMap* mb = &p.map_b[nbox == 8 ? 0 : nbox == 16 ? 1 : nbox == 32 ? 2 : 3];
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    const int slot = g % Cfg::STAGES;
+                    if (g >= (uint32_t)Cfg::STAGES && !mbar_wait(&sh->empty[slot], ((g / Cfg::STAGES) - 1) & 1)) { ok = false; break; }
+                    if (sh->abort_flag) { ok = false; break; }
+                    uint8_t* st = smem + (size_t)slot * Cfg::STAGE_BYTES;
+                    sh->info[slot] = TcStageInfo{u.x, u.y, u.z, nbox, tile, unit, kb, kb == kblocks - 1};
+                    const uint32_t bytes = NA * (TC_A_TILE + TC_SF_TILE) + nbox * TC_KB_BYTES + TC_SF_TILE;
+                    mbar_arrive_expect_tx(&sh->full[slot], bytes);
+#pragma unroll
+                    for (int a = 0; a < NA; ++a) {
+                        // gate_up: A0 = rows [tile*128, +128) of the gate half, A1 = same rows of the up half
+                        const int row_in_expert = (NA == 2 ? a * p.N : 0) + tile * TC_ROWS;
+                        const long long row = (long long)e * p.rows + row_in_expert;
+                        tma_load_2d(st + a * TC_A_TILE, ma, kb * TC_KB_BYTES, (int)row, &sh->full[slot]);
+                        const size_t atom0 = ((size_t)(row / TC_ROWS) * (p.K / 64) + (size_t)kb * 4) * 512;
+                        bulk_g2s(st + Cfg::OFF_SFA + a * TC_SF_TILE, sfa + atom0, TC_SF_TILE, &sh->full[slot]);
+                    }
+                    tma_load_2d(st + Cfg::OFF_B, mb, kb * TC_KB_BYTES, u.y, &sh->full[slot]);
+                    bulk_g2s(st + Cfg::OFF_SFB, p.sfb + ((size_t)unit * (p.K / 64) + (size_t)kb * 4) * 512, TC_SF_TILE, &sh->full[slot]);
+                    ++g;
+                }
+            }
+            if (!ok) tc_timeout(p.ws, sh);
+            // end marker
+            const int slot = g % Cfg::STAGES;
+            if (g < (uint32_t)Cfg::STAGES || mbar_wait(&sh->empty[slot], ((g / Cfg::STAGES) - 1) & 1)) {
+                sh->info[slot] = TcStageInfo{-1, 0, 0, 0, 0, 0, 0, 1};
+                mbar_arrive(&sh->full[slot]);
+            } else {
+                tc_timeout(p.ws, sh);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            uint32_t g = 0, it = 0;
+            bool ok = true;
+            while (ok) {
+                const int buf = it & 1;
+                bool first = true;
+                bool end = false;
+                while (true) {
+                    const int slot = g % Cfg::STAGES;
+                    if (!mbar_wait(&sh->full[slot], (g / Cfg::STAGES) & 1)) { ok = false; break; }
+                    tc_fence_after();
+                    const TcStageInfo inf = sh->info[slot];
+                    if (first) {
+                        // accumulator buffer must have been drained by the epilogue two items ago
+                        if (it >= 2 && !mbar_wait(&sh->tmem_empty[buf], ((it >> 1) - 1) & 1)) { ok = false; break; }
+                        tc_fence_after();
+                        first = false;
+                    }
+                    if (inf.expert < 0) {
+                        sh->epi[buf] = inf;
+                        end = true;
+                        break;
+                    }
+                    const uint32_t st = smem_u32(smem + (size_t)slot * Cfg::STAGE_BYTES);
+                    const uint32_t sfcol = tmem + TC_SF_COL0 + (g & 1) * TC_SF_COLS;
+#pragma unroll
+                    for (int a = 0; a < NA; ++a)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            tc_cp_sf(sfcol + a * 16 + j * 4, desc_sf(st + Cfg::OFF_SFA + a * TC_SF_TILE + j * 512));
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        tc_cp_sf(sfcol + 32 + j * 4, desc_sf(st + Cfg::OFF_SFB + j * 512));
+                    const uint32_t idesc = idesc_nvf4(inf.nbox);
+#pragma unroll
+                    for (int a = 0; a < NA; ++a)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            tc_mma(tmem + buf * TC_ACC_STRIDE + a * TC_UNIT_TOK,
+                                   desc_sw128(st + a * TC_A_TILE + j * 32), desc_sw128(st + Cfg::OFF_B + j * 32),
+                                   idesc, sfcol + a * 16 + j * 4, sfcol + 32 + j * 4, (inf.kb > 0 || j > 0) ? 1u : 0u);
+                    tc_commit(&sh->empty[slot]);       // stage (and its scale columns) reusable when these finish
+                    ++g;
+                    if (inf.last) { sh->epi[buf] = inf; break; }
+                }
+                if (!ok) break;
+                tc_commit(&sh->tmem_full[buf]);        // fires when every MMA of the item has finished
+                mbar_arrive(&sh->tmem_full[buf]);      // releases the epi[] record
+                ++it;
+                if (end) break;
+            }
+            if (!ok) {
+                tc_timeout(p.ws, sh);
+                // let the epilogue leave
+                sh->epi[it & 1] = TcStageInfo{-1, 0, 0, 0, 0, 0, 0, 1};
+                tc_commit(&sh->tmem_full[it & 1]);
+                mbar_arrive(&sh->tmem_full[it & 1]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------- epilogue
+        const int quad = warp & 3;                        // TMEM lanes [32*quad, 32*quad + 32)
+        const int row = quad * 32 + lane;                 // row of the 128-row tile
+        uint32_t it = 0;
+        while (true) {
+            const int buf = it & 1;
+            if (!mbar_wait(&sh->tmem_full[buf], (it >> 1) & 1)) { if (lane == 0) tc_timeout(p.ws, sh); break; }
+            tc_fence_after();
+            const TcStageInfo inf = sh->epi[buf];
+            if (inf.expert < 0) break;
+            const bool shd = inf.expert >= p.E;
+            const float alpha = shd ? p.gs_shared[0] : p.gs_routed[inf.expert];
+            const uint32_t tacc = tmem + ((uint32_t)(quad * 32) << 16) + buf * TC_ACC_STRIDE;
+            if (NA == 2) {
+                const int n = inf.tile * TC_ROWS + row;       // intermediate index of this lane
+                for (int c0 = 0; c0 < inf.nbox; c0 += 8) {
+                    uint32_t gr[8], ur[8];
+                    tc_ld8(tacc + c0, gr);
+                    tc_ld8(tacc + TC_UNIT_TOK + c0, ur);
+                    tc_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const int t = c0 + c;
+                        const float gate = __uint_as_float(gr[c]) * alpha, up = __uint_as_float(ur[c]) * alpha;
+                        const float sw = up * silu(gate);
+                        float gm = fabsf(sw);
+#pragma unroll
+                        for (int o = 1; o < 16; o <<= 1) gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, o));
+                        const uint8_t sb = e4m3_encode(fmaxf(gm / 6.0f, 1e-30f));
+                        float sc = e4m3_decode(sb);
+                        if (sc < 1e-30f) sc = 1e-30f;
+                        const uint32_t nib = e2m1_encode(sw / sc);
+                        const uint32_t nb = __shfl_down_sync(0xffffffffu, nib, 1);
+                        if (t < inf.ntok) {
+                            const size_t srow = (size_t)(inf.slot0 + t);
+                            if ((lane & 1) == 0) p.ws.inter_q[srow * (p.N / 2) + (n >> 1)] = (uint8_t)(nib | (nb << 4));
+                            if ((lane & 15) == 0) p.ws.inter_sf[srow * (p.N / 16) + (n >> 4)] = sb;   // linear copy (stage checks)
+                            if ((lane & 15) == 0)   // scale of block n/16 of token row t, in the atom layout of the down GEMM's B operand
+                                p.ws.inter_sf_atoms[((size_t)inf.unit * (p.N / 64) + (n >> 6)) * 512 + (t & 31) * 16 + (t >> 5) * 4 + ((n >> 4) & 3)] = sb;
+                        }
+                    }
+                }
+            } else {
+                const int j = inf.tile * TC_ROWS + row;       // hidden index of this lane
+                for (int c0 = 0; c0 < inf.nbox; c0 += 8) {
+                    uint32_t yr[8];
+                    tc_ld8(tacc + c0, yr);
+                    tc_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        const int t = c0 + c;
+                        if (t < inf.ntok) {
+                            const int srow = inf.slot0 + t;
+                            const float scale = p.ws.scatter_weights[srow] * alpha;
+                            p.ws.pair_out[(size_t)srow * p.hidden + j] = scale * __uint_as_float(yr[c]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->tmem_empty[buf]);
+            ++it;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// bf16 -> NVFP4 quantiser that writes rows in sorted-slot order (every token row goes to the slot
+// of each of its pairs and to its shared-expert slot) and block scales in the 128-row x 4-scale
+// atom layout of the tensor-core B operand, relative to the first slot of the row's work unit.
+// Same arithmetic as quantize_kernel (…tma_ext.cu:249-279).
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+permute_quantize_kernel(const __nv_bfloat16* __restrict__ x, int M, int K, int T, int E, int has_shared,
+                        const int32_t* __restrict__ topk_ids, const int32_t* __restrict__ expert_map, Workspace ws) {
+    const int bpr = K / SF_BLOCK;
+    const long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= (long long)M * bpr) return;
+    const int m = (int)(b / bpr), kb = (int)(b % bpr);
+    const uint4* src = reinterpret_cast<const uint4*>(x + b * SF_BLOCK);
+    uint4 raw[2] = {src[0], src[1]};
+    const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(raw);
+    float v[SF_BLOCK];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < SF_BLOCK; ++i) { v[i] = __bfloat162float(h[i]); amax = fmaxf(amax, fabsf(v[i])); }
+    const uint8_t sb = e4m3_encode(fmaxf(amax / 6.0f, 1e-30f));
+    float scale = e4m3_decode(sb);
+    if (scale < 1e-30f) scale = 1e-30f;
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) lo |= e2m1_encode(v[i] / scale) << (4 * i);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) hi |= e2m1_encode(v[8 + i] / scale) << (4 * i);
+    // token-order copy (stage-wise checks and the GEMV path read it)
+    reinterpret_cast<uint2*>(ws.act_q)[b] = make_uint2(lo, hi);
+    ws.act_sf[b] = sb;
+    for (int j = 0; j <= T; ++j) {
+        int e, slot;
+        if (j < T) {
+            slot = ws.pair_slot[m * T + j];
+            if (slot < 0) continue;
+            e = topk_ids[m * T + j];
+            if (expert_map) e = expert_map[e];
+        } else {
+            if (!has_shared) break;
+            e = E;
+            slot = ws.expert_offsets[E] + m;
+        }
+        const int rank = slot - ws.expert_offsets[e];
+        const int unit = ws.tc_unit_base[e] + rank / TC_UNIT_TOK;
+        const int r = rank % TC_UNIT_TOK;
+        reinterpret_cast<uint2*>(ws.act_q_sorted + (size_t)slot * (K / 2))[kb] = make_uint2(lo, hi);
+        ws.act_sf_atoms[((size_t)unit * (K / 64) + (kb >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = sb;
+    }
+}
+
+// linear block scales [rows, K/16] -> atoms [rows/128][K/64][32][4][4]; NaN patterns become 0x00
+// (they decode to zero: …tma_ext.cu:48-55).  Returns through *bad the number of signed bytes.
+__global__ void __launch_bounds__(256)
+prep_sf_kernel(const uint8_t* __restrict__ sf, long long rows, int K, uint8_t* __restrict__ atoms, int* bad) {
+    const int spr = K / SF_BLOCK;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * spr) return;
+    const long long row = i / spr; const int kb = (int)(i % spr);
+    uint8_t v = sf[i];
+    if ((v & 0x7F) == 0x7F) v = 0;
+    else if (v & 0x80) { atomicAdd(bad, 1); }
+    const int r = (int)(row % TC_ROWS);
+    atoms[((row / TC_ROWS) * (K / 64) + (kb >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = v;
+}
+
+// ---------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------
+static PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+
+static int get_encoder() {
+    if (g_encode) return VMOE_OK;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) return VMOE_ERR_CUDA;
+    g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    return VMOE_OK;
+}
+
+// 2-D byte tensor [rows, row_bytes], box [box_rows, 128 bytes], 128-byte swizzle
+static int make_map(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows) {
+    const cuuint64_t dims[2] = {row_bytes, rows};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {TC_KB_BYTES, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? VMOE_OK : VMOE_ERR_CUDA;
+}
+
+static int tc_sm_count() {
+    static int n = 0;
+    if (n == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev); if (n <= 0) n = 148; }
+    return n;
+}
+
+int launch_permute_quantize(const vmoe_shape& s, const __nv_bfloat16* x, const int32_t* ids, const int32_t* expert_map,
+                            int M, const Workspace& ws, cudaStream_t st) {
+    const long long nblocks = (long long)M * (s.hidden / SF_BLOCK);
+    if (nblocks == 0) return VMOE_OK;
+    permute_quantize_kernel<<<(unsigned)((nblocks + 255) / 256), 256, 0, st>>>(x, M, s.hidden, s.topk, s.num_experts,
+                                                                               s.has_shared, ids, expert_map, ws);
+    return cuda_status(cudaGetLastError());
+}
+
+int launch_prep_sf(const uint8_t* sf, long long rows, int K, uint8_t* atoms, int* bad, cudaStream_t st) {
+    const long long n = rows * (K / SF_BLOCK);
+    if (n == 0) return VMOE_OK;
+    prep_sf_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(sf, rows, K, atoms, bad);
+    return cuda_status(cudaGetLastError());
+}
+
+template <int NA>
+static int launch_tc(const vmoe_shape& s, const WeightSet& routed, const WeightSet& shared, const PreparedSet& prep,
+                     int M, const Workspace& ws, cudaStream_t st) {
+    using Cfg = TcCfg<NA>;
+    int rc = get_encoder();
+    if (rc) return rc;
+    TcParams p;
+    memset(&p, 0, sizeof(p));
+    const int K = (NA == 2) ? s.hidden : s.inter;              // reduction length
+    const int rows = (NA == 2) ? 2 * s.inter : s.hidden;       // weight rows per expert
+    const uint8_t* wr = (NA == 2) ? routed.w13 : routed.w2;
+    const uint8_t* wsx = (NA == 2) ? shared.w13 : shared.w2;
+    if ((rc = make_map(&p.map_a_routed, wr, K / 2, (uint64_t)s.num_experts * rows, TC_ROWS))) return rc;
+    if (s.has_shared) { if ((rc = make_map(&p.map_a_shared, wsx, K / 2, rows, TC_ROWS))) return rc; }
+    else p.map_a_shared = p.map_a_routed;
+    const long long S = (long long)s.max_tokens * s.topk + (s.has_shared ? s.max_tokens : 0);
+    const uint8_t* bsrc = (NA == 2) ? ws.act_q_sorted : ws.inter_q;
+    const int boxes[4] = {8, 16, 32, 64};
+    for (int i = 0; i < 4; ++i)
+        if ((rc = make_map(&p.map_b[i], bsrc, K / 2, (uint64_t)(S > 0 ? S : 1), boxes[i]))) return rc;
+    p.sfa_routed = (NA == 2) ? prep.w13_sf_atoms : prep.w2_sf_atoms;
+    p.sfa_shared = (NA == 2) ? prep.shared_w13_sf_atoms : prep.shared_w2_sf_atoms;
+    p.sfb = (NA == 2) ? ws.act_sf_atoms : ws.inter_sf_atoms;
+    p.gs_routed = (NA == 2) ? routed.w13_gs : routed.w2_gs;
+    p.gs_shared = (NA == 2) ? shared.w13_gs : shared.w2_gs;
+    p.ws = ws; p.K = K; p.rows = rows; p.N = s.inter; p.hidden = s.hidden; p.E = s.num_experts;
+    p.tiles = (NA == 2) ? s.inter / TC_ROWS : s.hidden / TC_ROWS;
+    p.queue = (NA == 2) ? CNT_QUEUE1 : CNT_QUEUE2;
+    const size_t smem = (size_t)Cfg::STAGES * Cfg::STAGE_BYTES + sizeof(TcShared) + 1024;
+    if (cudaFuncSetAttribute(tc_gemm_kernel<NA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return VMOE_ERR_CUDA;
+    const long long units_hint = min((long long)M * s.topk + (s.has_shared ? M : 0), (long long)max_tc_units(&s));
+    long long grid = min((long long)tc_sm_count(), units_hint * p.tiles);
+    if (grid < 1) grid = 1;
+    tc_gemm_kernel<NA><<<(unsigned)grid, TC_THREADS, smem, st>>>(p);
+    return cuda_status(cudaGetLastError());
+}
+
+int launch_tc_gate_up(const vmoe_shape& s, const WeightSet& routed, const WeightSet& shared, const PreparedSet& prep,
+                      int M, const Workspace& ws, cudaStream_t st) {
+    if (M == 0) return VMOE_OK;
+    return launch_tc<2>(s, routed, shared, prep, M, ws, st);
+}
+int launch_tc_down(const vmoe_shape& s, const WeightSet& routed, const WeightSet& shared, const PreparedSet& prep,
+                   int M, const Workspace& ws, cudaStream_t st) {
+    if (M == 0) return VMOE_OK;
+    return launch_tc<1>(s, routed, shared, prep, M, ws, st);
+}
+
+}  // namespace vmoe

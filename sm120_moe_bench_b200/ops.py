@@ -40,10 +40,11 @@ class MoEShape:
     max_tokens: int
     has_shared: bool = False
     num_global_experts: int | None = None
+    path: int = 0             # 0 automatic, 1 streaming GEMV (CUDA cores), 2 tcgen05 tensor cores
 
     def cstruct(self) -> VmoeShape:
         return VmoeShape(self.hidden, self.inter, self.num_experts, self.topk, self.max_tokens,
-                         int(self.has_shared), self.num_global_experts or self.num_experts, 0)
+                         int(self.has_shared), self.num_global_experts or self.num_experts, self.path)
 
 
 class MoEWeights:
@@ -64,8 +65,30 @@ class MoEWeights:
         if self.w13_sf.shape != (E, N2, Kh // 8) or self.w2.shape != (E, Kh * 2, N2 // 4) \
                 or self.w2_sf.shape != (E, Kh * 2, N2 // 32) or self.w13_gs.numel() != E or self.w2_gs.numel() != E:
             raise ValueError("inconsistent NVFP4 weight shapes")
+        self.w13_sf_atoms = None
+        self.w2_sf_atoms = None
         self._c = VmoeWeights(self.w13.data_ptr(), self.w13_sf.data_ptr(), self.w13_gs.data_ptr(),
-                              self.w2.data_ptr(), self.w2_sf.data_ptr(), self.w2_gs.data_ptr())
+                              self.w2.data_ptr(), self.w2_sf.data_ptr(), self.w2_gs.data_ptr(), None, None)
+
+    def prepare(self) -> "MoEWeights":
+        """One-time re-layout of the block scales for the tensor-core path (``vmoe_prepare_sf``);
+        raises if a scale byte has its sign bit set.  Needs 2N and K to be multiples of 128."""
+        if self.w13_sf_atoms is not None:
+            return self
+        bad = torch.zeros(1, dtype=torch.int32, device=self.w13.device)
+        outs = []
+        for sf in (self.w13_sf, self.w2_sf):
+            E, R, C16 = sf.shape
+            atoms = torch.empty(sf.numel(), dtype=torch.uint8, device=sf.device)
+            check(lib.vmoe_prepare_sf(sf.data_ptr(), E * R, C16 * 16, atoms.data_ptr(), bad.data_ptr(), _stream()),
+                  "vmoe_prepare_sf")
+            outs.append(atoms)
+        if int(bad.item()) != 0:
+            raise ValueError(f"{int(bad.item())} block-scale bytes have the sign bit set; NVFP4 scales are unsigned")
+        self.w13_sf_atoms, self.w2_sf_atoms = outs
+        self._c.w13_sf_atoms = self.w13_sf_atoms.data_ptr()
+        self._c.w2_sf_atoms = self.w2_sf_atoms.data_ptr()
+        return self
 
     num_experts = property(lambda self: self.w13.shape[0])
     hidden = property(lambda self: self.w13.shape[2] * 2)
@@ -114,6 +137,8 @@ class Workspace:
             scatter_weights=self.view("scatter_weights", torch.float32, slots).cpu(),
             num_units=int(cnt[0]), num_slots=slots,
             units=self.view("units", torch.int32, int(cnt[0]) * 4).cpu().view(-1, 4),
+            num_tc_units=int(cnt[5]),
+            tc_units=self.view("tc_units", torch.int32, int(cnt[5]) * 4).cpu().view(-1, 4),
         )
 
 

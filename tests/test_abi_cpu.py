@@ -19,12 +19,12 @@ def test_library_exports_every_declared_symbol():
     __graft_entry__.build()
     lib = ctypes.CDLL(os.path.join(ROOT, "sm120_moe_bench_b200", "libvmoe.so"))
     names = _declared()
-    assert len(names) >= 13
+    assert len(names) >= 15
     for n in names:
         assert hasattr(lib, n), n
     from sm120_moe_bench_b200 import _lib
     assert sorted(_lib.SIGNATURES) == names
-    assert _lib.lib.vmoe_abi_version() == 1
+    assert _lib.lib.vmoe_abi_version() == 2
     assert _lib.lib.vmoe_status_string(6) == b"a bounded device-side wait ran out"
 
 

@@ -17,17 +17,25 @@ def vm():
     return pkg
 
 
-def _device_layer(vm, layer):
+GEMV, TC = 1, 2      # vmoe_path values: streaming GEMV on CUDA cores / tcgen05 tensor cores
+PATHS = [pytest.param(GEMV, id="gemv"), pytest.param(TC, id="tc")]
+
+
+def _device_layer(vm, layer, prepare=True):
     from sm120_moe_bench_b200 import ops
     routed = ops.MoEWeights(*[t.cuda() for t in layer["routed"]])
     shared = ops.MoEWeights(*[t.cuda() for t in layer["shared"]]) if layer["shared"] is not None else None
+    if prepare:
+        routed.prepare()
+        if shared is not None:
+            shared.prepare()
     return routed, shared
 
 
-def _run_and_check(vm, cfg, layer, hidden, logits, M, expert_subset=True, use_logits=True):
+def _run_and_check(vm, cfg, layer, hidden, logits, M, expert_subset=True, use_logits=True, path=GEMV):
     from sm120_moe_bench_b200 import ops
     routed, shared = _device_layer(vm, layer)
-    shape = vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, M, has_shared=cfg.shared)
+    shape = vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, M, has_shared=cfg.shared, path=path)
     ws = vm.Workspace(shape)
     hid_d, log_d = hidden.cuda(), logits.cuda()
     ids_ref, w_ref = omoe.route(logits.cpu().numpy(), cfg.topk)
@@ -98,23 +106,46 @@ def _run_and_check(vm, cfg, layer, hidden, logits, M, expert_subset=True, use_lo
     return util.assert_output_close(got, ref), float(flips)
 
 
-def test_config_tiny(vm):
+@pytest.mark.parametrize("path", PATHS)
+def test_config_tiny(vm, path):
     """BASELINE config 1: hidden 1024, 8 experts, top-2, intermediate 512, 4 tokens, seed 0."""
     from sm120_moe_bench_b200 import synth
     cfg = synth.CONFIG_TINY
     layer = synth.make_layer(cfg, seed=0)
     hidden, logits = synth.make_inputs(cfg, 4, seed=0)
-    _run_and_check(vm, cfg, layer, hidden, logits, 4, expert_subset=False, use_logits=True)
-    _run_and_check(vm, cfg, layer, hidden, logits, 4, expert_subset=False, use_logits=False)
+    _run_and_check(vm, cfg, layer, hidden, logits, 4, expert_subset=False, use_logits=True, path=path)
+    _run_and_check(vm, cfg, layer, hidden, logits, 4, expert_subset=False, use_logits=False, path=path)
 
 
-@pytest.mark.parametrize("M", [1, 3, 16, 50])
-def test_small_shapes_with_shared(vm, M):
+@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("M", [1, 3, 16, 50, 150])
+def test_small_shapes_with_shared(vm, M, path):
     from sm120_moe_bench_b200 import synth
     cfg = synth.LayerConfig("mid", 512, 256, 12, 3, True)
     layer = synth.make_layer(cfg, seed=3)
     hidden, logits = synth.make_inputs(cfg, M, seed=M)
-    _run_and_check(vm, cfg, layer, hidden, logits, M, expert_subset=False)
+    _run_and_check(vm, cfg, layer, hidden, logits, M, expert_subset=False, path=path)
+
+
+def test_prepared_scale_layout(vm):
+    """vmoe_prepare_sf: linear [rows, K/16] -> [rows/128][K/64][32][4][4] atoms, NaN bytes -> 0."""
+    from sm120_moe_bench_b200._lib import lib
+    g = torch.Generator().manual_seed(11)
+    rows, K = 256, 512
+    sf = torch.randint(0, 0x7F, (rows, K // 16), dtype=torch.uint8, generator=g)
+    sf[3, 5] = 0x7F
+    atoms = torch.full((rows * K // 16,), 0xEE, dtype=torch.uint8, device="cuda")
+    bad = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert lib.vmoe_prepare_sf(sf.cuda().data_ptr(), rows, K, atoms.data_ptr(), bad.data_ptr(), None) == 0
+    torch.cuda.synchronize()
+    ref = sf.clone(); ref[3, 5] = 0
+    # [rows/128][r/32 (4)][r%32 (32)][K/64][kb%4] -> [rows/128][K/64][r%32][r/32][kb%4]
+    ref = ref.view(rows // 128, 4, 32, K // 64, 4).permute(0, 3, 2, 1, 4).contiguous().view(-1)
+    assert torch.equal(atoms.cpu(), ref) and int(bad.item()) == 0
+    sf[0, 0] = 0x85
+    assert lib.vmoe_prepare_sf(sf.cuda().data_ptr(), rows, K, atoms.data_ptr(), bad.data_ptr(), None) == 0
+    torch.cuda.synchronize()
+    assert int(bad.item()) == 1
 
 
 @pytest.fixture(scope="module")
@@ -123,17 +154,19 @@ def large_layer():
     return synth.make_layer(synth.CONFIG_LARGE, seed=0, device="cuda")
 
 
+@pytest.mark.parametrize("path", PATHS)
 @pytest.mark.parametrize("M", [1, 4])
-def test_config_large_decode(vm, large_layer, M):
+def test_config_large_decode(vm, large_layer, M, path):
     """BASELINE config 2 (hidden 4096, 512 experts top-10 + shared, intermediate 1024) at the batch
     sizes the oracle finishes in seconds; only the experts the batch touches are copied back."""
     from sm120_moe_bench_b200 import synth
     cfg = synth.CONFIG_LARGE
     hidden, logits = synth.make_inputs(cfg, M, seed=M)
-    _run_and_check(vm, cfg, large_layer, hidden, logits, M, expert_subset=True)
+    _run_and_check(vm, cfg, large_layer, hidden, logits, M, expert_subset=True, path=path)
 
 
-def test_config_large_bs64_properties(vm, large_layer):
+@pytest.mark.parametrize("path", PATHS)
+def test_config_large_bs64_properties(vm, large_layer, path):
     """Batch 64 at full size, checked through size-independent properties: (1) a token's output does
     not depend on which other tokens share the batch (rows of the bs-64 run equal bs-1 runs bit for
     bit, as each token only uses its own top-k: fused-moe/test_expert_union.py:228-405), (2) run-twice
@@ -143,7 +176,7 @@ def test_config_large_bs64_properties(vm, large_layer):
     routed, shared = _device_layer(vm, large_layer)
     hidden, logits = synth.make_inputs(cfg, 64, seed=64)
     hid_d, log_d = hidden.cuda(), logits.cuda()
-    ws = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, 64, has_shared=True))
+    ws = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, 64, has_shared=True, path=path))
     out1 = vm.fused_moe(hid_d, routed, ws, router_logits=log_d, shared=shared).clone()
     out2 = vm.fused_moe(hid_d, routed, ws, router_logits=log_d, shared=shared)
     torch.cuda.synchronize()
