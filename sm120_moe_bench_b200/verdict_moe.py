@@ -75,6 +75,8 @@ class _VerdictCommon:
     #            hands g_alphas = a_scale * w_scale_2 and a_gscale = 1 / a_scale);
     # "weight":  alpha = g_alphas (frameworks that hand the raw weight global scale).
     alpha_convention = os.environ.get("VMOE_ALPHA_CONVENTION", "product")
+    # 0 = automatic (tensor cores when the shape allows), 1 = CUDA-core streaming GEMV, 2 = tcgen05
+    kernel_path = int(os.environ.get("VMOE_KERNEL_PATH", "0"))
 
     @property
     def expects_unquantized_inputs(self) -> bool:
@@ -141,7 +143,7 @@ class _VerdictCommon:
         """Allocate the workspace once (fused-moe/verdict_moe.py:243-414).  Later calls only reuse it."""
         shape = ops.MoEShape(K, N_half, num_experts, max_topk, max_tokens,
                              has_shared=self._shared is not None,
-                             num_global_experts=num_global_experts or num_experts)
+                             num_global_experts=num_global_experts or num_experts, path=self.kernel_path)
         self._ws = ops.Workspace(shape, device)
         self._buffers_ready = True
 
@@ -158,6 +160,10 @@ class _VerdictCommon:
         if self._weights_key != key:
             a1, a2 = self._alphas()
             self._weights = ops.MoEWeights(w1, self.w1_scale, a1, w2, self.w2_scale, a2)
+            if self.kernel_path != 1 and self._weights.hidden % 256 == 0 and self._weights.inter % 256 == 0:
+                self._weights.prepare()      # one-time scale re-layout, as process_weights_after_loading would do
+                if self._shared is not None:
+                    self._shared.prepare()
             self._weights_key = key
         return self._weights
 
