@@ -13,6 +13,9 @@
 // them in fp32 and reduce across lanes with shuffles.
 #include "vmoe_common.cuh"
 
+#include <mutex>
+#include <vector>
+
 namespace vmoe {
 
 constexpr int CONSUMER_WARPS = 4;
@@ -392,11 +395,24 @@ static void fill(GemvParams& p, const vmoe_shape& s, const WeightSet& r, const W
 
 template <typename Kern>
 static int launch_persistent(Kern kern, const GemvParams& p, size_t smem, int M, int units_hint, cudaStream_t st) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return VMOE_ERR_CUDA;
-    int per_sm = 1;
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, GEMV_THREADS, smem);
-    if (per_sm < 1) per_sm = 1;
+    // attribute + occupancy are looked up once per (kernel, device, smem size)
+    struct Cached { const void* kern; int dev; size_t smem; int per_sm; };
+    static std::mutex mu;
+    static std::vector<Cached> cache;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int per_sm = 0;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        for (const Cached& c : cache)
+            if (c.kern == (const void*)kern && c.dev == dev && c.smem == smem) per_sm = c.per_sm;
+        if (per_sm == 0) {
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return VMOE_ERR_CUDA;
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, GEMV_THREADS, smem);
+            if (per_sm < 1) per_sm = 1;
+            cache.push_back(Cached{(const void*)kern, dev, smem, per_sm});
+        }
+    }
     long long want = (long long)units_hint * p.tiles;          // upper bound on items
     long long grid = (long long)sm_count() * per_sm;
     if (want < grid) grid = want;

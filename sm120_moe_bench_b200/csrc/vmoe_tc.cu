@@ -18,6 +18,9 @@
 
 #include <string.h>
 
+#include <mutex>
+#include <vector>
+
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
@@ -109,6 +112,15 @@ __device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
     // no swizzle: 32 rows of 16 bytes, 8-row groups 128 bytes apart
     return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
 }
+// the same descriptors as (low word = start address >> 4 | LBO << 16, constant high word)
+constexpr uint32_t DESC_SW128_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+constexpr uint32_t DESC_SF_HI = (128u >> 4) | (1u << 14);
+constexpr uint32_t DESC_SW128_LBO = 1u << 16;
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr16, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(addr16), "r"(hi));
+    return d;
+}
 __device__ __forceinline__ uint32_t idesc_nvf4(int n) {
     // a/b format E2M1 (1), K-major both, N >> 3, scale format UE4M3 (0), M = 128 (>> 4), K = 64
     return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24);
@@ -156,12 +168,18 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
             const int kblocks = p.K / 256;
             uint32_t g = 0;
             bool ok = true;
+            // The queue pop and the unit record of the NEXT item are requested before the loads of
+            // the current one are issued, so their L2 round trips never stall the stream.
+            long long next = atomicAdd(&p.ws.counters[p.queue], 1);
+            int4 next_u = (next < total) ? p.ws.tc_units[next / p.tiles] : make_int4(0, 0, 0, 8);
             while (ok) {
-                const long long item = atomicAdd(&p.ws.counters[p.queue], 1);
+                const long long item = next;
                 if (item >= total) break;
                 // unit-major order: consecutive items are the row tiles of one unit
                 const int unit = (int)(item / p.tiles), tile = (int)(item % p.tiles);
-                const int4 u = p.ws.tc_units[unit];
+                const int4 u = next_u;
+                next = atomicAdd(&p.ws.counters[p.queue], 1);
+                next_u = (next < total) ? p.ws.tc_units[next / p.tiles] : make_int4(0, 0, 0, 8);
                 const bool shd = u.x >= p.E;
                 const int e = shd ? 0 : u.x;
                 const CUtensorMap* ma = shd ? &p.map_a_shared : &p.map_a_routed;
@@ -203,7 +221,8 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
     } else if (warp == 1) {
         // ------------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            uint32_t g = 0, it = 0;
+            uint32_t g = 0, it = 0, idesc = 0;
+            const uint32_t smem16 = smem_u32(smem) >> 4;
             bool ok = true;
             while (ok) {
                 const int buf = it & 1;
@@ -225,23 +244,27 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                         end = true;
                         break;
                     }
-                    const uint32_t st = smem_u32(smem + (size_t)slot * Cfg::STAGE_BYTES);
+                    // descriptors: only the 14-bit start-address field (bytes >> 4) differs between
+                    // tiles, so each one is a single add on a per-stage base
+                    const uint32_t st16 = smem16 + slot * (Cfg::STAGE_BYTES >> 4);
                     const uint32_t sfcol = tmem + TC_SF_COL0 + (g & 1) * TC_SF_COLS;
 #pragma unroll
                     for (int a = 0; a < NA; ++a)
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
-                            tc_cp_sf(sfcol + a * 16 + j * 4, desc_sf(st + Cfg::OFF_SFA + a * TC_SF_TILE + j * 512));
+                            tc_cp_sf(sfcol + a * 16 + j * 4, make_desc(st16 + ((Cfg::OFF_SFA + a * TC_SF_TILE + j * 512) >> 4), DESC_SF_HI));
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
-                        tc_cp_sf(sfcol + 32 + j * 4, desc_sf(st + Cfg::OFF_SFB + j * 512));
-                    const uint32_t idesc = idesc_nvf4(inf.nbox);
+                        tc_cp_sf(sfcol + 32 + j * 4, make_desc(st16 + ((Cfg::OFF_SFB + j * 512) >> 4), DESC_SF_HI));
+                    if (inf.kb == 0) idesc = idesc_nvf4(inf.nbox);
+                    const uint32_t dcol = tmem + buf * TC_ACC_STRIDE;
 #pragma unroll
                     for (int a = 0; a < NA; ++a)
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
-                            tc_mma(tmem + buf * TC_ACC_STRIDE + a * TC_UNIT_TOK,
-                                   desc_sw128(st + a * TC_A_TILE + j * 32), desc_sw128(st + Cfg::OFF_B + j * 32),
+                            tc_mma(dcol + a * TC_UNIT_TOK,
+                                   make_desc(st16 + ((a * TC_A_TILE + j * 32) >> 4) + DESC_SW128_LBO, DESC_SW128_HI),
+                                   make_desc(st16 + ((Cfg::OFF_B + j * 32) >> 4) + DESC_SW128_LBO, DESC_SW128_HI),
                                    idesc, sfcol + a * 16 + j * 4, sfcol + 32 + j * 4, (inf.kb > 0 || j > 0) ? 1u : 0u);
                     tc_commit(&sh->empty[slot]);       // stage (and its scale columns) reusable when these finish
                     ++g;
@@ -415,8 +438,23 @@ static int get_encoder() {
     return VMOE_OK;
 }
 
-// 2-D byte tensor [rows, row_bytes], box [box_rows, 128 bytes], 128-byte swizzle
+// 2-D byte tensor [rows, row_bytes], box [box_rows, 128 bytes], 128-byte swizzle.  Encoded maps are
+// kept in a small cache keyed by (device, base, shape): a forward call re-uses them instead of
+// paying a driver call per map per launch.
+struct MapKey { int dev; const void* base; uint64_t row_bytes, rows; uint32_t box_rows; };
+struct MapEntry { MapKey key; CUtensorMap map; };
+static std::mutex g_map_mutex;
+static std::vector<MapEntry> g_map_cache;
+
 static int make_map(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    for (const MapEntry& e : g_map_cache)
+        if (e.key.dev == dev && e.key.base == base && e.key.row_bytes == row_bytes && e.key.rows == rows && e.key.box_rows == box_rows) {
+            *map = e.map;
+            return VMOE_OK;
+        }
     const cuuint64_t dims[2] = {row_bytes, rows};
     const cuuint64_t strides[1] = {row_bytes};
     const cuuint32_t box[2] = {TC_KB_BYTES, box_rows};
@@ -424,7 +462,10 @@ static int make_map(CUtensorMap* map, const void* base, uint64_t row_bytes, uint
     const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? VMOE_OK : VMOE_ERR_CUDA;
+    if (r != CUDA_SUCCESS) return VMOE_ERR_CUDA;
+    if (g_map_cache.size() >= 256) g_map_cache.erase(g_map_cache.begin());
+    g_map_cache.push_back(MapEntry{MapKey{dev, base, row_bytes, rows, box_rows}, *map});
+    return VMOE_OK;
 }
 
 static int tc_sm_count() {
@@ -478,8 +519,14 @@ static int launch_tc(const vmoe_shape& s, const WeightSet& routed, const WeightS
     p.tiles = (NA == 2) ? s.inter / TC_ROWS : s.hidden / TC_ROWS;
     p.queue = (NA == 2) ? CNT_QUEUE1 : CNT_QUEUE2;
     const size_t smem = (size_t)Cfg::STAGES * Cfg::STAGE_BYTES + sizeof(TcShared) + 1024;
-    if (cudaFuncSetAttribute(tc_gemm_kernel<NA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-        return VMOE_ERR_CUDA;
+    static bool attr_set[64] = {false};       // per device, per instantiation
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+        if (cudaFuncSetAttribute(tc_gemm_kernel<NA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return VMOE_ERR_CUDA;
+        if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
     const long long units_hint = min((long long)M * s.topk + (s.has_shared ? M : 0), (long long)max_tc_units(&s));
     long long grid = min((long long)tc_sm_count(), units_hint * p.tiles);
     if (grid < 1) grid = 1;
