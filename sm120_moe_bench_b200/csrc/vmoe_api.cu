@@ -13,9 +13,19 @@ int max_units(const vmoe_shape* s) {
     return (int)(s->num_experts + 1 + (P + TOK_PER_UNIT - 1) / TOK_PER_UNIT);
 }
 
+// Units carry at most 16 tokens while the batch averages <= 4 tokens per expert (memory-bound:
+// a small token tile leaves shared memory for a deeper weight ring), else 64.
+int tc_unit_cap(const vmoe_shape& s, int M) {
+    return ((long long)M * s.topk <= 4LL * s.num_experts) ? TC_UNIT_TOK_SMALL : TC_UNIT_TOK;
+}
+
 int max_tc_units(const vmoe_shape* s) {
-    const long long P = (long long)s->max_tokens * s->topk + (s->has_shared ? s->max_tokens : 0);
-    return (int)(s->num_experts + 1 + (P + TC_UNIT_TOK - 1) / TC_UNIT_TOK);
+    const long long S = (long long)s->max_tokens * s->topk + (s->has_shared ? s->max_tokens : 0);
+    // small-unit regime only exists up to M*T = 4E pairs (+ their shared rows)
+    long long small_slots = 4LL * s->num_experts + (s->has_shared ? 4LL * s->num_experts / s->topk + 1 : 0);
+    if (small_slots > S) small_slots = S;
+    const long long a = (S + TC_UNIT_TOK - 1) / TC_UNIT_TOK, b = (small_slots + TC_UNIT_TOK_SMALL - 1) / TC_UNIT_TOK_SMALL;
+    return (int)(s->num_experts + 2 + (a > b ? a : b));
 }
 
 static int check_shape(const vmoe_shape* s) {
@@ -195,7 +205,8 @@ int vmoe_build_tables(const vmoe_shape* shape, const int32_t* topk_ids, const fl
     if (workspace_bytes < vmoe_workspace_bytes(shape)) return VMOE_ERR_WORKSPACE;
     Workspace ws;
     if ((rc = resolve_workspace(shape, workspace, &ws))) return rc;
-    return launch_tables(*shape, topk_ids, topk_weights, expert_map, M, ws, static_cast<cudaStream_t>(stream));
+    return launch_tables(*shape, topk_ids, topk_weights, expert_map, M, ws, static_cast<cudaStream_t>(stream),
+                         tc_unit_cap(*shape, M));
 }
 
 int vmoe_quantize(const void* x_bf16, int32_t rows, int32_t K, uint8_t* packed, uint8_t* sf, void* stream) {
@@ -283,7 +294,7 @@ int vmoe_forward(const vmoe_shape* shape, const vmoe_weights* routed, const vmoe
     }
     int path;
     if ((rc = pick_path(shape, routed, shared, &path))) return rc;
-    if ((rc = launch_tables(*shape, topk_ids, topk_weights, expert_map, M, ws, st))) return rc;
+    if ((rc = launch_tables(*shape, topk_ids, topk_weights, expert_map, M, ws, st, tc_unit_cap(*shape, M)))) return rc;
     if (path == VMOE_PATH_TC) {
         const PreparedSet prep = to_prep(routed, shape->has_shared ? shared : nullptr);
         if ((rc = launch_permute_quantize(*shape, static_cast<const __nv_bfloat16*>(hidden_bf16), topk_ids,

@@ -83,6 +83,7 @@ int launch_route(const float* logits, int M, int E, int T, int32_t* ids, float* 
 struct TableArgs {
     const int32_t* ids; const float* w; const int32_t* expert_map;
     int M, T, E, has_shared, words;   // words = ceil(M / 32)
+    int tc_cap;                       // tokens per tensor-core unit
     Workspace ws;
 };
 
@@ -131,7 +132,7 @@ __device__ void phase_scan(const TableArgs& a, int tid, int nthr, const int32_t*
         const int e = tid * per + k;
         if (e < n) {
             const int c = (e < a.E) ? s_count[e] : a.M;
-            csum += c; usum += (c + TOK_PER_UNIT - 1) / TOK_PER_UNIT; tsum += (c + TC_UNIT_TOK - 1) / TC_UNIT_TOK;
+            csum += c; usum += (c + TOK_PER_UNIT - 1) / TOK_PER_UNIT; tsum += (c + a.tc_cap - 1) / a.tc_cap;
         }
     }
     s_scan[tid] = csum; s_scan[nthr + tid] = usum; s_scan[2 * nthr + tid] = tsum;
@@ -167,8 +168,8 @@ __device__ void phase_scan(const TableArgs& a, int tid, int nthr, const int32_t*
                 a.ws.units[u++] = make_int4(e, c + s, min(TOK_PER_UNIT, cnt - s), 0);
             if (a.ws.tc_units) {
                 a.ws.tc_unit_base[e] = t;
-                for (int s = 0; s < cnt; s += TC_UNIT_TOK) {
-                    const int nt = min(TC_UNIT_TOK, cnt - s);
+                for (int s = 0; s < cnt; s += a.tc_cap) {
+                    const int nt = min(a.tc_cap, cnt - s);
                     a.ws.tc_units[t++] = make_int4(e, c + s, nt, tc_box(nt));
                 }
             }
@@ -226,8 +227,9 @@ __global__ void __launch_bounds__(TABLE_THREADS) tables_scan_kernel(TableArgs a)
 __global__ void tables_place_kernel(TableArgs a) { phase_place(a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x); }
 
 int launch_tables(const vmoe_shape& s, const int32_t* ids, const float* w, const int32_t* expert_map,
-                  int M, const Workspace& ws, cudaStream_t st) {
+                  int M, const Workspace& ws, cudaStream_t st, int tc_cap) {
     TableArgs a;
+    a.tc_cap = tc_cap;
     a.ids = ids; a.w = w; a.expert_map = expert_map;
     a.M = M; a.T = s.topk; a.E = s.num_experts; a.has_shared = s.has_shared; a.words = (M + 31) / 32;
     a.ws = ws;
@@ -325,6 +327,7 @@ extern "C" int vmoe_permute_noalloc(const int32_t* topk_ids, const float* topk_w
     TableArgs a;
     a.ids = topk_ids; a.w = topk_weights; a.expert_map = expert_map;
     a.M = M; a.T = T; a.E = E; a.has_shared = has_shared ? 1 : 0; a.words = (M + 31) / 32;
+    a.tc_cap = TC_UNIT_TOK;
     a.ws = Workspace{};
     a.ws.expert_offsets = expert_offsets; a.ws.sorted_pair = sorted_pair; a.ws.pair_slot = pair_slot;
     a.ws.gather_idx = gather_idx; a.ws.scatter_weights = scatter_weights;

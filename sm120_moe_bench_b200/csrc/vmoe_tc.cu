@@ -30,28 +30,36 @@ constexpr int TC_THREADS = 192;
 constexpr int TC_ROWS = 128;                 // weight rows per tile (UMMA M)
 constexpr int TC_KB_BYTES = 128;             // bytes of K per row per stage = 256 E2M1 elements
 constexpr int TC_A_TILE = TC_ROWS * TC_KB_BYTES;            // 16 KiB
-constexpr int TC_B_TILE = TC_UNIT_TOK * TC_KB_BYTES;        // 8 KiB
 constexpr int TC_SF_TILE = 4 * 512;                         // four 128-row x 4-scale atoms
 constexpr int TC_TMEM_COLS = 512;
-constexpr int TC_ACC_STRIDE = 128;           // TMEM columns per accumulator buffer (gate | up)
 constexpr int TC_SF_COL0 = 256;              // first TMEM column of the scale-factor area
-constexpr int TC_SF_COLS = 48;               // per parity: 16 (A0) + 16 (A1) + 16 (B)
 
-template <int NA> struct TcCfg {
-    static constexpr int STAGE_BYTES = NA * TC_A_TILE + TC_B_TILE + NA * TC_SF_TILE + TC_SF_TILE;
-    static constexpr int STAGES = (NA == 2) ? 4 : 6;
-    static constexpr int OFF_B = NA * TC_A_TILE;
-    static constexpr int OFF_SFA = OFF_B + TC_B_TILE;
-    static constexpr int OFF_SFB = OFF_SFA + NA * TC_SF_TILE;
+constexpr int TC_SMEM_BUDGET = 227 * 1024 - 3 * 1024;     // dynamic shared memory minus control block and alignment slack
+
+// NA = weight matrices per item (2: gate + up, 1: down); KS = 128-byte k-blocks per stage; UT = tokens
+// per unit (UMMA N <= UT).  A stage holds NA*KS weight tiles, KS token tiles and their scale atoms.
+template <int NA, int KS, int UT> struct TcCfg {
+    static constexpr int NT = NA * KS;
+    static constexpr int B_TILE = UT * TC_KB_BYTES;
+    static constexpr int STAGE_BYTES = NT * (TC_A_TILE + TC_SF_TILE) + KS * (B_TILE + TC_SF_TILE);
+    static constexpr int STAGES = (TC_SMEM_BUDGET / STAGE_BYTES) > 12 ? 12 : (TC_SMEM_BUDGET / STAGE_BYTES);
+    static constexpr int OFF_B = NT * TC_A_TILE;                 // [KS][UT x 128]
+    static constexpr int OFF_SFA = OFF_B + KS * B_TILE;           // [NA][KS][4 atoms]
+    static constexpr int OFF_SFB = OFF_SFA + NT * TC_SF_TILE;     // [KS][4 atoms]
+    static constexpr int SF_COLS = (NT + KS) * 16;                // TMEM columns of one stage's scales
+    // accumulator buffers in TMEM: short items (down) run further ahead of their epilogue
+    static constexpr int ACC_STRIDE = NA * UT;
+    static constexpr int NBUF = (256 / ACC_STRIDE) > 4 ? 4 : (256 / ACC_STRIDE);
+    static_assert(TC_SF_COL0 + 2 * SF_COLS <= TC_TMEM_COLS, "scale columns do not fit");
 };
 
-struct TcStageInfo { int expert, slot0, ntok, nbox, tile, unit, kb, last; };
+struct TcStageInfo { int expert, slot0, ntok, nbox, tile, unit, kb, last; };   // kb = step index within the item
 
 struct TcShared {
-    uint64_t full[8], empty[8];
-    uint64_t tmem_full[2], tmem_empty[2];
-    TcStageInfo info[8];
-    TcStageInfo epi[2];
+    uint64_t full[12], empty[12];
+    uint64_t tmem_full[4], tmem_empty[4];
+    TcStageInfo info[12];
+    TcStageInfo epi[4];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -135,10 +143,10 @@ __device__ __forceinline__ void tc_timeout(const Workspace& ws, TcShared* sh) {
 // The kernel.  NA = 2: gate_up (A0 = gate rows, A1 = up rows of the same 128-n tile);
 //              NA = 1: down.
 // ---------------------------------------------------------------------------------
-template <int NA>
+template <int NA, int KS, int UT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ TcParams p) {
-    using Cfg = TcCfg<NA>;
+    using Cfg = TcCfg<NA, KS, UT>;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     TcShared* sh = reinterpret_cast<TcShared*>(smem + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES);
@@ -146,7 +154,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
 
     if (tid == 0) {
         for (int i = 0; i < Cfg::STAGES; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(&sh->tmem_full[i], 2); mbar_init(&sh->tmem_empty[i], 4); }
+        for (int i = 0; i < Cfg::NBUF; ++i) { mbar_init(&sh->tmem_full[i], 2); mbar_init(&sh->tmem_empty[i], 4); }
         sh->abort_flag = 0;
         mbar_fence_init();
     }
@@ -186,25 +194,32 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                 const uint8_t* sfa = shd ? p.sfa_shared : p.sfa_routed;
                 const int nbox = u.w;
                 const CUtensorMap* mb = &p.map_b[nbox == 8 ? 0 : nbox == 16 ? 1 : nbox == 32 ? 2 : 3];
-                for (int kb = 0; kb < kblocks; ++kb) {
+                const int steps = kblocks / KS;
+                for (int ks = 0; ks < steps; ++ks) {
                     const int slot = g % Cfg::STAGES;
                     if (g >= (uint32_t)Cfg::STAGES && !mbar_wait(&sh->empty[slot], ((g / Cfg::STAGES) - 1) & 1)) { ok = false; break; }
                     if (sh->abort_flag) { ok = false; break; }
                     uint8_t* st = smem + (size_t)slot * Cfg::STAGE_BYTES;
-                    sh->info[slot] = TcStageInfo{u.x, u.y, u.z, nbox, tile, unit, kb, kb == kblocks - 1};
-                    const uint32_t bytes = NA * (TC_A_TILE + TC_SF_TILE) + nbox * TC_KB_BYTES + TC_SF_TILE;
+                    sh->info[slot] = TcStageInfo{u.x, u.y, u.z, nbox, tile, unit, ks, ks == steps - 1};
+                    const uint32_t bytes = Cfg::NT * (TC_A_TILE + TC_SF_TILE) + KS * (nbox * TC_KB_BYTES + TC_SF_TILE);
                     mbar_arrive_expect_tx(&sh->full[slot], bytes);
+                    const int kb0 = ks * KS;                       // first k-block of this stage
 #pragma unroll
                     for (int a = 0; a < NA; ++a) {
                         // gate_up: A0 = rows [tile*128, +128) of the gate half, A1 = same rows of the up half
                         const int row_in_expert = (NA == 2 ? a * p.N : 0) + tile * TC_ROWS;
                         const long long row = (long long)e * p.rows + row_in_expert;
-                        tma_load_2d(st + a * TC_A_TILE, ma, kb * TC_KB_BYTES, (int)row, &sh->full[slot]);
-                        const size_t atom0 = ((size_t)(row / TC_ROWS) * (p.K / 64) + (size_t)kb * 4) * 512;
-                        bulk_g2s(st + Cfg::OFF_SFA + a * TC_SF_TILE, sfa + atom0, TC_SF_TILE, &sh->full[slot]);
+#pragma unroll
+                        for (int kk = 0; kk < KS; ++kk)
+                            tma_load_2d(st + (a * KS + kk) * TC_A_TILE, ma, (kb0 + kk) * TC_KB_BYTES, (int)row, &sh->full[slot]);
+                        // the atoms of consecutive k-blocks of one row tile are contiguous
+                        const size_t atom0 = ((size_t)(row / TC_ROWS) * (p.K / 64) + (size_t)kb0 * 4) * 512;
+                        bulk_g2s(st + Cfg::OFF_SFA + a * KS * TC_SF_TILE, sfa + atom0, KS * TC_SF_TILE, &sh->full[slot]);
                     }
-                    tma_load_2d(st + Cfg::OFF_B, mb, kb * TC_KB_BYTES, u.y, &sh->full[slot]);
-                    bulk_g2s(st + Cfg::OFF_SFB, p.sfb + ((size_t)unit * (p.K / 64) + (size_t)kb * 4) * 512, TC_SF_TILE, &sh->full[slot]);
+#pragma unroll
+                    for (int kk = 0; kk < KS; ++kk)
+                        tma_load_2d(st + Cfg::OFF_B + kk * Cfg::B_TILE, mb, (kb0 + kk) * TC_KB_BYTES, u.y, &sh->full[slot]);
+                    bulk_g2s(st + Cfg::OFF_SFB, p.sfb + ((size_t)unit * (p.K / 64) + (size_t)kb0 * 4) * 512, KS * TC_SF_TILE, &sh->full[slot]);
                     ++g;
                 }
             }
@@ -225,7 +240,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
             const uint32_t smem16 = smem_u32(smem) >> 4;
             bool ok = true;
             while (ok) {
-                const int buf = it & 1;
+                const int buf = it % Cfg::NBUF;
                 bool first = true;
                 bool end = false;
                 while (true) {
@@ -234,8 +249,8 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                     tc_fence_after();
                     const TcStageInfo inf = sh->info[slot];
                     if (first) {
-                        // accumulator buffer must have been drained by the epilogue two items ago
-                        if (it >= 2 && !mbar_wait(&sh->tmem_empty[buf], ((it >> 1) - 1) & 1)) { ok = false; break; }
+                        // the accumulator buffer must have been drained by the epilogue NBUF items ago
+                        if (it >= (uint32_t)Cfg::NBUF && !mbar_wait(&sh->tmem_empty[buf], ((it / Cfg::NBUF) - 1) & 1)) { ok = false; break; }
                         tc_fence_after();
                         first = false;
                     }
@@ -247,25 +262,30 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                     // descriptors: only the 14-bit start-address field (bytes >> 4) differs between
                     // tiles, so each one is a single add on a per-stage base
                     const uint32_t st16 = smem16 + slot * (Cfg::STAGE_BYTES >> 4);
-                    const uint32_t sfcol = tmem + TC_SF_COL0 + (g & 1) * TC_SF_COLS;
+                    const uint32_t sfcol = tmem + TC_SF_COL0 + (g & 1) * Cfg::SF_COLS;
 #pragma unroll
-                    for (int a = 0; a < NA; ++a)
+                    for (int t = 0; t < Cfg::NT; ++t)          // weight scales: tile t = a * KS + kk
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
-                            tc_cp_sf(sfcol + a * 16 + j * 4, make_desc(st16 + ((Cfg::OFF_SFA + a * TC_SF_TILE + j * 512) >> 4), DESC_SF_HI));
+                            tc_cp_sf(sfcol + t * 16 + j * 4, make_desc(st16 + ((Cfg::OFF_SFA + (t * 4 + j) * 512) >> 4), DESC_SF_HI));
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        tc_cp_sf(sfcol + 32 + j * 4, make_desc(st16 + ((Cfg::OFF_SFB + j * 512) >> 4), DESC_SF_HI));
+                    for (int kk = 0; kk < KS; ++kk)             // token scales
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            tc_cp_sf(sfcol + Cfg::NT * 16 + kk * 16 + j * 4, make_desc(st16 + ((Cfg::OFF_SFB + (kk * 4 + j) * 512) >> 4), DESC_SF_HI));
                     if (inf.kb == 0) idesc = idesc_nvf4(inf.nbox);
-                    const uint32_t dcol = tmem + buf * TC_ACC_STRIDE;
+                    const uint32_t dcol = tmem + buf * Cfg::ACC_STRIDE;
 #pragma unroll
-                    for (int a = 0; a < NA; ++a)
+                    for (int kk = 0; kk < KS; ++kk)
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            tc_mma(dcol + a * TC_UNIT_TOK,
-                                   make_desc(st16 + ((a * TC_A_TILE + j * 32) >> 4) + DESC_SW128_LBO, DESC_SW128_HI),
-                                   make_desc(st16 + ((Cfg::OFF_B + j * 32) >> 4) + DESC_SW128_LBO, DESC_SW128_HI),
-                                   idesc, sfcol + a * 16 + j * 4, sfcol + 32 + j * 4, (inf.kb > 0 || j > 0) ? 1u : 0u);
+                        for (int a = 0; a < NA; ++a)
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                tc_mma(dcol + a * UT,
+                                       make_desc(st16 + (((a * KS + kk) * TC_A_TILE + j * 32) >> 4) + DESC_SW128_LBO, DESC_SW128_HI),
+                                       make_desc(st16 + ((Cfg::OFF_B + kk * Cfg::B_TILE + j * 32) >> 4) + DESC_SW128_LBO, DESC_SW128_HI),
+                                       idesc, sfcol + (a * KS + kk) * 16 + j * 4, sfcol + Cfg::NT * 16 + kk * 16 + j * 4,
+                                       (inf.kb > 0 || kk > 0 || j > 0) ? 1u : 0u);
                     tc_commit(&sh->empty[slot]);       // stage (and its scale columns) reusable when these finish
                     ++g;
                     if (inf.last) { sh->epi[buf] = inf; break; }
@@ -279,9 +299,9 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
             if (!ok) {
                 tc_timeout(p.ws, sh);
                 // let the epilogue leave
-                sh->epi[it & 1] = TcStageInfo{-1, 0, 0, 0, 0, 0, 0, 1};
-                tc_commit(&sh->tmem_full[it & 1]);
-                mbar_arrive(&sh->tmem_full[it & 1]);
+                sh->epi[it % Cfg::NBUF] = TcStageInfo{-1, 0, 0, 0, 0, 0, 0, 1};
+                tc_commit(&sh->tmem_full[it % Cfg::NBUF]);
+                mbar_arrive(&sh->tmem_full[it % Cfg::NBUF]);
             }
         }
     } else {
@@ -290,20 +310,20 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
         const int row = quad * 32 + lane;                 // row of the 128-row tile
         uint32_t it = 0;
         while (true) {
-            const int buf = it & 1;
-            if (!mbar_wait(&sh->tmem_full[buf], (it >> 1) & 1)) { if (lane == 0) tc_timeout(p.ws, sh); break; }
+            const int buf = it % Cfg::NBUF;
+            if (!mbar_wait(&sh->tmem_full[buf], (it / Cfg::NBUF) & 1)) { if (lane == 0) tc_timeout(p.ws, sh); break; }
             tc_fence_after();
             const TcStageInfo inf = sh->epi[buf];
             if (inf.expert < 0) break;
             const bool shd = inf.expert >= p.E;
             const float alpha = shd ? p.gs_shared[0] : p.gs_routed[inf.expert];
-            const uint32_t tacc = tmem + ((uint32_t)(quad * 32) << 16) + buf * TC_ACC_STRIDE;
+            const uint32_t tacc = tmem + ((uint32_t)(quad * 32) << 16) + buf * Cfg::ACC_STRIDE;
             if (NA == 2) {
                 const int n = inf.tile * TC_ROWS + row;       // intermediate index of this lane
                 for (int c0 = 0; c0 < inf.nbox; c0 += 8) {
                     uint32_t gr[8], ur[8];
                     tc_ld8(tacc + c0, gr);
-                    tc_ld8(tacc + TC_UNIT_TOK + c0, ur);
+                    tc_ld8(tacc + UT + c0, ur);
                     tc_ld_wait();
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {
@@ -365,7 +385,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
 // Same arithmetic as quantize_kernel (…tma_ext.cu:249-279).
 // ---------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
-permute_quantize_kernel(const __nv_bfloat16* __restrict__ x, int M, int K, int T, int E, int has_shared,
+permute_quantize_kernel(const __nv_bfloat16* __restrict__ x, int M, int K, int T, int E, int has_shared, int tc_cap,
                         const int32_t* __restrict__ topk_ids, const int32_t* __restrict__ expert_map, Workspace ws) {
     const int bpr = K / SF_BLOCK;
     const long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -402,8 +422,8 @@ permute_quantize_kernel(const __nv_bfloat16* __restrict__ x, int M, int K, int T
             slot = ws.expert_offsets[E] + m;
         }
         const int rank = slot - ws.expert_offsets[e];
-        const int unit = ws.tc_unit_base[e] + rank / TC_UNIT_TOK;
-        const int r = rank % TC_UNIT_TOK;
+        const int unit = ws.tc_unit_base[e] + rank / tc_cap;
+        const int r = rank % tc_cap;
         reinterpret_cast<uint2*>(ws.act_q_sorted + (size_t)slot * (K / 2))[kb] = make_uint2(lo, hi);
         ws.act_sf_atoms[((size_t)unit * (K / 64) + (kb >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = sb;
     }
@@ -479,7 +499,7 @@ int launch_permute_quantize(const vmoe_shape& s, const __nv_bfloat16* x, const i
     const long long nblocks = (long long)M * (s.hidden / SF_BLOCK);
     if (nblocks == 0) return VMOE_OK;
     permute_quantize_kernel<<<(unsigned)((nblocks + 255) / 256), 256, 0, st>>>(x, M, s.hidden, s.topk, s.num_experts,
-                                                                               s.has_shared, ids, expert_map, ws);
+                                                                               s.has_shared, tc_unit_cap(s, M), ids, expert_map, ws);
     return cuda_status(cudaGetLastError());
 }
 
@@ -490,10 +510,10 @@ int launch_prep_sf(const uint8_t* sf, long long rows, int K, uint8_t* atoms, int
     return cuda_status(cudaGetLastError());
 }
 
-template <int NA>
+template <int NA, int KS, int UT>
 static int launch_tc(const vmoe_shape& s, const WeightSet& routed, const WeightSet& shared, const PreparedSet& prep,
                      int M, const Workspace& ws, cudaStream_t st) {
-    using Cfg = TcCfg<NA>;
+    using Cfg = TcCfg<NA, KS, UT>;
     int rc = get_encoder();
     if (rc) return rc;
     TcParams p;
@@ -508,7 +528,7 @@ static int launch_tc(const vmoe_shape& s, const WeightSet& routed, const WeightS
     const long long S = (long long)s.max_tokens * s.topk + (s.has_shared ? s.max_tokens : 0);
     const uint8_t* bsrc = (NA == 2) ? ws.act_q_sorted : ws.inter_q;
     const int boxes[4] = {8, 16, 32, 64};
-    for (int i = 0; i < 4; ++i)
+    for (int i = 0; i < 4 && boxes[i] <= UT; ++i)
         if ((rc = make_map(&p.map_b[i], bsrc, K / 2, (uint64_t)(S > 0 ? S : 1), boxes[i]))) return rc;
     p.sfa_routed = (NA == 2) ? prep.w13_sf_atoms : prep.w2_sf_atoms;
     p.sfa_shared = (NA == 2) ? prep.shared_w13_sf_atoms : prep.shared_w2_sf_atoms;
@@ -523,26 +543,33 @@ static int launch_tc(const vmoe_shape& s, const WeightSet& routed, const WeightS
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        if (cudaFuncSetAttribute(tc_gemm_kernel<NA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(tc_gemm_kernel<NA, KS, UT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return VMOE_ERR_CUDA;
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
     const long long units_hint = min((long long)M * s.topk + (s.has_shared ? M : 0), (long long)max_tc_units(&s));
     long long grid = min((long long)tc_sm_count(), units_hint * p.tiles);
     if (grid < 1) grid = 1;
-    tc_gemm_kernel<NA><<<(unsigned)grid, TC_THREADS, smem, st>>>(p);
+    tc_gemm_kernel<NA, KS, UT><<<(unsigned)grid, TC_THREADS, smem, st>>>(p);
     return cuda_status(cudaGetLastError());
 }
 
 int launch_tc_gate_up(const vmoe_shape& s, const WeightSet& routed, const WeightSet& shared, const PreparedSet& prep,
                       int M, const Workspace& ws, cudaStream_t st) {
     if (M == 0) return VMOE_OK;
-    return launch_tc<2>(s, routed, shared, prep, M, ws, st);
+    return tc_unit_cap(s, M) == TC_UNIT_TOK_SMALL ? launch_tc<2, 1, TC_UNIT_TOK_SMALL>(s, routed, shared, prep, M, ws, st)
+                                                  : launch_tc<2, 1, TC_UNIT_TOK>(s, routed, shared, prep, M, ws, st);
 }
 int launch_tc_down(const vmoe_shape& s, const WeightSet& routed, const WeightSet& shared, const PreparedSet& prep,
                    int M, const Workspace& ws, cudaStream_t st) {
     if (M == 0) return VMOE_OK;
-    return launch_tc<1>(s, routed, shared, prep, M, ws, st);
+    // two k-blocks per stage when the reduction length allows: half as many ring round trips per byte
+    const bool small = tc_unit_cap(s, M) == TC_UNIT_TOK_SMALL;
+    if ((s.inter / 256) % 2 == 0)
+        return small ? launch_tc<1, 2, TC_UNIT_TOK_SMALL>(s, routed, shared, prep, M, ws, st)
+                     : launch_tc<1, 2, TC_UNIT_TOK>(s, routed, shared, prep, M, ws, st);
+    return small ? launch_tc<1, 1, TC_UNIT_TOK_SMALL>(s, routed, shared, prep, M, ws, st)
+                 : launch_tc<1, 1, TC_UNIT_TOK>(s, routed, shared, prep, M, ws, st);
 }
 
 }  // namespace vmoe
