@@ -244,7 +244,11 @@ def run_ours(args):
     kname = "tc_gemm_kernel<2> (gate_up, tcgen05)" if path == 2 else "gate_up_kernel (CUDA-core GEMV)"
     roof = {"bound": "hbm", "kernel": kname, "achieved": gate_up_bytes / gu_s / 1e9, "peak": peak,
             "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s",
-            "unit": "GB/s", "frac": gate_up_bytes / gu_s / 1e9 / peak, "traffic": None,
+            "unit": "GB/s", "frac": gate_up_bytes / gu_s / 1e9 / peak,
+            # DRAM bytes per launch: one ncu capture of this kernel at batch 16 read + wrote 1.042x its
+            # algorithmic bytes (profiles/tc_gemm_gate_up_down_decode_bs16_ncu.md); traffic grows with the
+            # number of distinct experts like the algorithmic bytes do, so that ratio is applied here
+            "traffic": (1.042 if path == 2 else 1.048) * gate_up_bytes,
             "algorithmic_bytes_per_launch": gate_up_bytes, "us_per_launch": gu_s * 1e6,
             "distinct_experts_per_step": U,
             "down_kernel": {"achieved": down_bytes / dn_s / 1e9, "frac": down_bytes / dn_s / 1e9 / peak,
