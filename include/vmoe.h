@@ -183,6 +183,48 @@ int vmoe_stage_combine(const vmoe_shape* shape, int32_t M, void* workspace,
  * counterpart (its waits are unbounded: …tma_ext.cu:156-167). */
 int vmoe_read_status(void* workspace, const vmoe_shape* shape, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Expert parallelism across the GPUs of one NVLink box.  One process per GPU.  Every rank owns
+ * `experts_per_rank` consecutive experts (gpu = e / experts_per_rank, as
+ * fused-moe/p2p_moe_routing.py:26-33) and a "slab" of device memory that its peers write into:
+ * quantised token rows + (local expert, pair, weight) records on the way in, weighted fp32 output
+ * rows on the way back.  The reference only sketches this exchange
+ * (fused-moe/p2p_moe_routing.py:113-131; its working variants replicate all tokens and all-reduce,
+ * fused-moe/patches/p2p_ep_communicator.py:99-155).
+ * Set-up (once, outside the forward path): vmoe_ep_alloc a slab of vmoe_ep_slab_bytes, export its
+ * IPC handle, exchange the 64-byte handles between ranks by any means, vmoe_ep_ipc_open the
+ * peers' handles and fill vmoe_ep_ctx.slab[] (own entry = own pointer). */
+typedef struct vmoe_ep_ctx {
+    int32_t rank, world;          /* world <= 16 */
+    int32_t experts_per_rank;
+    int32_t capacity;             /* rows one source rank may send to one destination rank per call */
+    int32_t max_local_tokens;     /* tokens a rank may bring to one call */
+    int32_t reserved[3];
+    void*   slab[16];             /* slab of every rank as mapped into this process */
+} vmoe_ep_ctx;
+
+size_t vmoe_ep_slab_bytes(const vmoe_ep_ctx* ctx, const vmoe_shape* shape);
+size_t vmoe_ep_workspace_bytes(const vmoe_ep_ctx* ctx, const vmoe_shape* shape);
+int    vmoe_ep_alloc(size_t bytes, void** out);          /* cudaMalloc + clear; set-up only */
+int    vmoe_ep_free(void* slab);
+int    vmoe_ep_ipc_export(void* slab, void* handle_out_64_bytes);
+int    vmoe_ep_ipc_open(const void* handle_64_bytes, void** out);
+int    vmoe_ep_ipc_close(void* mapped);
+
+/* One expert-parallel forward on this rank: route the M local tokens, dispatch them to the ranks
+ * that own their experts, run the local experts on what arrived (tensor-core path; weights must
+ * carry prepared scales), send each weighted row back to its owner, reduce.  shape->num_experts =
+ * experts_per_rank, shape->num_global_experts = world * experts_per_rank.  `epoch` must be > 0 and
+ * increase by one per call on every rank.  Every cross-GPU wait is bounded (about one second);
+ * on expiry the call's status word reads VMOE_ERR_TIMEOUT and the output is not written.
+ * VMOE_ERR_LIMIT in the status word: a (source, destination) pair exceeded `capacity`. */
+int vmoe_ep_forward(const vmoe_ep_ctx* ctx, const vmoe_shape* shape, const vmoe_weights* routed,
+                    const vmoe_weights* shared, const void* hidden_bf16, const float* router_logits,
+                    void* out_bf16, int32_t M, int32_t epoch, void* workspace, size_t workspace_bytes,
+                    void* stream);
+/* Status word of an expert-parallel workspace (synchronises the stream). */
+int vmoe_ep_read_status(const vmoe_ep_ctx* ctx, const vmoe_shape* shape, void* workspace, void* stream);
+
 /* Permutation by expert for callers that cannot allocate device memory.  It has no
  * counterpart in the reference.  Same tables as vmoe_build_tables, but written to arrays the
  * caller passes (expert_offsets [E + 2], sorted_pair / gather_idx / scatter_weights

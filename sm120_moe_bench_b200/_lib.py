@@ -30,6 +30,12 @@ _LAYOUT_FIELDS = ["total_bytes", "topk_ids", "topk_weights", "expert_offsets", "
                   "tc_unit_base", "act_q_sorted", "act_sf_atoms", "inter_sf_atoms"]
 
 
+class VmoeEpCtx(C.Structure):
+    _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("experts_per_rank", C.c_int32),
+                ("capacity", C.c_int32), ("max_local_tokens", C.c_int32), ("reserved", C.c_int32 * 3),
+                ("slab", C.c_void_p * 16)]
+
+
 class VmoeWsLayout(C.Structure):
     _fields_ = [(n, C.c_size_t) for n in _LAYOUT_FIELDS]
 
@@ -54,6 +60,16 @@ SIGNATURES = {
                                   C.c_int32, _P, _P]),
     "vmoe_stage_combine": (C.c_int, [C.POINTER(VmoeShape), C.c_int32, _P, _P, _P]),
     "vmoe_read_status": (C.c_int, [_P, C.POINTER(VmoeShape), _P]),
+    "vmoe_ep_slab_bytes": (C.c_size_t, [C.POINTER(VmoeEpCtx), C.POINTER(VmoeShape)]),
+    "vmoe_ep_workspace_bytes": (C.c_size_t, [C.POINTER(VmoeEpCtx), C.POINTER(VmoeShape)]),
+    "vmoe_ep_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p)]),
+    "vmoe_ep_free": (C.c_int, [_P]),
+    "vmoe_ep_ipc_export": (C.c_int, [_P, _P]),
+    "vmoe_ep_ipc_open": (C.c_int, [_P, C.POINTER(C.c_void_p)]),
+    "vmoe_ep_ipc_close": (C.c_int, [_P]),
+    "vmoe_ep_forward": (C.c_int, [C.POINTER(VmoeEpCtx), C.POINTER(VmoeShape), C.POINTER(VmoeWeights),
+                                  C.POINTER(VmoeWeights), _P, _P, _P, C.c_int32, C.c_int32, _P, C.c_size_t, _P]),
+    "vmoe_ep_read_status": (C.c_int, [C.POINTER(VmoeEpCtx), C.POINTER(VmoeShape), _P, _P]),
     "vmoe_permute_noalloc": (C.c_int, [_P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                        _P, _P, _P, _P, _P, _P]),
 }

@@ -102,6 +102,7 @@ int resolve_workspace(const vmoe_shape* s, void* base, Workspace* ws) {
     ws->act_q_sorted    = b + L.act_q_sorted;
     ws->act_sf_atoms    = b + L.act_sf_atoms;
     ws->inter_sf_atoms  = b + L.inter_sf_atoms;
+    ws->row_dst         = nullptr;
     return VMOE_OK;
 }
 

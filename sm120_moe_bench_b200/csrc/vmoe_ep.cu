@@ -1,0 +1,416 @@
+// Expert parallelism inside one NVLink / NVSwitch box: token dispatch and weighted combine as
+// peer-memory kernels.  One process per GPU; NCCL (or any other channel) is only used by the host
+// to exchange the IPC handles of the slabs once.
+//
+// Reference semantics: experts in contiguous blocks, gpu = e / (E / G), local = e % (E / G)
+// (fused-moe/p2p_moe_routing.py:26-33); the reference itself only sketches the exchange
+// (fused-moe/p2p_moe_routing.py:113-131) or replicates every token on every rank and all-reduces
+// (fused-moe/patches/p2p_ep_communicator.py:99-155).  Here each token row crosses NVLink once per
+// pair, already quantised (2304 bytes at K = 4096), and each weighted output row crosses once
+// (fp32, so the owner's fixed-order sum is bit-identical to the single-GPU result).
+//
+// Per forward call on rank r (one stream, no host synchronisation):
+//   route -> plan (slab positions) -> dispatch (quantise + 16-byte peer stores + release flag)
+//   -> gather (bounded acquire-wait on every source's flag, flat pair list) -> permutation tables
+//   -> permute (received rows into sorted-slot order) -> tcgen05 gate_up -> tcgen05 down whose
+//   epilogue stores each weighted row straight into the owner's combine slab over NVLink
+//   -> signal -> combine (bounded wait on every rank's flag, fixed-order sum -> bf16).
+// Plain peer loads / stores only: no multimem, no TMA from peer memory.
+#include "vmoe_common.cuh"
+
+#include <string.h>
+
+namespace vmoe {
+
+constexpr int EP_MAX_RANKS = 16;
+
+struct EpFlags {            // lives at the start of every rank's slab; written by peers
+    int32_t dispatch_flag[EP_MAX_RANKS];    // [src] epoch of the last completed dispatch from src
+    int32_t dispatch_count[EP_MAX_RANKS];   // [src] rows src wrote for that epoch
+    int32_t combine_flag[EP_MAX_RANKS];     // [src] epoch of the last completed down projection on src
+    int32_t pad[16];
+};
+
+struct EpLayout {           // byte offsets inside a slab; identical on every rank
+    size_t flags, recv_q, recv_sf, recv_meta, comb, total;
+};
+
+static size_t ep_align(size_t v) { return (v + 255) / 256 * 256; }
+
+static EpLayout ep_layout(int world, int capacity, int max_local_tokens, int K, int T) {
+    EpLayout L;
+    size_t off = 0;
+    auto take = [&](size_t b) { size_t o = off; off = ep_align(off + b); return o; };
+    L.flags = take(sizeof(EpFlags));
+    L.recv_q = take((size_t)world * capacity * (K / 2));
+    L.recv_sf = take((size_t)world * capacity * (K / 16));
+    L.recv_meta = take((size_t)world * capacity * 16);
+    L.comb = take((size_t)max_local_tokens * (T + 1) * K * 4);
+    L.total = off;
+    return L;
+}
+
+struct EpDev {              // by value into kernels
+    int rank, world, e_local, capacity, epoch;
+    uint8_t* slab[EP_MAX_RANKS];            // every rank's slab as mapped into this process
+    EpLayout L;
+    // plan scratch (local workspace)
+    int32_t* plan_dest; int32_t* plan_pos; int32_t* send_count; int32_t* ticket;
+    int32_t* flat_ids; float* flat_w; float** row_dst;
+};
+
+__device__ __forceinline__ void st_release_sys(int32_t* p, int32_t v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
+    int32_t v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// bounded wait for *p >= want; false when the limit passes
+__device__ __forceinline__ bool wait_flag(const int32_t* p, int32_t want) {
+    if (ld_acquire_sys(p) >= want) return true;
+    const unsigned long long t0 = global_timer_ns();
+    for (uint32_t i = 1;; ++i) {
+        if (ld_acquire_sys(p) >= want) return true;
+        if ((i & 15u) == 0 && global_timer_ns() - t0 > MBAR_WAIT_LIMIT_NS) return false;
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// plan: destination rank and position inside the (src -> dst) slab of every pair, in pair order
+// (deterministic).  Pair index p = m*T + j for routed pairs, M*T + m for the shared expert, which
+// stays on the owner.  One CTA.
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+ep_plan_kernel(const int32_t* __restrict__ topk_ids, int M, int T, int has_shared, EpDev ep) {
+    __shared__ int32_t s_warp[32];
+    __shared__ int32_t s_base;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int P = M * T + (has_shared ? M : 0);
+    for (int d = 0; d < ep.world; ++d) {
+        if (tid == 0) s_base = 0;
+        __syncthreads();
+        for (int p0 = 0; p0 < P; p0 += blockDim.x) {
+            const int p = p0 + tid;
+            int dest = -1;
+            if (p < P) dest = (p < M * T) ? topk_ids[p] / ep.e_local : ep.rank;
+            const bool mine = dest == d;
+            const unsigned bal = __ballot_sync(0xffffffffu, mine);
+            const int wcount = __popc(bal), wrank = __popc(bal & ((1u << lane) - 1u));
+            if (lane == 0) s_warp[warp] = wcount;
+            __syncthreads();
+            int wbase = 0, total = 0;
+            for (int w = 0; w < (int)(blockDim.x >> 5); ++w) { const int c = s_warp[w]; if (w < warp) wbase += c; total += c; }
+            if (mine) { ep.plan_dest[p] = d; ep.plan_pos[p] = s_base + wbase + wrank; }
+            __syncthreads();
+            if (tid == 0) s_base += total;
+            __syncthreads();
+        }
+        if (tid == 0) ep.send_count[d] = s_base;
+        __syncthreads();
+    }
+    if (tid == 0) *ep.ticket = 0;
+}
+
+// ---------------------------------------------------------------------------------
+// dispatch: quantise each 16-block once (same arithmetic as quantize_kernel), store it into the
+// slab of every destination of the token, then release the per-source flag on every peer.
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ topk_ids,
+                   const float* __restrict__ topk_w, int M, int K, int T, int has_shared, EpDev ep,
+                   int32_t* status) {
+    const int bpr = K / SF_BLOCK;
+    const long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < (long long)M * bpr) {
+        const int m = (int)(b / bpr), kb = (int)(b % bpr);
+        const uint4* src = reinterpret_cast<const uint4*>(x + b * SF_BLOCK);
+        uint4 raw[2] = {src[0], src[1]};
+        const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(raw);
+        float v[SF_BLOCK];
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < SF_BLOCK; ++i) { v[i] = __bfloat162float(h[i]); amax = fmaxf(amax, fabsf(v[i])); }
+        const uint8_t sb = e4m3_encode(fmaxf(amax / 6.0f, 1e-30f));
+        float scale = e4m3_decode(sb);
+        if (scale < 1e-30f) scale = 1e-30f;
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) lo |= e2m1_encode(v[i] / scale) << (4 * i);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) hi |= e2m1_encode(v[8 + i] / scale) << (4 * i);
+        for (int j = 0; j <= T; ++j) {
+            if (j == T && !has_shared) break;
+            const int p = (j < T) ? m * T + j : M * T + m;
+            const int d = ep.plan_dest[p], pos = ep.plan_pos[p];
+            if (pos >= ep.capacity) { if (kb == 0) atomicExch(status, VMOE_ERR_LIMIT); continue; }
+            uint8_t* slab = ep.slab[d];
+            const size_t row = (size_t)ep.rank * ep.capacity + pos;
+            reinterpret_cast<uint2*>(slab + ep.L.recv_q + row * (K / 2))[kb] = make_uint2(lo, hi);
+            (slab + ep.L.recv_sf + row * (K / 16))[kb] = sb;
+            if (kb == 0) {
+                const int le = (j < T) ? topk_ids[p] % ep.e_local : ep.e_local;     // shared expert = local id E_local
+                const float w = (j < T) ? topk_w[p] : 1.0f;
+                reinterpret_cast<int4*>(slab + ep.L.recv_meta)[row] = make_int4(le, p, __float_as_int(w), 0);
+            }
+        }
+    }
+    // last CTA to finish publishes the counts and the epoch flag on every peer
+    __threadfence_system();
+    __syncthreads();
+    __shared__ int s_last;
+    if (threadIdx.x == 0) s_last = (atomicAdd(ep.ticket, 1) == (int)gridDim.x - 1);
+    __syncthreads();
+    if (s_last && threadIdx.x < ep.world) {
+        __threadfence_system();
+        const int d = threadIdx.x;
+        EpFlags* f = reinterpret_cast<EpFlags*>(ep.slab[d] + ep.L.flags);
+        const int c = min(ep.send_count[d], ep.capacity);
+        f->dispatch_count[ep.rank] = c;
+        __threadfence_system();
+        st_release_sys(&f->dispatch_flag[ep.rank], ep.epoch);
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// gather: wait (bounded) for every source's flag, then lay the received pairs out as a flat list of
+// "tokens" with one expert each: index f = src * capacity + i; unused positions get expert -1.
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+ep_gather_kernel(EpDev ep, int32_t* status) {
+    __shared__ int s_ok;
+    const EpFlags* f = reinterpret_cast<const EpFlags*>(ep.slab[ep.rank] + ep.L.flags);
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < ep.world) {
+        if (!wait_flag(&f->dispatch_flag[threadIdx.x], ep.epoch)) { atomicExch(status, VMOE_ERR_TIMEOUT); s_ok = 0; }
+    }
+    __syncthreads();
+    const int total = ep.world * ep.capacity;
+    const int4* meta = reinterpret_cast<const int4*>(ep.slab[ep.rank] + ep.L.recv_meta);
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int s = i / ep.capacity, pos = i % ep.capacity;
+        const bool live = s_ok && pos < f->dispatch_count[s];
+        const int4 mt = live ? meta[i] : make_int4(-1, 0, 0, 0);
+        ep.flat_ids[i] = mt.x;
+        ep.flat_w[i] = __int_as_float(mt.z);
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// permute: received FP4 rows -> sorted-slot order + scale atoms (B operand of the tensor-core
+// GEMM), and the destination of each slot's output row in its owner's combine slab.
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+ep_permute_kernel(EpDev ep, int K, int tc_cap, Workspace ws) {
+    const int bpr = K / SF_BLOCK;
+    const long long total = (long long)ep.world * ep.capacity * bpr;
+    const long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= total) return;
+    const int i = (int)(b / bpr), kb = (int)(b % bpr);
+    const int slot = ws.pair_slot[i];
+    if (slot < 0) return;
+    const uint8_t* slab = ep.slab[ep.rank];
+    const uint2 q = reinterpret_cast<const uint2*>(slab + ep.L.recv_q + (size_t)i * (K / 2))[kb];
+    const uint8_t sb = (slab + ep.L.recv_sf + (size_t)i * (K / 16))[kb];
+    const int e = ep.flat_ids[i];
+    const int rank_in_e = slot - ws.expert_offsets[e];
+    const int unit = ws.tc_unit_base[e] + rank_in_e / tc_cap;
+    const int r = rank_in_e % tc_cap;
+    reinterpret_cast<uint2*>(ws.act_q_sorted + (size_t)slot * (K / 2))[kb] = q;
+    ws.act_sf_atoms[((size_t)unit * (K / 64) + (kb >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = sb;
+    if (kb == 0) {
+        const int4 mt = reinterpret_cast<const int4*>(slab + ep.L.recv_meta)[i];
+        const int src = i / ep.capacity;
+        ep.row_dst[slot] = reinterpret_cast<float*>(ep.slab[src] + ep.L.comb) + (size_t)mt.y * K;   // row of pair id mt.y
+    }
+}
+
+__global__ void ep_signal_kernel(EpDev ep) {
+    __threadfence_system();
+    if (threadIdx.x < ep.world) {
+        EpFlags* f = reinterpret_cast<EpFlags*>(ep.slab[threadIdx.x] + ep.L.flags);
+        st_release_sys(&f->combine_flag[ep.rank], ep.epoch);
+    }
+}
+
+// out[m, :] = bf16( sum_{j < T} comb[m*T + j, :] + comb[M*T + m, :] ), fp32, ascending j: the same
+// order as combine_kernel, over rows that arrived from the ranks owning the experts.
+__global__ void __launch_bounds__(256)
+ep_combine_kernel(EpDev ep, int M, int K, int T, int has_shared, __nv_bfloat16* __restrict__ out, int32_t* status) {
+    __shared__ int s_ok;
+    const EpFlags* f = reinterpret_cast<const EpFlags*>(ep.slab[ep.rank] + ep.L.flags);
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if (threadIdx.x < ep.world) {
+        if (!wait_flag(&f->combine_flag[threadIdx.x], ep.epoch)) { atomicExch(status, VMOE_ERR_TIMEOUT); s_ok = 0; }
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    const float* comb = reinterpret_cast<const float*>(ep.slab[ep.rank] + ep.L.comb);
+    const int k4 = K / 4;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)M * k4; i += (long long)gridDim.x * blockDim.x) {
+        const int m = (int)(i / k4), c = (int)(i % k4);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < T; ++j) {
+            const float4 v = reinterpret_cast<const float4*>(comb + (size_t)(m * T + j) * K)[c];
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        if (has_shared) {
+            const float4 v = reinterpret_cast<const float4*>(comb + (size_t)(M * T + m) * K)[c];
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+        uint2 o; o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
+        reinterpret_cast<uint2*>(out + (size_t)m * K)[c] = o;
+    }
+}
+
+}  // namespace vmoe
+
+using namespace vmoe;
+
+// ---------------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------------
+static int ep_check(const vmoe_ep_ctx* c) {
+    if (!c) return VMOE_ERR_NULL;
+    if (c->world < 1 || c->world > EP_MAX_RANKS || c->rank < 0 || c->rank >= c->world) return VMOE_ERR_SHAPE;
+    if (c->experts_per_rank <= 0 || c->capacity <= 0 || c->max_local_tokens <= 0) return VMOE_ERR_SHAPE;
+    for (int i = 0; i < c->world; ++i) if (!c->slab[i]) return VMOE_ERR_NULL;
+    return VMOE_OK;
+}
+
+// the shape the local expert compute runs with: G * capacity single-expert "tokens", experts
+// 0 .. E_local - 1 routed + id E_local = the shared expert
+static vmoe_shape ep_local_shape(const vmoe_ep_ctx* c, const vmoe_shape* s, bool for_tables) {
+    vmoe_shape l = *s;
+    l.max_tokens = c->world * c->capacity;
+    l.topk = 1;
+    l.num_experts = c->experts_per_rank + (for_tables ? 1 : 0);
+    l.num_global_experts = l.num_experts;
+    l.has_shared = for_tables ? 0 : 1;
+    l.path = VMOE_PATH_TC;
+    return l;
+}
+
+extern "C" {
+
+size_t vmoe_ep_slab_bytes(const vmoe_ep_ctx* ctx, const vmoe_shape* shape) {
+    if (ep_check(ctx) || !shape) return 0;
+    return ep_layout(ctx->world, ctx->capacity, ctx->max_local_tokens, shape->hidden, shape->topk).total;
+}
+
+size_t vmoe_ep_workspace_bytes(const vmoe_ep_ctx* ctx, const vmoe_shape* shape) {
+    if (ep_check(ctx) || !shape) return 0;
+    const vmoe_shape l = ep_local_shape(ctx, shape, true);
+    const size_t base = vmoe_workspace_bytes(&l);
+    if (!base) return 0;
+    const size_t rows = (size_t)ctx->world * ctx->capacity;
+    const size_t P = (size_t)ctx->max_local_tokens * (shape->topk + 1);
+    // + plan_dest, plan_pos [P], send_count[16], ticket, flat_ids, flat_w [rows], row_dst [rows], local topk ids / weights
+    return base + ep_align(P * 4) * 2 + 512 + ep_align(rows * 4) * 2 + ep_align(rows * 8) + ep_align(P * 4) * 2;
+}
+
+int vmoe_ep_alloc(size_t bytes, void** out) {
+    if (!out || bytes == 0) return VMOE_ERR_NULL;
+    if (cudaMalloc(out, bytes) != cudaSuccess) return VMOE_ERR_CUDA;
+    return cudaMemset(*out, 0, bytes) == cudaSuccess ? VMOE_OK : VMOE_ERR_CUDA;
+}
+int vmoe_ep_free(void* p) { return cuda_status(cudaFree(p)); }
+
+int vmoe_ep_ipc_export(void* slab, void* handle_out_64_bytes) {
+    if (!slab || !handle_out_64_bytes) return VMOE_ERR_NULL;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    return cuda_status(cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(handle_out_64_bytes), slab));
+}
+int vmoe_ep_ipc_open(const void* handle_64_bytes, void** out) {
+    if (!handle_64_bytes || !out) return VMOE_ERR_NULL;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle_64_bytes, sizeof(h));
+    return cuda_status(cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess));
+}
+int vmoe_ep_ipc_close(void* p) { return cuda_status(cudaIpcCloseMemHandle(p)); }
+
+int vmoe_ep_forward(const vmoe_ep_ctx* ctx, const vmoe_shape* shape, const vmoe_weights* routed,
+                    const vmoe_weights* shared, const void* hidden_bf16, const float* router_logits,
+                    void* out_bf16, int32_t M, int32_t epoch, void* workspace, size_t workspace_bytes,
+                    void* stream) {
+    int rc = ep_check(ctx);
+    if (rc) return rc;
+    if (!shape || !routed || !workspace) return VMOE_ERR_NULL;
+    if (M > 0 && (!hidden_bf16 || !router_logits || !out_bf16)) return VMOE_ERR_NULL;   // a rank may bring no tokens
+    if (shape->has_shared && !shared) return VMOE_ERR_NULL;
+    if (M < 0 || M > ctx->max_local_tokens || epoch <= 0) return VMOE_ERR_SHAPE;
+    if (shape->num_global_experts != ctx->world * ctx->experts_per_rank || shape->num_experts != ctx->experts_per_rank) return VMOE_ERR_SHAPE;
+    if (shape->hidden % 256 || shape->inter % 256) return VMOE_ERR_SHAPE;
+    if (!routed->w13_sf_atoms || !routed->w2_sf_atoms || (shape->has_shared && (!shared->w13_sf_atoms || !shared->w2_sf_atoms)))
+        return VMOE_ERR_NULL;                              // the expert-parallel path runs on the tensor cores only
+    if (workspace_bytes < vmoe_ep_workspace_bytes(ctx, shape)) return VMOE_ERR_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int K = shape->hidden, T = shape->topk;
+    const vmoe_shape lt = ep_local_shape(ctx, shape, true), lk = ep_local_shape(ctx, shape, false);
+    Workspace ws;
+    if ((rc = resolve_workspace(&lt, workspace, &ws))) return rc;
+    // EP scratch behind the regular workspace
+    uint8_t* extra = static_cast<uint8_t*>(workspace) + vmoe_workspace_bytes(&lt);
+    const size_t rows = (size_t)ctx->world * ctx->capacity;
+    const size_t P = (size_t)ctx->max_local_tokens * (T + 1);
+    EpDev ep;
+    memset(&ep, 0, sizeof(ep));
+    ep.rank = ctx->rank; ep.world = ctx->world; ep.e_local = ctx->experts_per_rank; ep.capacity = ctx->capacity; ep.epoch = epoch;
+    for (int i = 0; i < ctx->world; ++i) ep.slab[i] = static_cast<uint8_t*>(ctx->slab[i]);
+    ep.L = ep_layout(ctx->world, ctx->capacity, ctx->max_local_tokens, K, T);
+    auto take = [&](size_t b) { uint8_t* p = extra; extra += ep_align(b); return p; };
+    ep.plan_dest = reinterpret_cast<int32_t*>(take(P * 4));
+    ep.plan_pos = reinterpret_cast<int32_t*>(take(P * 4));
+    ep.send_count = reinterpret_cast<int32_t*>(take(256));
+    ep.ticket = reinterpret_cast<int32_t*>(take(256));
+    ep.flat_ids = reinterpret_cast<int32_t*>(take(rows * 4));
+    ep.flat_w = reinterpret_cast<float*>(take(rows * 4));
+    ep.row_dst = reinterpret_cast<float**>(take(rows * 8));
+    int32_t* loc_ids = reinterpret_cast<int32_t*>(take(P * 4));
+    float* loc_w = reinterpret_cast<float*>(take(P * 4));
+    int32_t* status = ws.counters + CNT_STATUS;
+    const int has_shared = shape->has_shared ? 1 : 0;
+
+    if ((rc = launch_route(router_logits, M, shape->num_global_experts, T, loc_ids, loc_w, st))) return rc;
+    ep_plan_kernel<<<1, 1024, 0, st>>>(loc_ids, M, T, has_shared, ep);
+    {
+        const long long nb = (long long)M * (K / SF_BLOCK);
+        const unsigned grid = (unsigned)((nb + 255) / 256 > 0 ? (nb + 255) / 256 : 1);
+        ep_dispatch_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(hidden_bf16), loc_ids, loc_w, M, K, T,
+                                                 has_shared, ep, status);
+    }
+    ep_gather_kernel<<<64, 256, 0, st>>>(ep, status);
+    const int Mr = (int)rows;
+    const int cap = tc_unit_cap(lt, Mr);
+    if ((rc = launch_tables(lt, ep.flat_ids, ep.flat_w, nullptr, Mr, ws, st, cap))) return rc;
+    {
+        const long long nb = (long long)rows * (K / SF_BLOCK);
+        ep_permute_kernel<<<(unsigned)((nb + 255) / 256), 256, 0, st>>>(ep, K, cap, ws);
+    }
+    const WeightSet r{routed->w13, routed->w13_sf, routed->w13_gs, routed->w2, routed->w2_sf, routed->w2_gs};
+    const WeightSet sh = shape->has_shared ? WeightSet{shared->w13, shared->w13_sf, shared->w13_gs, shared->w2, shared->w2_sf, shared->w2_gs}
+                                           : r;
+    PreparedSet prep{routed->w13_sf_atoms, routed->w2_sf_atoms,
+                     shape->has_shared ? shared->w13_sf_atoms : routed->w13_sf_atoms,
+                     shape->has_shared ? shared->w2_sf_atoms : routed->w2_sf_atoms};
+    ws.row_dst = ep.row_dst;
+    if ((rc = launch_tc_gate_up(lk, r, sh, prep, Mr, ws, st, cap, Mr))) return rc;
+    if ((rc = launch_tc_down(lk, r, sh, prep, Mr, ws, st, cap, Mr))) return rc;
+    ep_signal_kernel<<<1, 32, 0, st>>>(ep);
+    ep_combine_kernel<<<296, 256, 0, st>>>(ep, M, K, T, has_shared, static_cast<__nv_bfloat16*>(out_bf16), status);
+    return cuda_status(cudaGetLastError());
+}
+
+int vmoe_ep_read_status(const vmoe_ep_ctx* ctx, const vmoe_shape* shape, void* workspace, void* stream) {
+    int rc = ep_check(ctx);
+    if (rc) return rc;
+    if (!shape || !workspace) return VMOE_ERR_NULL;
+    const vmoe_shape lt = ep_local_shape(ctx, shape, true);
+    return vmoe_read_status(workspace, &lt, stream);
+}
+
+}  // extern "C"

@@ -359,7 +359,9 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                         if (t < inf.ntok) {
                             const int srow = inf.slot0 + t;
                             const float scale = p.ws.scatter_weights[srow] * alpha;
-                            p.ws.pair_out[(size_t)srow * p.hidden + j] = scale * __uint_as_float(yr[c]);
+                            // expert parallelism: the row goes straight to its owner's combine slab (peer store)
+                            float* orow = p.ws.row_dst ? p.ws.row_dst[srow] : p.ws.pair_out + (size_t)srow * p.hidden;
+                            orow[j] = scale * __uint_as_float(yr[c]);
                         }
                     }
                 }
@@ -512,7 +514,7 @@ int launch_prep_sf(const uint8_t* sf, long long rows, int K, uint8_t* atoms, int
 
 template <int NA, int KS, int UT>
 static int launch_tc(const vmoe_shape& s, const WeightSet& routed, const WeightSet& shared, const PreparedSet& prep,
-                     int M, const Workspace& ws, cudaStream_t st) {
+                     int M, const Workspace& ws, cudaStream_t st, long long b_rows) {
     using Cfg = TcCfg<NA, KS, UT>;
     int rc = get_encoder();
     if (rc) return rc;
@@ -525,7 +527,7 @@ static int launch_tc(const vmoe_shape& s, const WeightSet& routed, const WeightS
     if ((rc = make_map(&p.map_a_routed, wr, K / 2, (uint64_t)s.num_experts * rows, TC_ROWS))) return rc;
     if (s.has_shared) { if ((rc = make_map(&p.map_a_shared, wsx, K / 2, rows, TC_ROWS))) return rc; }
     else p.map_a_shared = p.map_a_routed;
-    const long long S = (long long)s.max_tokens * s.topk + (s.has_shared ? s.max_tokens : 0);
+    const long long S = b_rows >= 0 ? b_rows : (long long)s.max_tokens * s.topk + (s.has_shared ? s.max_tokens : 0);
     const uint8_t* bsrc = (NA == 2) ? ws.act_q_sorted : ws.inter_q;
     const int boxes[4] = {8, 16, 32, 64};
     for (int i = 0; i < 4 && boxes[i] <= UT; ++i)
@@ -555,21 +557,22 @@ static int launch_tc(const vmoe_shape& s, const WeightSet& routed, const WeightS
 }
 
 int launch_tc_gate_up(const vmoe_shape& s, const WeightSet& routed, const WeightSet& shared, const PreparedSet& prep,
-                      int M, const Workspace& ws, cudaStream_t st) {
+                      int M, const Workspace& ws, cudaStream_t st, int unit_cap, long long b_rows) {
     if (M == 0) return VMOE_OK;
-    return tc_unit_cap(s, M) == TC_UNIT_TOK_SMALL ? launch_tc<2, 1, TC_UNIT_TOK_SMALL>(s, routed, shared, prep, M, ws, st)
-                                                  : launch_tc<2, 1, TC_UNIT_TOK>(s, routed, shared, prep, M, ws, st);
+    const bool small = (unit_cap > 0 ? unit_cap : tc_unit_cap(s, M)) == TC_UNIT_TOK_SMALL;
+    return small ? launch_tc<2, 1, TC_UNIT_TOK_SMALL>(s, routed, shared, prep, M, ws, st, b_rows)
+                 : launch_tc<2, 1, TC_UNIT_TOK>(s, routed, shared, prep, M, ws, st, b_rows);
 }
 int launch_tc_down(const vmoe_shape& s, const WeightSet& routed, const WeightSet& shared, const PreparedSet& prep,
-                   int M, const Workspace& ws, cudaStream_t st) {
+                   int M, const Workspace& ws, cudaStream_t st, int unit_cap, long long b_rows) {
     if (M == 0) return VMOE_OK;
     // two k-blocks per stage when the reduction length allows: half as many ring round trips per byte
-    const bool small = tc_unit_cap(s, M) == TC_UNIT_TOK_SMALL;
+    const bool small = (unit_cap > 0 ? unit_cap : tc_unit_cap(s, M)) == TC_UNIT_TOK_SMALL;
     if ((s.inter / 256) % 2 == 0)
-        return small ? launch_tc<1, 2, TC_UNIT_TOK_SMALL>(s, routed, shared, prep, M, ws, st)
-                     : launch_tc<1, 2, TC_UNIT_TOK>(s, routed, shared, prep, M, ws, st);
-    return small ? launch_tc<1, 1, TC_UNIT_TOK_SMALL>(s, routed, shared, prep, M, ws, st)
-                 : launch_tc<1, 1, TC_UNIT_TOK>(s, routed, shared, prep, M, ws, st);
+        return small ? launch_tc<1, 2, TC_UNIT_TOK_SMALL>(s, routed, shared, prep, M, ws, st, b_rows)
+                     : launch_tc<1, 2, TC_UNIT_TOK>(s, routed, shared, prep, M, ws, st, b_rows);
+    return small ? launch_tc<1, 1, TC_UNIT_TOK_SMALL>(s, routed, shared, prep, M, ws, st, b_rows)
+                 : launch_tc<1, 1, TC_UNIT_TOK>(s, routed, shared, prep, M, ws, st, b_rows);
 }
 
 }  // namespace vmoe
