@@ -40,6 +40,11 @@ def parse():
     ap.add_argument("--rotate", type=int, default=4, help="distinct input sets cycled through")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-tokens", type=int, default=2)
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "stack"],
+                    help="decode: BASELINE config 2 (default, the headline); prefill: config 3 (8192 tokens, "
+                         "FP4 TFLOP/s); stack: config 5 shape on one GPU (15 layers, batch 32, CUDA graph)")
+    ap.add_argument("--zipf", type=float, default=None, help="prefill: Zipf exponent of the routing bias (1.2 = skewed variant)")
+    ap.add_argument("--layers", type=int, default=15)
     ap.add_argument("--path", default="tc", choices=["tc", "gemv"],
                     help="tc: tcgen05 block-scaled path (default); gemv: CUDA-core streaming GEMV path")
     return ap.parse_args()
@@ -155,7 +160,8 @@ def run_reference_arm(args):
 
 
 def workload_config(tokens, gpus):
-    return {"workload": "single-GPU decode MoE layer, large-MoE shape (BASELINE config 2)",
+    return {"workload": "single-GPU decode MoE layer, large-MoE shape (BASELINE config 2)" if gpus == 1 else
+            f"decode MoE layer, large-MoE shape (BASELINE config 2 layer), expert parallel over {gpus} GPUs",
             "hidden": 4096, "inter": 1024, "experts": 512, "topk": 10, "shared_experts": 1,
             "tokens_per_gpu": tokens, "weights": "NVFP4 (E2M1 + E4M3 per-16 + fp32 global), N(0,0.02), seed 0",
             "parallelism": "single GPU" if gpus == 1 else f"{gpus} independent replicas",
@@ -179,6 +185,13 @@ def run_ours(args):
     import sm120_moe_bench_b200 as vm
     from sm120_moe_bench_b200 import ops, synth
     from sm120_moe_bench_b200.verdict_moe import VerdictMoEMonolithic
+
+    if world > 1:
+        return run_expert_parallel(args, world, rank, local, dev)
+    if args.workload == "prefill":
+        return run_prefill(args, dev)
+    if args.workload == "stack":
+        return run_stack(args, dev)
 
     cfg = synth.CONFIG_LARGE
     M = args.tokens
@@ -326,6 +339,258 @@ def run_ours(args):
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+NOMINAL_FP4_TFLOPS = 9000.0     # dense FP4, B200 data sheet; no measured FP4 figure is provided
+
+
+def run_prefill(args, dev):
+    """BASELINE config 3: 8192 tokens through the same layer on one GPU; FP4 TFLOP/s of the whole layer
+    (2 * M * (T + 1) * 3 * K * N flops) and of the two grouped GEMMs, event-timed."""
+    import torch
+
+    import sm120_moe_bench_b200 as vm
+    from sm120_moe_bench_b200 import ops, synth
+    cfg = synth.CONFIG_LARGE
+    M = args.tokens if args.tokens != 64 else 8192
+    layer = synth.make_layer(cfg, seed=0, device=dev)
+    routed = ops.MoEWeights(*layer["routed"]).prepare()
+    shared = ops.MoEWeights(*layer["shared"]).prepare()
+    ws = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, M, has_shared=True, path=2), dev)
+    sets = [synth.make_inputs(cfg, M, seed=i, device=dev, zipf_s=args.zipf) for i in range(2)]
+    out = torch.empty(M, cfg.hidden, dtype=torch.bfloat16, device=dev)
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    for i in range(args.warmup):
+        vm.fused_moe(sets[i % 2][0], routed, ws, router_logits=sets[i % 2][1], shared=shared, out=out)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        vm.fused_moe(sets[i % 2][0], routed, ws, router_logits=sets[i % 2][1], shared=shared, out=out)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    stage_ms = {"gate_up": 0.0, "down": 0.0}
+    for i in range(min(args.steps, 10)):
+        ids = ws.view("topk_ids", torch.int32, M * cfg.topk).view(M, cfg.topk).clone()
+        w = ws.view("topk_weights", torch.float32, M * cfg.topk).view(M, cfg.topk).clone()
+        vm.build_tables(ws, ids, w)
+        for name in ("gate_up", "down"):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); ops.run_stage(name, ws, routed, shared, M); b.record(); b.synchronize()
+            stage_ms[name] += a.elapsed_time(b) / min(args.steps, 10)
+    clocks = sampler.stop()
+    K, N, T = cfg.hidden, cfg.inter, cfg.topk
+    flops = 2.0 * M * (T + 1) * 3 * K * N
+    gu_flops, dn_flops = flops * 2 / 3, flops / 3
+    peak_hbm, kind = measured_peak_gbs()
+    bytes_alg = (cfg.num_experts + 1) * routed.nbytes_per_expert() + M * K * 4
+    line = {"metric": "moe_layer_prefill_fp4_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "nvfp4(w4a4)->f32", "data": "synthetic",
+            "config": {"workload": "single-GPU prefill MoE layer (BASELINE config 3)", "tokens": M, "zipf_s": args.zipf,
+                       "hidden": K, "inter": N, "experts": cfg.num_experts, "topk": T, "shared_experts": 1},
+            "tokens_per_s": M / (ms * 1e-3),
+            "roofline": {"bound": "tensor", "kernel": "tc_gemm_kernel<2,1,64> (gate_up, tcgen05)",
+                         "achieved": gu_flops / (stage_ms["gate_up"] * 1e-3) / 1e12, "peak": NOMINAL_FP4_TFLOPS,
+                         "peak_source": "nominal dense FP4 (no measured FP4 peak available)", "unit": "TFLOP/s",
+                         "frac": gu_flops / (stage_ms["gate_up"] * 1e-3) / 1e12 / NOMINAL_FP4_TFLOPS, "traffic": None,
+                         "us_per_launch": stage_ms["gate_up"] * 1e3,
+                         "down_kernel": {"achieved": dn_flops / (stage_ms["down"] * 1e-3) / 1e12,
+                                         "us_per_launch": stage_ms["down"] * 1e3},
+                         "layer_hbm": {"algorithmic_bytes": bytes_alg, "achieved_gbs": bytes_alg / (ms * 1e-3) / 1e9,
+                                       "frac_of_hbm_peak": bytes_alg / (ms * 1e-3) / 1e9 / peak_hbm, "peak_source": kind}},
+            "clocks": clocks, "device_status": ws.status()}
+    print(json.dumps(line), flush=True)
+
+
+def run_stack(args, dev):
+    """BASELINE config 5 shape on one GPU: ``--layers`` consecutive layers with independent seeded weights,
+    ``x <- x + moe(x)``, decode batch ``--tokens`` (default 32), replayed from one CUDA graph.  Reports the
+    latency of one pass (= per-token latency of the stack) and tokens/s."""
+    import torch
+
+    import sm120_moe_bench_b200 as vm
+    from sm120_moe_bench_b200 import ops, synth
+    cfg = synth.CONFIG_LARGE
+    M = args.tokens if args.tokens != 64 else 32
+    L = args.layers
+    layers = []
+    for li in range(L):
+        lay = synth.make_layer(cfg, seed=li, device=dev)
+        layers.append((ops.MoEWeights(*lay["routed"]).prepare(), ops.MoEWeights(*lay["shared"]).prepare()))
+    ws = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, M, has_shared=True, path=2), dev)
+    x0, _ = synth.make_inputs(cfg, M, seed=0, device=dev)
+    logits = [synth.make_inputs(cfg, M, seed=1000 + li, device=dev)[1] for li in range(L)]
+    x = x0.clone()
+    y = torch.empty_like(x)
+
+    def one_pass():
+        x.copy_(x0)
+        for li in range(L):
+            vm.fused_moe(x, layers[li][0], ws, router_logits=logits[li], shared=layers[li][1], out=y)
+            x.add_(y)                                   # residual
+
+    one_pass()                                          # warm: tensor maps, attributes
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        one_pass()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            one_pass()
+    torch.cuda.synchronize()
+    eager_ref = x.clone()
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    for _ in range(args.warmup):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms_graph = e0.elapsed_time(e1) / args.steps
+    same = bool(torch.equal(x, eager_ref))
+    e0.record()
+    for _ in range(args.steps):
+        one_pass()
+    e1.record()
+    torch.cuda.synchronize()
+    ms_eager = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop()
+    line = {"metric": "moe_stack_latency_ms", "value": ms_graph, "unit": "ms per pass (per-token latency)", "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_graph, "higher_is_better": False,
+            "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4(w4a4)->f32", "data": "synthetic",
+            "config": {"workload": "stack of MoE layers, config-2 shape, residual add, one CUDA graph (BASELINE config 5 on one GPU)",
+                       "layers": L, "tokens": M},
+            "us_per_layer": ms_graph * 1e3 / L, "tokens_per_s": M / (ms_graph * 1e-3),
+            "eager_ms_per_pass": ms_eager, "graph_equals_eager": same, "clocks": clocks, "device_status": ws.status()}
+    print(json.dumps(line), flush=True)
+
+
+def run_expert_parallel(args, world, rank, local, dev):
+    """N > 1: the same layer with its 512 experts split evenly over the ranks (64 per GPU at N = 8),
+    every rank bringing ``--tokens`` tokens of its own (weak scaling); dispatch and combine run as
+    peer-memory kernels over NVLink, NCCL is only used for set-up and for the timing barriers."""
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from sm120_moe_bench_b200 import ep, ops, synth
+
+    cfg = synth.CONFIG_LARGE
+    M = args.tokens
+    layer = synth.make_layer(cfg, seed=0, device=dev)              # identical on every rank (same seed)
+    first, per = ep.expert_partition(cfg.num_experts, world, rank)
+    mine = ops.MoEWeights(*[t[first:first + per].contiguous() for t in layer["routed"]]).prepare()
+    shared = ops.MoEWeights(*layer["shared"]).prepare()
+    del layer
+    torch.cuda.empty_cache()
+    moe = ep.ExpertParallelMoE(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, mine, shared, max_local_tokens=max(M, 1))
+    sets = [synth.make_inputs(cfg, M, seed=100 * rank + i, device=dev) for i in range(max(args.rotate, 1))]
+    out = torch.empty(M, cfg.hidden, dtype=torch.bfloat16, device=dev)
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    # untimed: how many distinct local experts each input set touches on this rank, and the NVLink rows
+    from sm120_moe_bench_b200 import route as dev_route
+    local_experts, remote_pairs = [], []
+    for h, l in sets:
+        ids, _ = dev_route(l, cfg.topk)
+        gathered = [torch.empty_like(ids) for _ in range(world)]
+        dist.all_gather(gathered, ids)
+        allids = torch.cat(gathered).flatten()
+        mine_mask = (allids >= first) & (allids < first + per)
+        local_experts.append(int(torch.unique(allids[mine_mask]).numel()) + 1)
+        remote_pairs.append(int(((ids.flatten() < first) | (ids.flatten() >= first + per)).sum()))
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    for i in range(args.warmup):
+        moe.forward(*sets[i % len(sets)], out=out)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        moe.forward(*sets[i % len(sets)], out=out)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    status = moe.status()
+
+    host_sets = [(h.cpu().pin_memory(), l.cpu().pin_memory()) for h, l in sets]
+    host_out = torch.empty(M, cfg.hidden, dtype=torch.bfloat16).pin_memory()
+    h_dev = torch.empty(M, cfg.hidden, dtype=torch.bfloat16, device=dev)
+    l_dev = torch.empty(M, cfg.num_experts, dtype=torch.float32, device=dev)
+
+    def e2e_step(i):
+        hh, lh = host_sets[i % len(host_sets)]
+        h_dev.copy_(hh, non_blocking=True)
+        l_dev.copy_(lh, non_blocking=True)
+        moe.forward(h_dev, l_dev, out=out)
+        host_out.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(args.warmup):
+        e2e_step(i)
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for i in range(args.steps):
+        e2e_step(i)
+    f1.record()
+    barrier()
+    e2e_ms = f0.elapsed_time(f1)
+    clocks = sampler.stop() if rank == 0 else None
+
+    K, N = cfg.hidden, cfg.inter
+    per_expert = mine.nbytes_per_expert()
+    my_bytes = float(np.mean(local_experts)) * per_expert
+    nv_bytes = float(np.mean(remote_pairs)) * (K // 2 + K // 16 + 16 + K * 4)
+    t = torch.tensor([ms, e2e_ms, -my_bytes, -nv_bytes], device=dev, dtype=torch.float64)
+    tmax = t.clone(); dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+    tsum = t.clone(); dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+    ms, e2e_ms = tmax[0].item(), tmax[1].item()
+    total_bytes, total_nv = -tsum[2].item(), -tsum[3].item()
+    st = torch.tensor([status], device=dev); dist.all_reduce(st, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        peak, peak_kind = measured_peak_gbs()
+        step_s = ms / args.steps * 1e-3
+        tokens_total = M * world * args.steps
+        config = workload_config(M, world)
+        config["parallelism"] = f"expert parallel over {world} GPUs ({per} routed experts per GPU, shared expert replicated), dispatch/combine as NVLink peer-memory kernels"
+        config["kernel_path"] = "tc"
+        line = {
+            "metric": METRIC, "value": tokens_total / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4(w4a4)->f32",
+            "data": "synthetic", "config": config,
+            "roofline": {"bound": "hbm", "kernel": "expert-parallel layer (all kernels of one step, per GPU)",
+                         "achieved": total_bytes / world / step_s / 1e9, "peak": peak, "unit": "GB/s",
+                         "frac": total_bytes / world / step_s / 1e9 / peak, "traffic": None,
+                         "peak_source": peak_kind, "algorithmic_bytes_per_step_all_gpus": total_bytes,
+                         "nvlink_bytes_per_step_all_gpus": total_nv,
+                         "nvlink_gbs_per_gpu": total_nv / world / step_s / 1e9},
+            "clocks": clocks,
+            "e2e": {"value": tokens_total / (e2e_ms * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": M * (cfg.hidden * 2 + cfg.num_experts * 4) * world,
+                    "d2h_bytes_per_step": M * cfg.hidden * 2 * world, "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": 13 * args.steps * world,   # route, plan, dispatch, gather, tables, permute, gate_up, down, signal, combine (+3 when tables run as phases)
+            "device_status": int(st.item()),
+        }
+        print(json.dumps(line), flush=True)
+    barrier()
+    moe.close()
+    dist.destroy_process_group()
 
 
 def main():
