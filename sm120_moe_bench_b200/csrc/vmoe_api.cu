@@ -14,9 +14,13 @@ int max_units(const vmoe_shape* s) {
 }
 
 // Units carry at most 16 tokens while the batch averages <= 4 tokens per expert (memory-bound:
-// a small token tile leaves shared memory for a deeper weight ring), else 64.
+// a small token tile leaves shared memory for a deeper weight ring), 128 from 32 tokens per expert
+// on (token-major tiles, compute-bound), else 64.
 int tc_unit_cap(const vmoe_shape& s, int M) {
-    return ((long long)M * s.topk <= 4LL * s.num_experts) ? TC_UNIT_TOK_SMALL : TC_UNIT_TOK;
+    const long long pairs = (long long)M * s.topk;
+    if (pairs <= 4LL * s.num_experts) return TC_UNIT_TOK_SMALL;
+    if (pairs >= 32LL * s.num_experts) return TC_UNIT_TOK_PREFILL;
+    return TC_UNIT_TOK;
 }
 
 int max_tc_units(const vmoe_shape* s) {

@@ -14,7 +14,7 @@
 // Math follows fused-moe/csrc/verdict_fused_cooperative_tma_ext.cu:323-538 of the reference.
 // Warp roles per persistent CTA: warp 0 = TMA / bulk-copy producer, warp 1 = MMA issuer and TMEM
 // owner, warps 2-5 = epilogue (one TMEM lane quadrant each).  Every wait is bounded.
-#include "vmoe_common.cuh"
+#include "vmoe_tc_common.cuh"
 
 #include <string.h>
 
@@ -25,16 +25,6 @@
 #include <cudaTypedefs.h>
 
 namespace vmoe {
-
-constexpr int TC_THREADS = 192;
-constexpr int TC_ROWS = 128;                 // weight rows per tile (UMMA M)
-constexpr int TC_KB_BYTES = 128;             // bytes of K per row per stage = 256 E2M1 elements
-constexpr int TC_A_TILE = TC_ROWS * TC_KB_BYTES;            // 16 KiB
-constexpr int TC_SF_TILE = 4 * 512;                         // four 128-row x 4-scale atoms
-constexpr int TC_TMEM_COLS = 512;
-constexpr int TC_SF_COL0 = 256;              // first TMEM column of the scale-factor area
-
-constexpr int TC_SMEM_BUDGET = 227 * 1024 - 3 * 1024;     // dynamic shared memory minus control block and alignment slack
 
 // NA = weight matrices per item (2: gate + up, 1: down); KS = 128-byte k-blocks per stage; UT = tokens
 // per unit (UMMA N <= UT).  A stage holds NA*KS weight tiles, KS token tiles and their scale atoms.
@@ -53,17 +43,6 @@ template <int NA, int KS, int UT> struct TcCfg {
     static_assert(TC_SF_COL0 + 2 * SF_COLS <= TC_TMEM_COLS, "scale columns do not fit");
 };
 
-struct TcStageInfo { int expert, slot0, ntok, nbox, tile, unit, kb, last; };   // kb = step index within the item
-
-struct TcShared {
-    uint64_t full[12], empty[12];
-    uint64_t tmem_full[4], tmem_empty[4];
-    TcStageInfo info[12];
-    TcStageInfo epi[4];
-    uint32_t tmem_base;
-    int abort_flag;
-};
-
 struct TcParams {
     CUtensorMap map_a_routed, map_a_shared;    // weights [rows, K/2] bytes, box 128 x 128, swizzle 128B
     CUtensorMap map_b[4];                      // activations [slots, K/2] bytes, box 128 x {8,16,32,64}
@@ -79,65 +58,6 @@ struct TcParams {
     int tiles;        // items per unit
     int queue;        // counter index of the work queue
 };
-
-// ---------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t sdesc) {
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
-__device__ __forceinline__ void tc_mma(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                       uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
-    asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-        " tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n}\n"
-        ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb) : "memory");
-}
-__device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t (&r)[8]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// shared-memory matrix descriptors (sm_100 format: version 1 in bits 46-47)
-__device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
-    // K-major, 128-byte swizzle: rows are 128 bytes apart, 8-row groups 1024 bytes apart
-    return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
-           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-__device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
-    // no swizzle: 32 rows of 16 bytes, 8-row groups 128 bytes apart
-    return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
-}
-// the same descriptors as (low word = start address >> 4 | LBO << 16, constant high word)
-constexpr uint32_t DESC_SW128_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
-constexpr uint32_t DESC_SF_HI = (128u >> 4) | (1u << 14);
-constexpr uint32_t DESC_SW128_LBO = 1u << 16;
-__device__ __forceinline__ uint64_t make_desc(uint32_t addr16, uint32_t hi) {
-    uint64_t d;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(addr16), "r"(hi));
-    return d;
-}
-__device__ __forceinline__ uint32_t idesc_nvf4(int n) {
-    // a/b format E2M1 (1), K-major both, N >> 3, scale format UE4M3 (0), M = 128 (>> 4), K = 64
-    return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_ROWS >> 4) << 24);
-}
-
-__device__ __forceinline__ void tc_timeout(const Workspace& ws, TcShared* sh) {
-    atomicExch(&ws.counters[CNT_STATUS], VMOE_ERR_TIMEOUT);
-    atomicExch(&sh->abort_flag, 1);
-}
 
 // ---------------------------------------------------------------------------------
 // The kernel.  NA = 2: gate_up (A0 = gate rows, A1 = up rows of the same 128-n tile);
@@ -451,7 +371,7 @@ prep_sf_kernel(const uint8_t* __restrict__ sf, long long rows, int K, uint8_t* _
 // ---------------------------------------------------------------------------------
 static PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
 
-static int get_encoder() {
+int get_encoder() {
     if (g_encode) return VMOE_OK;
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult q;
@@ -468,7 +388,7 @@ struct MapEntry { MapKey key; CUtensorMap map; };
 static std::mutex g_map_mutex;
 static std::vector<MapEntry> g_map_cache;
 
-static int make_map(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows) {
+int make_map(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows) {
     int dev = 0;
     cudaGetDevice(&dev);
     std::lock_guard<std::mutex> lock(g_map_mutex);
@@ -490,7 +410,7 @@ static int make_map(CUtensorMap* map, const void* base, uint64_t row_bytes, uint
     return VMOE_OK;
 }
 
-static int tc_sm_count() {
+int tc_sm_count() {
     static int n = 0;
     if (n == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev); if (n <= 0) n = 148; }
     return n;
@@ -559,15 +479,19 @@ static int launch_tc(const vmoe_shape& s, const WeightSet& routed, const WeightS
 int launch_tc_gate_up(const vmoe_shape& s, const WeightSet& routed, const WeightSet& shared, const PreparedSet& prep,
                       int M, const Workspace& ws, cudaStream_t st, int unit_cap, long long b_rows) {
     if (M == 0) return VMOE_OK;
-    const bool small = (unit_cap > 0 ? unit_cap : tc_unit_cap(s, M)) == TC_UNIT_TOK_SMALL;
+    const int cap = unit_cap > 0 ? unit_cap : tc_unit_cap(s, M);
+    if (cap == TC_UNIT_TOK_PREFILL) return launch_pf_gate_up(s, routed, shared, prep, M, ws, st, b_rows);
+    const bool small = cap == TC_UNIT_TOK_SMALL;
     return small ? launch_tc<2, 1, TC_UNIT_TOK_SMALL>(s, routed, shared, prep, M, ws, st, b_rows)
                  : launch_tc<2, 1, TC_UNIT_TOK>(s, routed, shared, prep, M, ws, st, b_rows);
 }
 int launch_tc_down(const vmoe_shape& s, const WeightSet& routed, const WeightSet& shared, const PreparedSet& prep,
                    int M, const Workspace& ws, cudaStream_t st, int unit_cap, long long b_rows) {
     if (M == 0) return VMOE_OK;
+    const int cap = unit_cap > 0 ? unit_cap : tc_unit_cap(s, M);
+    if (cap == TC_UNIT_TOK_PREFILL) return launch_pf_down(s, routed, shared, prep, M, ws, st, b_rows);
     // two k-blocks per stage when the reduction length allows: half as many ring round trips per byte
-    const bool small = (unit_cap > 0 ? unit_cap : tc_unit_cap(s, M)) == TC_UNIT_TOK_SMALL;
+    const bool small = cap == TC_UNIT_TOK_SMALL;
     if ((s.inter / 256) % 2 == 0)
         return small ? launch_tc<1, 2, TC_UNIT_TOK_SMALL>(s, routed, shared, prep, M, ws, st, b_rows)
                      : launch_tc<1, 2, TC_UNIT_TOK>(s, routed, shared, prep, M, ws, st, b_rows);

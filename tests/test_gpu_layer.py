@@ -118,7 +118,7 @@ def test_config_tiny(vm, path):
 
 
 @pytest.mark.parametrize("path", PATHS)
-@pytest.mark.parametrize("M", [1, 3, 16, 50, 150])
+@pytest.mark.parametrize("M", [1, 3, 16, 50, 150, 300])
 def test_small_shapes_with_shared(vm, M, path):
     from sm120_moe_bench_b200 import synth
     cfg = synth.LayerConfig("mid", 512, 256, 12, 3, True)
@@ -186,6 +186,32 @@ def test_config_large_bs64_properties(vm, large_layer, path):
         o = vm.fused_moe(hid_d[m:m + 1].contiguous(), routed, ws, router_logits=log_d[m:m + 1].contiguous(), shared=shared)
         assert torch.equal(o[0], out1[m])
     assert torch.isfinite(out1.float()).all() and out1.float().abs().max() > 0
+
+
+def test_config_large_prefill_properties(vm, large_layer):
+    """BASELINE config 3 at full size (8192 tokens, token-major tcgen05 tiles), through size-independent
+    properties: run-twice determinism, and single rows against batch-1 runs of the same tokens (different
+    kernels, so within the layer tolerance rather than bit for bit), uniform and Zipf-skewed routing."""
+    from sm120_moe_bench_b200 import synth
+    from tests import util
+    cfg = synth.CONFIG_LARGE
+    routed, shared = _device_layer(vm, large_layer)
+    M = 8192
+    ws = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, M, has_shared=True, path=TC))
+    ws1 = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, 1, has_shared=True, path=TC))
+    for zipf in (None, 1.2):
+        hidden, logits = synth.make_inputs(cfg, M, seed=3, device="cuda", zipf_s=zipf)
+        out1 = vm.fused_moe(hidden, routed, ws, router_logits=logits, shared=shared).clone()
+        out2 = vm.fused_moe(hidden, routed, ws, router_logits=logits, shared=shared)
+        torch.cuda.synchronize()
+        assert ws.status() == 0
+        assert torch.equal(out1, out2)
+        assert torch.isfinite(out1.float()).all()
+        t = ws.tables(M)
+        assert t["num_slots"] == M * (cfg.topk + 1)
+        for m in (0, 4097, 8191):
+            o = vm.fused_moe(hidden[m:m + 1].contiguous(), routed, ws1, router_logits=logits[m:m + 1].contiguous(), shared=shared)
+            util.assert_output_close(out1[m].float().cpu().numpy(), o[0].float().cpu().numpy())
 
 
 def test_expert_parallel_halves_sum_to_whole(vm):
