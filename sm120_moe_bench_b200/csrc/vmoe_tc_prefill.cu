@@ -2,43 +2,47 @@
 //
 // When an expert receives many tokens (>= 32 on average) the operand roles are the usual ones: the
 // 128 UMMA rows are TOKENS (A operand: 128 consecutive sorted slots of one expert), the UMMA N
-// dimension holds weight rows (B operand).  A thread of the epilogue then owns one token row, so the
-// SiLU * up product, the 16-wide amax, the E4M3 scale and the E2M1 pack of a scale block are
-// register-local (no shuffles) and each block leaves as one 8-byte store.
+// dimension holds 256 weight rows (B operand), so one tcgen05.mma does 128 x 256 x 64 MACs and its
+// fixed issue cost is amortised.  A thread of the epilogue owns one token row, so the SiLU * up
+// product, the 16-wide amax, the E4M3 scale and the E2M1 pack of a scale block are register-local
+// (no shuffles) and each block leaves as one 8-byte store.
 //
-//   pf_kernel<1> gate_up: B = 64 gate rows + 64 up rows of the same n range, two N = 64 MMAs per
-//                k-step into columns [0, 64) (gate) and [64, 128) (up) of the accumulator; the
-//                scale atoms are the standard 128-row atoms of the weight matrix, the odd 64-row
-//                half is addressed by a two-column offset in TMEM.
-//   pf_kernel<0> down:    B = 128 rows of w2, one N = 128 MMA per k-step; the epilogue scales by
-//                (router weight x alpha2) and stores 128 consecutive floats per token.
+//   pf_kernel<1> gate_up: B = 128 gate rows + 128 up rows of the same n range; accumulator columns
+//                [0, 128) = gate, [128, 256) = up.
+//   pf_kernel<0> down:    B = 256 rows of w2; the epilogue scales by (router weight x alpha2) and
+//                stores 256 consecutive floats per token.
+// The scale atoms are the standard 128-row atoms of the weight matrices: two per k-step, copied to
+// eight consecutive TMEM columns.  The 256-column accumulator is single-buffered (the other half of
+// TMEM holds the scale columns), so eight epilogue warps (two per TMEM lane quadrant) drain it.
 //
 // Same math as fused-moe/csrc/verdict_fused_cooperative_tma_ext.cu:323-538 of the reference; the
 // reference has no large-batch kernel (it loops token by token above 4 tokens,
-// fused-moe/verdict_moe.py:670-713).  Same warp roles, ring, bounded waits and TMEM ownership as
-// the decode kernel in vmoe_tc.cu.
+// fused-moe/verdict_moe.py:670-713).  Same ring, bounded waits and TMEM ownership as the decode
+// kernel in vmoe_tc.cu.
 #include "vmoe_tc_common.cuh"
 
 #include <string.h>
 
 namespace vmoe {
 
+constexpr int PF_THREADS = 320;              // producer warp, MMA warp, 8 epilogue warps
+constexpr int PF_N = 256;                    // weight rows per item (UMMA N)
+
 template <int GU> struct PfCfg {
-    static constexpr int B_BYTES = TC_A_TILE;                        // 128 weight rows x 128 B (2 x 64 for gate_up)
-    static constexpr int SFB_BYTES = GU ? 2 * TC_SF_TILE : TC_SF_TILE;
+    static constexpr int B_BYTES = PF_N * TC_KB_BYTES;               // 256 weight rows x 128 B
+    static constexpr int SFB_BYTES = 2 * TC_SF_TILE;                 // two 128-row atom sets
     static constexpr int STAGE_BYTES = TC_A_TILE + B_BYTES + TC_SF_TILE + SFB_BYTES;
-    static constexpr int STAGES = TC_SMEM_BUDGET / STAGE_BYTES;     // 5 (gate_up) / 6 (down)
+    static constexpr int STAGES = TC_SMEM_BUDGET / STAGE_BYTES;     // 4
     static constexpr int OFF_B = TC_A_TILE;
     static constexpr int OFF_SFA = OFF_B + B_BYTES;
     static constexpr int OFF_SFB = OFF_SFA + TC_SF_TILE;
-    static constexpr int SF_COLS = 16 + (GU ? 32 : 16);
-    static constexpr int ACC_STRIDE = 128;
-    static constexpr int NBUF = 2;
+    static constexpr int SF_COLS = 16 + 32;
+    static constexpr int NBUF = 1;
 };
 
 struct PfParams {
     CUtensorMap map_tok;                         // sorted-slot token rows [S, K/2], box 128 rows
-    CUtensorMap map_w_routed, map_w_shared;      // weights [rows, K/2], box 64 rows (gate_up) / 128 rows (down)
+    CUtensorMap map_w_routed, map_w_shared;      // weights [rows, K/2], box 128 rows
     const uint8_t* sf_tok;                       // per-unit token scale atoms [unit][K/64][512]
     const uint8_t* sfw_routed; const uint8_t* sfw_shared;   // weight scale atoms [rows/128][K/64][512]
     const float* gs_routed; const float* gs_shared;
@@ -55,7 +59,7 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 
 template <int GU>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(PF_THREADS, 1)
 pf_kernel(const __grid_constant__ PfParams p) {
     using Cfg = PfCfg<GU>;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -65,7 +69,7 @@ pf_kernel(const __grid_constant__ PfParams p) {
 
     if (tid == 0) {
         for (int i = 0; i < Cfg::STAGES; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], 1); }
-        for (int i = 0; i < Cfg::NBUF; ++i) { mbar_init(&sh->tmem_full[i], 2); mbar_init(&sh->tmem_empty[i], 4); }
+        for (int i = 0; i < Cfg::NBUF; ++i) { mbar_init(&sh->tmem_full[i], 2); mbar_init(&sh->tmem_empty[i], 8); }
         sh->abort_flag = 0;
         mbar_fence_init();
     }
@@ -101,16 +105,11 @@ pf_kernel(const __grid_constant__ PfParams p) {
                 const int e = shd ? 0 : u.x;
                 const CUtensorMap* mw = shd ? &p.map_w_shared : &p.map_w_routed;
                 const uint8_t* sfw = shd ? p.sfw_shared : p.sfw_routed;
-                // weight rows of this item and the 128-row scale tiles they belong to
-                long long row0, row1 = 0, sft0, sft1 = 0;
-                if (GU) {
-                    row0 = (long long)e * 2 * p.N + tile * 64;             // gate rows
-                    row1 = row0 + p.N;                                      // up rows
-                    sft0 = row0 / TC_ROWS; sft1 = row1 / TC_ROWS;
-                } else {
-                    row0 = (long long)e * p.hidden + tile * TC_ROWS;
-                    sft0 = row0 / TC_ROWS;
-                }
+                // the two 128-row weight tiles of this item and their scale tiles
+                long long row0, row1;
+                if (GU) { row0 = (long long)e * 2 * p.N + tile * TC_ROWS; row1 = row0 + p.N; }       // gate rows, up rows
+                else    { row0 = (long long)e * p.hidden + tile * PF_N;   row1 = row0 + TC_ROWS; }
+                const long long sft0 = row0 / TC_ROWS, sft1 = row1 / TC_ROWS;
                 for (int kb = 0; kb < kblocks; ++kb) {
                     const int slot = g % Cfg::STAGES;
                     if (g >= (uint32_t)Cfg::STAGES && !mbar_wait(&sh->empty[slot], ((g / Cfg::STAGES) - 1) & 1)) { ok = false; break; }
@@ -120,15 +119,10 @@ pf_kernel(const __grid_constant__ PfParams p) {
                     mbar_arrive_expect_tx(&sh->full[slot], Cfg::STAGE_BYTES);
                     tma_load_2d(st, &p.map_tok, kb * TC_KB_BYTES, u.y, &sh->full[slot]);
                     bulk_g2s(st + Cfg::OFF_SFA, p.sf_tok + ((size_t)unit * atoms_k + (size_t)kb * 4) * 512, TC_SF_TILE, &sh->full[slot]);
-                    if (GU) {
-                        tma_load_2d(st + Cfg::OFF_B, mw, kb * TC_KB_BYTES, (int)row0, &sh->full[slot]);
-                        tma_load_2d(st + Cfg::OFF_B + 64 * TC_KB_BYTES, mw, kb * TC_KB_BYTES, (int)row1, &sh->full[slot]);
-                        bulk_g2s(st + Cfg::OFF_SFB, sfw + ((size_t)sft0 * atoms_k + (size_t)kb * 4) * 512, TC_SF_TILE, &sh->full[slot]);
-                        bulk_g2s(st + Cfg::OFF_SFB + TC_SF_TILE, sfw + ((size_t)sft1 * atoms_k + (size_t)kb * 4) * 512, TC_SF_TILE, &sh->full[slot]);
-                    } else {
-                        tma_load_2d(st + Cfg::OFF_B, mw, kb * TC_KB_BYTES, (int)row0, &sh->full[slot]);
-                        bulk_g2s(st + Cfg::OFF_SFB, sfw + ((size_t)sft0 * atoms_k + (size_t)kb * 4) * 512, TC_SF_TILE, &sh->full[slot]);
-                    }
+                    tma_load_2d(st + Cfg::OFF_B, mw, kb * TC_KB_BYTES, (int)row0, &sh->full[slot]);
+                    tma_load_2d(st + Cfg::OFF_B + TC_A_TILE, mw, kb * TC_KB_BYTES, (int)row1, &sh->full[slot]);
+                    bulk_g2s(st + Cfg::OFF_SFB, sfw + ((size_t)sft0 * atoms_k + (size_t)kb * 4) * 512, TC_SF_TILE, &sh->full[slot]);
+                    bulk_g2s(st + Cfg::OFF_SFB + TC_SF_TILE, sfw + ((size_t)sft1 * atoms_k + (size_t)kb * 4) * 512, TC_SF_TILE, &sh->full[slot]);
                     ++g;
                 }
             }
@@ -146,10 +140,10 @@ pf_kernel(const __grid_constant__ PfParams p) {
         if (lane == 0) {
             uint32_t g = 0, it = 0;
             const uint32_t smem16 = smem_u32(smem) >> 4;
-            const uint32_t idesc = idesc_nvf4(GU ? 64 : 128);
+            const uint32_t idesc = idesc_nvf4(PF_N);
             bool ok = true;
             while (ok) {
-                const int buf = it % Cfg::NBUF;
+                const int buf = 0;
                 bool first = true, end = false;
                 while (true) {
                     const int slot = g % Cfg::STAGES;
@@ -157,7 +151,8 @@ pf_kernel(const __grid_constant__ PfParams p) {
                     tc_fence_after();
                     const TcStageInfo inf = sh->info[slot];
                     if (first) {
-                        if (it >= (uint32_t)Cfg::NBUF && !mbar_wait(&sh->tmem_empty[buf], ((it / Cfg::NBUF) - 1) & 1)) { ok = false; break; }
+                        // single accumulator: the epilogue of the previous item must have drained it
+                        if (it >= 1 && !mbar_wait(&sh->tmem_empty[buf], (it - 1) & 1)) { ok = false; break; }
                         tc_fence_after();
                         first = false;
                     }
@@ -168,24 +163,15 @@ pf_kernel(const __grid_constant__ PfParams p) {
                     for (int j = 0; j < 4; ++j)      // token scales
                         tc_cp_sf(sfcol + j * 4, make_desc(st16 + ((Cfg::OFF_SFA + j * 512) >> 4), DESC_SF_HI));
 #pragma unroll
-                    for (int j = 0; j < (GU ? 8 : 4); ++j)   // weight scales: gate atoms, then up atoms
-                        tc_cp_sf(sfcol + 16 + j * 4, make_desc(st16 + ((Cfg::OFF_SFB + j * 512) >> 4), DESC_SF_HI));
-                    const uint32_t dcol = tmem + buf * Cfg::ACC_STRIDE;
-                    const uint32_t half = GU ? (uint32_t)(inf.tile & 1) * 2 : 0;   // odd 64-row half of the 128-row scale tile
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const uint64_t adesc = make_desc(st16 + ((j * 32) >> 4) + DESC_SW128_LBO, DESC_SW128_HI);
-                        const uint32_t acc = (inf.kb > 0 || j > 0) ? 1u : 0u;
-                        if (GU) {
-                            tc_mma(dcol, adesc, make_desc(st16 + ((Cfg::OFF_B + j * 32) >> 4) + DESC_SW128_LBO, DESC_SW128_HI),
-                                   idesc, sfcol + j * 4, sfcol + 16 + j * 4 + half, acc);
-                            tc_mma(dcol + 64, adesc, make_desc(st16 + ((Cfg::OFF_B + 64 * TC_KB_BYTES + j * 32) >> 4) + DESC_SW128_LBO, DESC_SW128_HI),
-                                   idesc, sfcol + j * 4, sfcol + 32 + j * 4 + half, acc);
-                        } else {
-                            tc_mma(dcol, adesc, make_desc(st16 + ((Cfg::OFF_B + j * 32) >> 4) + DESC_SW128_LBO, DESC_SW128_HI),
-                                   idesc, sfcol + j * 4, sfcol + 16 + j * 4, acc);
-                        }
+                    for (int j = 0; j < 4; ++j) {    // weight scales of k-step j: first tile -> columns +0..3, second -> +4..7
+                        tc_cp_sf(sfcol + 16 + j * 8, make_desc(st16 + ((Cfg::OFF_SFB + j * 512) >> 4), DESC_SF_HI));
+                        tc_cp_sf(sfcol + 16 + j * 8 + 4, make_desc(st16 + ((Cfg::OFF_SFB + TC_SF_TILE + j * 512) >> 4), DESC_SF_HI));
                     }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        tc_mma(tmem, make_desc(st16 + ((j * 32) >> 4) + DESC_SW128_LBO, DESC_SW128_HI),
+                               make_desc(st16 + ((Cfg::OFF_B + j * 32) >> 4) + DESC_SW128_LBO, DESC_SW128_HI),
+                               idesc, sfcol + j * 4, sfcol + 16 + j * 8, (inf.kb > 0 || j > 0) ? 1u : 0u);
                     tc_commit(&sh->empty[slot]);
                     ++g;
                     if (inf.last) { sh->epi[buf] = inf; break; }
@@ -204,27 +190,28 @@ pf_kernel(const __grid_constant__ PfParams p) {
             }
         }
     } else {
-        // ------------------------------------------------------------- epilogue: one token row per thread
+        // ------------------------------------------------------------- epilogue: one token row per thread,
+        // two warps per TMEM lane quadrant, each draining half of the 16-column chunks
         const int quad = warp & 3;
+        const int half = (warp - 2) >> 2;                   // 0: first half of the chunks, 1: second half
         const int t = quad * 32 + lane;                     // token row inside the unit
         uint32_t it = 0;
         while (true) {
-            const int buf = it % Cfg::NBUF;
-            if (!mbar_wait(&sh->tmem_full[buf], (it / Cfg::NBUF) & 1)) { if (lane == 0) tc_timeout(p.ws, sh); break; }
+            if (!mbar_wait(&sh->tmem_full[0], it & 1)) { if (lane == 0) tc_timeout(p.ws, sh); break; }
             tc_fence_after();
-            const TcStageInfo inf = sh->epi[buf];
+            const TcStageInfo inf = sh->epi[0];
             if (inf.expert < 0) break;
             const bool shd = inf.expert >= p.E;
             const float alpha = shd ? p.gs_shared[0] : p.gs_routed[inf.expert];
-            const uint32_t tacc = tmem + ((uint32_t)(quad * 32) << 16) + buf * Cfg::ACC_STRIDE;
+            const uint32_t tacc = tmem + ((uint32_t)(quad * 32) << 16);
             const bool valid = t < inf.ntok;
             const size_t srow = (size_t)(inf.slot0 + (valid ? t : 0));
             if (GU) {
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {                // four scale blocks of 16 n
+                for (int c = half * 4; c < half * 4 + 4; ++c) {     // scale blocks of 16 n; 8 per item
                     uint32_t gr[16], ur[16];
                     tc_ld16(tacc + c * 16, gr);
-                    tc_ld16(tacc + 64 + c * 16, ur);
+                    tc_ld16(tacc + TC_ROWS + c * 16, ur);
                     tc_ld_wait();
                     float sw[16];
                     float gm = 0.f;
@@ -243,17 +230,17 @@ pf_kernel(const __grid_constant__ PfParams p) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) hi |= e2m1_encode(sw[8 + i] / sc) << (4 * i);
                     if (valid) {
-                        const int n0 = inf.tile * 64 + c * 16;
+                        const int n0 = inf.tile * TC_ROWS + c * 16;
                         *reinterpret_cast<uint2*>(p.ws.inter_q + srow * (p.N / 2) + n0 / 2) = make_uint2(lo, hi);
                         p.ws.inter_sf[srow * (p.N / 16) + (n0 >> 4)] = sb;
-                        p.ws.inter_sf_atoms[((size_t)inf.unit * (p.N / 64) + inf.tile) * 512 + (t & 31) * 16 + (t >> 5) * 4 + c] = sb;
+                        p.ws.inter_sf_atoms[((size_t)inf.unit * (p.N / 64) + (n0 >> 6)) * 512 + (t & 31) * 16 + (t >> 5) * 4 + ((n0 >> 4) & 3)] = sb;
                     }
                 }
             } else {
                 const float scale = valid ? p.ws.scatter_weights[srow] * alpha : 0.f;
-                float* orow = (p.ws.row_dst ? p.ws.row_dst[srow] : p.ws.pair_out + srow * p.hidden) + inf.tile * TC_ROWS;
+                float* orow = (p.ws.row_dst ? p.ws.row_dst[srow] : p.ws.pair_out + srow * p.hidden) + inf.tile * PF_N;
 #pragma unroll 1
-                for (int c = 0; c < 8; ++c) {
+                for (int c = half * 8; c < half * 8 + 8; ++c) {
                     uint32_t yr[16];
                     tc_ld16(tacc + c * 16, yr);
                     tc_ld_wait();
@@ -268,7 +255,7 @@ pf_kernel(const __grid_constant__ PfParams p) {
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&sh->tmem_empty[buf]);
+            if (lane == 0) mbar_arrive(&sh->tmem_empty[0]);
             ++it;
         }
     }
@@ -292,7 +279,7 @@ static int launch_pf(const vmoe_shape& s, const WeightSet& routed, const WeightS
     const int rows = GU ? 2 * s.inter : s.hidden;
     const long long S = b_rows >= 0 ? b_rows : (long long)s.max_tokens * s.topk + (s.has_shared ? s.max_tokens : 0);
     if ((rc = make_map(&p.map_tok, GU ? ws.act_q_sorted : ws.inter_q, K / 2, (uint64_t)(S > 0 ? S : 1), TC_ROWS))) return rc;
-    const uint32_t wbox = GU ? 64 : TC_ROWS;
+    const uint32_t wbox = TC_ROWS;
     if ((rc = make_map(&p.map_w_routed, GU ? routed.w13 : routed.w2, K / 2, (uint64_t)s.num_experts * rows, wbox))) return rc;
     if (s.has_shared) { if ((rc = make_map(&p.map_w_shared, GU ? shared.w13 : shared.w2, K / 2, rows, wbox))) return rc; }
     else p.map_w_shared = p.map_w_routed;
@@ -302,7 +289,7 @@ static int launch_pf(const vmoe_shape& s, const WeightSet& routed, const WeightS
     p.gs_routed = GU ? routed.w13_gs : routed.w2_gs;
     p.gs_shared = GU ? shared.w13_gs : shared.w2_gs;
     p.ws = ws; p.K = K; p.N = s.inter; p.hidden = s.hidden; p.E = s.num_experts;
-    p.tiles = GU ? s.inter / 64 : s.hidden / TC_ROWS;
+    p.tiles = GU ? s.inter / TC_ROWS : s.hidden / PF_N;
     p.queue = GU ? CNT_QUEUE1 : CNT_QUEUE2;
     const size_t smem = (size_t)Cfg::STAGES * Cfg::STAGE_BYTES + sizeof(TcShared) + 1024;
     static bool attr_set[64] = {false};
@@ -313,7 +300,7 @@ static int launch_pf(const vmoe_shape& s, const WeightSet& routed, const WeightS
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
     (void)M;
-    pf_kernel<GU><<<(unsigned)tc_sm_count(), TC_THREADS, smem, st>>>(p);
+    pf_kernel<GU><<<(unsigned)tc_sm_count(), PF_THREADS, smem, st>>>(p);
     return cuda_status(cudaGetLastError());
 }
 
