@@ -225,6 +225,12 @@ int vmoe_ep_forward(const vmoe_ep_ctx* ctx, const vmoe_shape* shape, const vmoe_
 /* Status word of an expert-parallel workspace (synchronises the stream). */
 int vmoe_ep_read_status(const vmoe_ep_ctx* ctx, const vmoe_shape* shape, void* workspace, void* stream);
 
+/* Development aid, no counterpart in the reference: cycle counters per warp role of the large-batch
+ * tensor-core kernels, summed over CTAs since the previous call (MMA warp: waiting for data / for the
+ * accumulator / issuing; epilogue: waiting / working; producer: waiting for a ring slot; items; stages).
+ * Synchronises the device. */
+int vmoe_debug_read_profile(unsigned long long* out8);
+
 /* Permutation by expert for callers that cannot allocate device memory.  It has no
  * counterpart in the reference.  Same tables as vmoe_build_tables, but written to arrays the
  * caller passes (expert_offsets [E + 2], sorted_pair / gather_idx / scatter_weights

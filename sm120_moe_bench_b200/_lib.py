@@ -70,6 +70,7 @@ SIGNATURES = {
     "vmoe_ep_forward": (C.c_int, [C.POINTER(VmoeEpCtx), C.POINTER(VmoeShape), C.POINTER(VmoeWeights),
                                   C.POINTER(VmoeWeights), _P, _P, _P, C.c_int32, C.c_int32, _P, C.c_size_t, _P]),
     "vmoe_ep_read_status": (C.c_int, [C.POINTER(VmoeEpCtx), C.POINTER(VmoeShape), _P, _P]),
+    "vmoe_debug_read_profile": (C.c_int, [_P]),
     "vmoe_permute_noalloc": (C.c_int, [_P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                        _P, _P, _P, _P, _P, _P]),
 }

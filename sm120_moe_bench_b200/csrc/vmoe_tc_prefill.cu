@@ -58,6 +58,12 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "r"(taddr) : "memory");
 }
 
+// Cycle counters per role, summed over CTAs (development aid; read and cleared by vmoe_debug_read_profile):
+// [0] MMA warp: waiting for a full stage, [1] MMA warp: waiting for the accumulator, [2] MMA warp: issuing,
+// [3] epilogue warp 2: waiting for the accumulator, [4] epilogue warp 2: working, [5] producer: waiting for a slot,
+// [6] items, [7] stages.
+static __device__ unsigned long long g_pf_prof[8];
+
 template <int GU>
 __global__ void __launch_bounds__(PF_THREADS, 1)
 pf_kernel(const __grid_constant__ PfParams p) {
@@ -92,6 +98,7 @@ pf_kernel(const __grid_constant__ PfParams p) {
             const int atoms_k = p.K / 64;
             uint32_t g = 0;
             bool ok = true;
+            long long prof_wait = 0;
             long long next = atomicAdd(&p.ws.counters[p.queue], 1);
             int4 next_u = (next < total) ? p.ws.tc_units[next / p.tiles] : make_int4(0, 0, 0, 8);
             while (ok) {
@@ -112,7 +119,9 @@ pf_kernel(const __grid_constant__ PfParams p) {
                 const long long sft0 = row0 / TC_ROWS, sft1 = row1 / TC_ROWS;
                 for (int kb = 0; kb < kblocks; ++kb) {
                     const int slot = g % Cfg::STAGES;
+                    const long long tw0 = clock64();
                     if (g >= (uint32_t)Cfg::STAGES && !mbar_wait(&sh->empty[slot], ((g / Cfg::STAGES) - 1) & 1)) { ok = false; break; }
+                    prof_wait += clock64() - tw0;
                     if (sh->abort_flag) { ok = false; break; }
                     uint8_t* st = smem + (size_t)slot * Cfg::STAGE_BYTES;
                     sh->info[slot] = TcStageInfo{u.x, u.y, u.z, 0, tile, unit, kb, kb == kblocks - 1};
@@ -127,6 +136,8 @@ pf_kernel(const __grid_constant__ PfParams p) {
                 }
             }
             if (!ok) tc_timeout(p.ws, sh);
+            atomicAdd(&g_pf_prof[5], (unsigned long long)prof_wait);
+            atomicAdd(&g_pf_prof[7], (unsigned long long)g);
             const int slot = g % Cfg::STAGES;
             if (g < (uint32_t)Cfg::STAGES || mbar_wait(&sh->empty[slot], ((g / Cfg::STAGES) - 1) & 1)) {
                 sh->info[slot] = TcStageInfo{-1, 0, 0, 0, 0, 0, 0, 1};
@@ -142,20 +153,26 @@ pf_kernel(const __grid_constant__ PfParams p) {
             const uint32_t smem16 = smem_u32(smem) >> 4;
             const uint32_t idesc = idesc_nvf4(PF_N);
             bool ok = true;
+            long long pw_full = 0, pw_acc = 0, p_issue = 0;
             while (ok) {
                 const int buf = 0;
                 bool first = true, end = false;
                 while (true) {
                     const int slot = g % Cfg::STAGES;
+                    const long long c0 = clock64();
                     if (!mbar_wait(&sh->full[slot], (g / Cfg::STAGES) & 1)) { ok = false; break; }
+                    const long long c1 = clock64();
+                    pw_full += c1 - c0;
                     tc_fence_after();
                     const TcStageInfo inf = sh->info[slot];
                     if (first) {
                         // single accumulator: the epilogue of the previous item must have drained it
                         if (it >= 1 && !mbar_wait(&sh->tmem_empty[buf], (it - 1) & 1)) { ok = false; break; }
+                        pw_acc += clock64() - c1;
                         tc_fence_after();
                         first = false;
                     }
+                    const long long c2 = clock64();
                     if (inf.expert < 0) { sh->epi[buf] = inf; end = true; break; }
                     const uint32_t st16 = smem16 + slot * (Cfg::STAGE_BYTES >> 4);
                     const uint32_t sfcol = tmem + TC_SF_COL0 + (g & 1) * Cfg::SF_COLS;
@@ -173,6 +190,7 @@ pf_kernel(const __grid_constant__ PfParams p) {
                                make_desc(st16 + ((Cfg::OFF_B + j * 32) >> 4) + DESC_SW128_LBO, DESC_SW128_HI),
                                idesc, sfcol + j * 4, sfcol + 16 + j * 8, (inf.kb > 0 || j > 0) ? 1u : 0u);
                     tc_commit(&sh->empty[slot]);
+                    p_issue += clock64() - c2;
                     ++g;
                     if (inf.last) { sh->epi[buf] = inf; break; }
                 }
@@ -182,6 +200,10 @@ pf_kernel(const __grid_constant__ PfParams p) {
                 ++it;
                 if (end) break;
             }
+            atomicAdd(&g_pf_prof[0], (unsigned long long)pw_full);
+            atomicAdd(&g_pf_prof[1], (unsigned long long)pw_acc);
+            atomicAdd(&g_pf_prof[2], (unsigned long long)p_issue);
+            atomicAdd(&g_pf_prof[6], (unsigned long long)it);
             if (!ok) {
                 tc_timeout(p.ws, sh);
                 sh->epi[it % Cfg::NBUF] = TcStageInfo{-1, 0, 0, 0, 0, 0, 0, 1};
@@ -196,8 +218,12 @@ pf_kernel(const __grid_constant__ PfParams p) {
         const int half = (warp - 2) >> 2;                   // 0: first half of the chunks, 1: second half
         const int t = quad * 32 + lane;                     // token row inside the unit
         uint32_t it = 0;
+        long long pe_wait = 0, pe_work = 0;
         while (true) {
+            const long long c0 = clock64();
             if (!mbar_wait(&sh->tmem_full[0], it & 1)) { if (lane == 0) tc_timeout(p.ws, sh); break; }
+            const long long c1 = clock64();
+            pe_wait += c1 - c0;
             tc_fence_after();
             const TcStageInfo inf = sh->epi[0];
             if (inf.expert < 0) break;
@@ -256,7 +282,12 @@ pf_kernel(const __grid_constant__ PfParams p) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh->tmem_empty[0]);
+            pe_work += clock64() - c1;
             ++it;
+        }
+        if (warp == 2 && lane == 0) {
+            atomicAdd(&g_pf_prof[3], (unsigned long long)pe_wait);
+            atomicAdd(&g_pf_prof[4], (unsigned long long)pe_work);
         }
     }
     tc_fence_before();
@@ -313,4 +344,17 @@ int launch_pf_down(const vmoe_shape& s, const WeightSet& routed, const WeightSet
     return launch_pf<0>(s, routed, shared, prep, M, ws, st, b_rows);
 }
 
+int debug_read_pf_profile(unsigned long long* out8) {
+    if (cudaMemcpyFromSymbol(out8, g_pf_prof, sizeof(g_pf_prof)) != cudaSuccess) return VMOE_ERR_CUDA;
+    unsigned long long zero[8] = {0};
+    return cuda_status(cudaMemcpyToSymbol(g_pf_prof, zero, sizeof(zero)));
+}
+
 }  // namespace vmoe
+
+// Development aid: role cycle counters of the large-batch kernels (see g_pf_prof), summed over CTAs
+// since the last call.  Synchronises the device.  Not part of the operator surface.
+extern "C" int vmoe_debug_read_profile(unsigned long long* out8) {
+    if (!out8) return VMOE_ERR_NULL;
+    return vmoe::debug_read_pf_profile(out8);
+}
