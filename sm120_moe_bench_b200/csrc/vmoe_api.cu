@@ -13,20 +13,22 @@ int max_units(const vmoe_shape* s) {
     return (int)(s->num_experts + 1 + (P + TOK_PER_UNIT - 1) / TOK_PER_UNIT);
 }
 
-// Units carry at most 16 tokens while the batch averages <= 4 tokens per expert (memory-bound:
-// a small token tile leaves shared memory for a deeper weight ring), 128 from 32 tokens per expert
-// on (token-major tiles, compute-bound), else 64.
+// Units carry at most 16 tokens while the batch averages <= 12 tokens per expert (memory-bound:
+// a small token tile leaves shared memory for a deeper weight ring; the few experts above 16 tokens
+// are split and re-read through L2), 128 from 32 tokens per expert on (token-major tiles,
+// compute-bound), else 64.
+constexpr long long TC_SMALL_PER_EXPERT = 12;
 int tc_unit_cap(const vmoe_shape& s, int M) {
     const long long pairs = (long long)M * s.topk;
-    if (pairs <= 4LL * s.num_experts) return TC_UNIT_TOK_SMALL;
+    if (pairs <= TC_SMALL_PER_EXPERT * s.num_experts) return TC_UNIT_TOK_SMALL;
     if (pairs >= 32LL * s.num_experts) return TC_UNIT_TOK_PREFILL;
     return TC_UNIT_TOK;
 }
 
 int max_tc_units(const vmoe_shape* s) {
     const long long S = (long long)s->max_tokens * s->topk + (s->has_shared ? s->max_tokens : 0);
-    // small-unit regime only exists up to M*T = 4E pairs (+ their shared rows)
-    long long small_slots = 4LL * s->num_experts + (s->has_shared ? 4LL * s->num_experts / s->topk + 1 : 0);
+    // small-unit regime only exists up to M*T = 12E pairs (+ their shared rows)
+    long long small_slots = TC_SMALL_PER_EXPERT * s->num_experts + (s->has_shared ? TC_SMALL_PER_EXPERT * s->num_experts / s->topk + 1 : 0);
     if (small_slots > S) small_slots = S;
     const long long a = (S + TC_UNIT_TOK - 1) / TC_UNIT_TOK, b = (small_slots + TC_UNIT_TOK_SMALL - 1) / TC_UNIT_TOK_SMALL;
     return (int)(s->num_experts + 2 + (a > b ? a : b));

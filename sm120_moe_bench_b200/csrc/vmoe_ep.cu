@@ -385,7 +385,11 @@ int vmoe_ep_forward(const vmoe_ep_ctx* ctx, const vmoe_shape* shape, const vmoe_
     }
     ep_gather_kernel<<<64, 256, 0, st>>>(ep, status);
     const int Mr = (int)rows;
-    const int cap = tc_unit_cap(lt, Mr);
+    // Tokens per work unit: the slab is sized for the worst case, so the choice is made from the rows a
+    // rank receives under balanced routing (about its own M * (T + 1)), not from the slab capacity.
+    vmoe_shape est = lt;
+    est.topk = 1;
+    const int cap = tc_unit_cap(est, M * (T + 1));
     if ((rc = launch_tables(lt, ep.flat_ids, ep.flat_w, nullptr, Mr, ws, st, cap))) return rc;
     {
         const long long nb = (long long)rows * (K / SF_BLOCK);

@@ -205,10 +205,15 @@ __device__ void phase_place(const TableArgs& a, int tid, int nthr) {
 constexpr int TABLE_THREADS = 1024;
 
 // small problems: everything in one CTA
-__global__ void __launch_bounds__(TABLE_THREADS) tables_fused_kernel(TableArgs a) {
-    extern __shared__ int32_t s_mem[];          // [E] counts + [3 * nthr] scan
+__global__ void __launch_bounds__(TABLE_THREADS) tables_fused_kernel(TableArgs a, int tables_in_smem) {
+    extern __shared__ int32_t s_mem[];          // [E] counts + [3 * nthr] scan (+ bitmap and running popcounts)
     int32_t* s_count = s_mem; int32_t* s_scan = s_mem + a.E;
     const int tid = threadIdx.x, nthr = blockDim.x;
+    if (tables_in_smem) {
+        // the bitmap and its popcounts are touched by every phase: keep them on chip when they fit
+        a.ws.bitmap = reinterpret_cast<uint32_t*>(s_scan + 3 * nthr);
+        a.ws.word_prefix = reinterpret_cast<int32_t*>(a.ws.bitmap + (size_t)a.E * a.words);
+    }
     phase_clear(a, tid, nthr);       __syncthreads();
     phase_mark(a, tid, nthr);        __syncthreads();
     phase_count(a, tid >> 5, nthr >> 5, tid & 31, s_count); __syncthreads();
@@ -235,12 +240,16 @@ int launch_tables(const vmoe_shape& s, const int32_t* ids, const float* w, const
     a.ws = ws;
     const size_t smem = ((size_t)a.E + 3 * TABLE_THREADS) * sizeof(int32_t);
     if (smem > 200 * 1024) return VMOE_ERR_SHAPE;
-    if (smem > 48 * 1024) {
-        cudaFuncSetAttribute(tables_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cudaFuncSetAttribute(tables_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const size_t smem_tab = smem + 2 * (size_t)a.E * a.words * sizeof(int32_t);
+    const bool in_smem = smem_tab <= 200 * 1024;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaFuncSetAttribute(tables_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(tables_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        attr_done = true;
     }
     if ((long long)M * s.topk <= 16384) {
-        tables_fused_kernel<<<1, TABLE_THREADS, smem, st>>>(a);
+        tables_fused_kernel<<<1, TABLE_THREADS, in_smem ? smem_tab : smem, st>>>(a, in_smem ? 1 : 0);
     } else {
         const int blocks = 296;
         tables_clear_kernel<<<blocks, 256, 0, st>>>(a);
