@@ -63,6 +63,11 @@ struct TcParams {
 // The kernel.  NA = 2: gate_up (A0 = gate rows, A1 = up rows of the same 128-n tile);
 //              NA = 1: down.
 // ---------------------------------------------------------------------------------
+// Cycle counters per role, summed over CTAs (development aid, same slots as the large-batch kernels):
+// [0] MMA: waiting for a full stage, [1] MMA: waiting for an accumulator buffer, [2] MMA: issuing,
+// [3] epilogue warp 2: waiting, [4] epilogue warp 2: working, [5] producer: waiting for a slot, [6] items, [7] stages.
+__device__ unsigned long long g_tc_prof[8];
+
 template <int NA, int KS, int UT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 tc_gemm_kernel(const __grid_constant__ TcParams p) {
@@ -96,6 +101,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
             const int kblocks = p.K / 256;
             uint32_t g = 0;
             bool ok = true;
+            long long prof_wait = 0;
             // The queue pop and the unit record of the NEXT item are requested before the loads of
             // the current one are issued, so their L2 round trips never stall the stream.
             long long next = atomicAdd(&p.ws.counters[p.queue], 1);
@@ -117,7 +123,9 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                 const int steps = kblocks / KS;
                 for (int ks = 0; ks < steps; ++ks) {
                     const int slot = g % Cfg::STAGES;
+                    const long long tw0 = clock64();
                     if (g >= (uint32_t)Cfg::STAGES && !mbar_wait(&sh->empty[slot], ((g / Cfg::STAGES) - 1) & 1)) { ok = false; break; }
+                    prof_wait += clock64() - tw0;
                     if (sh->abort_flag) { ok = false; break; }
                     uint8_t* st = smem + (size_t)slot * Cfg::STAGE_BYTES;
                     sh->info[slot] = TcStageInfo{u.x, u.y, u.z, nbox, tile, unit, ks, ks == steps - 1};
@@ -144,6 +152,8 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                 }
             }
             if (!ok) tc_timeout(p.ws, sh);
+            atomicAdd(&g_tc_prof[5], (unsigned long long)prof_wait);
+            atomicAdd(&g_tc_prof[7], (unsigned long long)g);
             // end marker
             const int slot = g % Cfg::STAGES;
             if (g < (uint32_t)Cfg::STAGES || mbar_wait(&sh->empty[slot], ((g / Cfg::STAGES) - 1) & 1)) {
@@ -155,83 +165,115 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
-            uint32_t g = 0, it = 0, idesc = 0;
-            const uint32_t smem16 = smem_u32(smem) >> 4;
-            bool ok = true;
-            while (ok) {
-                const int buf = it % Cfg::NBUF;
-                bool first = true;
-                bool end = false;
-                while (true) {
-                    const int slot = g % Cfg::STAGES;
-                    if (!mbar_wait(&sh->full[slot], (g / Cfg::STAGES) & 1)) { ok = false; break; }
+        // The whole warp walks the loop with identical values and only the tcgen05 instructions are
+        // predicated on one elected lane: operands then stay warp-uniform and each instruction issues
+        // in ~10-20 cycles; issued from inside a single-lane branch they cost ~50 cycles each
+        // (measured), which made this warp, not HBM, the limit.
+        const bool leader = elect_one();
+        uint32_t g = 0, it = 0, idesc = 0;
+        const uint32_t smem16 = smem_u32(smem) >> 4;
+        bool ok = true;
+        long long pw_full = 0, pw_acc = 0, p_issue = 0;
+        while (ok) {
+            const int buf = it % Cfg::NBUF;
+            bool first = true;
+            bool end = false;
+            while (true) {
+                const int slot = g % Cfg::STAGES;
+                const long long c0 = clock64();
+                if (!__all_sync(0xffffffffu, mbar_wait(&sh->full[slot], (g / Cfg::STAGES) & 1))) { ok = false; break; }
+                const long long c1 = clock64();
+                pw_full += c1 - c0;
+                tc_fence_after();
+                const volatile int* ip = reinterpret_cast<const volatile int*>(&sh->info[slot]);
+                TcStageInfo inf;
+                inf.expert = ip[0]; inf.slot0 = ip[1]; inf.ntok = ip[2]; inf.nbox = ip[3];
+                inf.tile = ip[4]; inf.unit = ip[5]; inf.kb = ip[6]; inf.last = ip[7];
+                if (first) {
+                    // the accumulator buffer must have been drained by the epilogue NBUF items ago
+                    bool w = true;
+                    if (it >= (uint32_t)Cfg::NBUF) w = mbar_wait(&sh->tmem_empty[buf], ((it / Cfg::NBUF) - 1) & 1);
+                    if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+                    pw_acc += clock64() - c1;
                     tc_fence_after();
-                    const TcStageInfo inf = sh->info[slot];
-                    if (first) {
-                        // the accumulator buffer must have been drained by the epilogue NBUF items ago
-                        if (it >= (uint32_t)Cfg::NBUF && !mbar_wait(&sh->tmem_empty[buf], ((it / Cfg::NBUF) - 1) & 1)) { ok = false; break; }
-                        tc_fence_after();
-                        first = false;
-                    }
-                    if (inf.expert < 0) {
-                        sh->epi[buf] = inf;
-                        end = true;
-                        break;
-                    }
-                    // descriptors: only the 14-bit start-address field (bytes >> 4) differs between
-                    // tiles, so each one is a single add on a per-stage base
-                    const uint32_t st16 = smem16 + slot * (Cfg::STAGE_BYTES >> 4);
-                    const uint32_t sfcol = tmem + TC_SF_COL0 + (g & 1) * Cfg::SF_COLS;
-#pragma unroll
-                    for (int t = 0; t < Cfg::NT; ++t)          // weight scales: tile t = a * KS + kk
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            tc_cp_sf(sfcol + t * 16 + j * 4, make_desc(st16 + ((Cfg::OFF_SFA + (t * 4 + j) * 512) >> 4), DESC_SF_HI));
-#pragma unroll
-                    for (int kk = 0; kk < KS; ++kk)             // token scales
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            tc_cp_sf(sfcol + Cfg::NT * 16 + kk * 16 + j * 4, make_desc(st16 + ((Cfg::OFF_SFB + (kk * 4 + j) * 512) >> 4), DESC_SF_HI));
-                    if (inf.kb == 0) idesc = idesc_nvf4(inf.nbox);
-                    const uint32_t dcol = tmem + buf * Cfg::ACC_STRIDE;
-#pragma unroll
-                    for (int kk = 0; kk < KS; ++kk)
-#pragma unroll
-                        for (int a = 0; a < NA; ++a)
-#pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                tc_mma(dcol + a * UT,
-                                       make_desc(st16 + (((a * KS + kk) * TC_A_TILE + j * 32) >> 4) + DESC_SW128_LBO, DESC_SW128_HI),
-                                       make_desc(st16 + ((Cfg::OFF_B + kk * Cfg::B_TILE + j * 32) >> 4) + DESC_SW128_LBO, DESC_SW128_HI),
-                                       idesc, sfcol + (a * KS + kk) * 16 + j * 4, sfcol + Cfg::NT * 16 + kk * 16 + j * 4,
-                                       (inf.kb > 0 || kk > 0 || j > 0) ? 1u : 0u);
-                    tc_commit(&sh->empty[slot]);       // stage (and its scale columns) reusable when these finish
-                    ++g;
-                    if (inf.last) { sh->epi[buf] = inf; break; }
+                    first = false;
                 }
-                if (!ok) break;
+                if (inf.expert < 0) {
+                    if (leader) sh->epi[buf] = inf;
+                    end = true;
+                    break;
+                }
+                const long long c2 = clock64();
+                // descriptors: only the 14-bit start-address field (bytes >> 4) differs between
+                // tiles, so each one is a single add on a per-stage base
+                const uint32_t st16 = smem16 + slot * (Cfg::STAGE_BYTES >> 4);
+                const uint32_t sfcol = tmem + TC_SF_COL0 + (g & 1) * Cfg::SF_COLS;
+#pragma unroll
+                for (int t = 0; t < Cfg::NT; ++t)          // weight scales: tile t = a * KS + kk
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint64_t d = make_desc(st16 + ((Cfg::OFF_SFA + (t * 4 + j) * 512) >> 4), DESC_SF_HI);
+                        if (leader) tc_cp_sf(sfcol + t * 16 + j * 4, d);
+                    }
+#pragma unroll
+                for (int kk = 0; kk < KS; ++kk)             // token scales
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint64_t d = make_desc(st16 + ((Cfg::OFF_SFB + (kk * 4 + j) * 512) >> 4), DESC_SF_HI);
+                        if (leader) tc_cp_sf(sfcol + Cfg::NT * 16 + kk * 16 + j * 4, d);
+                    }
+                if (inf.kb == 0) idesc = idesc_nvf4(inf.nbox);
+                const uint32_t dcol = tmem + buf * Cfg::ACC_STRIDE;
+#pragma unroll
+                for (int kk = 0; kk < KS; ++kk)
+#pragma unroll
+                    for (int a = 0; a < NA; ++a)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint64_t da = make_desc(st16 + (((a * KS + kk) * TC_A_TILE + j * 32) >> 4) + DESC_SW128_LBO, DESC_SW128_HI);
+                            const uint64_t db = make_desc(st16 + ((Cfg::OFF_B + kk * Cfg::B_TILE + j * 32) >> 4) + DESC_SW128_LBO, DESC_SW128_HI);
+                            const uint32_t acc = (inf.kb > 0 || kk > 0 || j > 0) ? 1u : 0u;
+                            if (leader) tc_mma(dcol + a * UT, da, db, idesc, sfcol + (a * KS + kk) * 16 + j * 4,
+                                               sfcol + Cfg::NT * 16 + kk * 16 + j * 4, acc);
+                        }
+                if (leader) tc_commit(&sh->empty[slot]);       // stage (and its scale columns) reusable when these finish
+                p_issue += clock64() - c2;
+                ++g;
+                if (inf.last) { if (leader) sh->epi[buf] = inf; break; }
+            }
+            if (!ok) break;
+            if (leader) {
                 tc_commit(&sh->tmem_full[buf]);        // fires when every MMA of the item has finished
                 mbar_arrive(&sh->tmem_full[buf]);      // releases the epi[] record
-                ++it;
-                if (end) break;
             }
-            if (!ok) {
-                tc_timeout(p.ws, sh);
-                // let the epilogue leave
-                sh->epi[it % Cfg::NBUF] = TcStageInfo{-1, 0, 0, 0, 0, 0, 0, 1};
-                tc_commit(&sh->tmem_full[it % Cfg::NBUF]);
-                mbar_arrive(&sh->tmem_full[it % Cfg::NBUF]);
-            }
+            ++it;
+            if (end) break;
+        }
+        if (leader) {
+            atomicAdd(&g_tc_prof[0], (unsigned long long)pw_full);
+            atomicAdd(&g_tc_prof[1], (unsigned long long)pw_acc);
+            atomicAdd(&g_tc_prof[2], (unsigned long long)p_issue);
+            atomicAdd(&g_tc_prof[6], (unsigned long long)it);
+        }
+        if (!ok && leader) {
+            tc_timeout(p.ws, sh);
+            // let the epilogue leave
+            sh->epi[it % Cfg::NBUF] = TcStageInfo{-1, 0, 0, 0, 0, 0, 0, 1};
+            tc_commit(&sh->tmem_full[it % Cfg::NBUF]);
+            mbar_arrive(&sh->tmem_full[it % Cfg::NBUF]);
         }
     } else {
         // ------------------------------------------------------------- epilogue
         const int quad = warp & 3;                        // TMEM lanes [32*quad, 32*quad + 32)
         const int row = quad * 32 + lane;                 // row of the 128-row tile
         uint32_t it = 0;
+        long long pe_wait = 0, pe_work = 0;
         while (true) {
             const int buf = it % Cfg::NBUF;
+            const long long c0 = clock64();
             if (!mbar_wait(&sh->tmem_full[buf], (it / Cfg::NBUF) & 1)) { if (lane == 0) tc_timeout(p.ws, sh); break; }
+            const long long c1 = clock64();
+            pe_wait += c1 - c0;
             tc_fence_after();
             const TcStageInfo inf = sh->epi[buf];
             if (inf.expert < 0) break;
@@ -289,7 +331,12 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh->tmem_empty[buf]);
+            pe_work += clock64() - c1;
             ++it;
+        }
+        if (warp == 2 && lane == 0) {
+            atomicAdd(&g_tc_prof[3], (unsigned long long)pe_wait);
+            atomicAdd(&g_tc_prof[4], (unsigned long long)pe_work);
         }
     }
     tc_fence_before();
@@ -497,6 +544,12 @@ int launch_tc_down(const vmoe_shape& s, const WeightSet& routed, const WeightSet
                      : launch_tc<1, 2, TC_UNIT_TOK>(s, routed, shared, prep, M, ws, st, b_rows);
     return small ? launch_tc<1, 1, TC_UNIT_TOK_SMALL>(s, routed, shared, prep, M, ws, st, b_rows)
                  : launch_tc<1, 1, TC_UNIT_TOK>(s, routed, shared, prep, M, ws, st, b_rows);
+}
+
+int debug_read_tc_profile(unsigned long long* out8) {
+    if (cudaMemcpyFromSymbol(out8, g_tc_prof, sizeof(g_tc_prof)) != cudaSuccess) return VMOE_ERR_CUDA;
+    unsigned long long zero[8] = {0};
+    return cuda_status(cudaMemcpyToSymbol(g_tc_prof, zero, sizeof(zero)));
 }
 
 }  // namespace vmoe

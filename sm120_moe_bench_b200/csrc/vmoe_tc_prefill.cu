@@ -352,9 +352,11 @@ int debug_read_pf_profile(unsigned long long* out8) {
 
 }  // namespace vmoe
 
-// Development aid: role cycle counters of the large-batch kernels (see g_pf_prof), summed over CTAs
-// since the last call.  Synchronises the device.  Not part of the operator surface.
-extern "C" int vmoe_debug_read_profile(unsigned long long* out8) {
-    if (!out8) return VMOE_ERR_NULL;
-    return vmoe::debug_read_pf_profile(out8);
+// Development aid: role cycle counters of the tensor-core kernels (see g_pf_prof / g_tc_prof), summed over
+// CTAs since the last call.  Synchronises the device.  Not part of the operator surface.
+namespace vmoe { int debug_read_tc_profile(unsigned long long* out8); }
+extern "C" int vmoe_debug_read_profile(unsigned long long* out16) {
+    if (!out16) return VMOE_ERR_NULL;
+    const int rc = vmoe::debug_read_pf_profile(out16);          // [0..7]  large-batch kernels
+    return rc ? rc : vmoe::debug_read_tc_profile(out16 + 8);    // [8..15] decode kernels
 }
