@@ -229,7 +229,8 @@ int vmoe_ep_read_status(const vmoe_ep_ctx* ctx, const vmoe_shape* shape, void* w
  * tensor-core kernels, summed over CTAs since the previous call (MMA warp: waiting for data / for the
  * accumulator / issuing; epilogue: waiting / working; producer: waiting for a ring slot; items; stages).
  * Synchronises the device. */
-int vmoe_debug_read_profile(unsigned long long* out16);   /* [0..7] large-batch kernels, [8..15] decode kernels */
+int vmoe_debug_read_profile(unsigned long long* out20);   /* [0..7] large-batch kernels, [8..15] decode kernels,
+                                                             [16..19] large-batch epilogue: TMEM loads, arithmetic, stores */
 
 /* Permutation by expert for callers that cannot allocate device memory.  It has no
  * counterpart in the reference.  Same tables as vmoe_build_tables, but written to arrays the

@@ -136,10 +136,11 @@ ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restric
         float scale = e4m3_decode(sb);
         if (scale < 1e-30f) scale = 1e-30f;
         uint32_t lo = 0, hi = 0;
+        const ScaleDivider div_scale(scale);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) lo |= e2m1_encode(v[i] / scale) << (4 * i);
+        for (int i = 0; i < 8; ++i) lo |= e2m1_encode(div_scale(v[i])) << (4 * i);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) hi |= e2m1_encode(v[8 + i] / scale) << (4 * i);
+        for (int i = 0; i < 8; ++i) hi |= e2m1_encode(div_scale(v[8 + i])) << (4 * i);
         for (int j = 0; j <= T; ++j) {
             if (j == T && !has_shared) break;
             const int p = (j < T) ? m * T + j : M * T + m;

@@ -248,7 +248,7 @@ __device__ __forceinline__ bool gate_up_item(const GemvParams& p, RingState* rs,
         const uint8_t sb = e4m3_encode(fmaxf(gm / 6.0f, 1e-30f));
         float sc = e4m3_decode(sb);
         if (sc < 1e-30f) sc = 1e-30f;
-        const uint32_t nib = e2m1_encode(sw / sc);
+        const uint32_t nib = e2m1_encode(ScaleDivider(sc)(sw));
         const uint32_t nb = __shfl_down_sync(mask, nib, 1);
         if (t < ntok) {
             const size_t slot_row = (size_t)(inf.slot0 + t);

@@ -26,10 +26,11 @@ quantize_kernel(const __nv_bfloat16* __restrict__ x, long long nblocks, int bloc
     float scale = e4m3_decode(sb);
     if (scale < 1e-30f) scale = 1e-30f;
     uint32_t lo = 0, hi = 0;
+    const ScaleDivider div_scale(scale);
 #pragma unroll
-    for (int i = 0; i < 8; ++i)  lo |= e2m1_encode(v[i] / scale) << (4 * i);
+    for (int i = 0; i < 8; ++i)  lo |= e2m1_encode(div_scale(v[i])) << (4 * i);
 #pragma unroll
-    for (int i = 0; i < 8; ++i)  hi |= e2m1_encode(v[8 + i] / scale) << (4 * i);
+    for (int i = 0; i < 8; ++i)  hi |= e2m1_encode(div_scale(v[8 + i])) << (4 * i);
     reinterpret_cast<uint2*>(packed)[b] = make_uint2(lo, hi);
     sf[b] = sb;
     (void)blocks_per_row;

@@ -94,69 +94,86 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
     pdl_wait();
 
     if (warp == 0) {
-        // ------------------------------------------------------------- producer
-        if (lane == 0) {
-            const int num_units = p.ws.counters[CNT_TC_UNITS];
-            const long long total = (long long)num_units * p.tiles;
-            const int kblocks = p.K / 256;
-            uint32_t g = 0;
-            bool ok = true;
-            long long prof_wait = 0;
-            // The queue pop and the unit record of the NEXT item are requested before the loads of
-            // the current one are issued, so their L2 round trips never stall the stream.
-            long long next = atomicAdd(&p.ws.counters[p.queue], 1);
-            int4 next_u = (next < total) ? p.ws.tc_units[next / p.tiles] : make_int4(0, 0, 0, 8);
-            while (ok) {
-                const long long item = next;
-                if (item >= total) break;
-                // unit-major order: consecutive items are the row tiles of one unit
-                const int unit = (int)(item / p.tiles), tile = (int)(item % p.tiles);
-                const int4 u = next_u;
-                next = atomicAdd(&p.ws.counters[p.queue], 1);
-                next_u = (next < total) ? p.ws.tc_units[next / p.tiles] : make_int4(0, 0, 0, 8);
-                const bool shd = u.x >= p.E;
-                const int e = shd ? 0 : u.x;
-                const CUtensorMap* ma = shd ? &p.map_a_shared : &p.map_a_routed;
-                const uint8_t* sfa = shd ? p.sfa_shared : p.sfa_routed;
-                const int nbox = u.w;
-                const CUtensorMap* mb = &p.map_b[nbox == 8 ? 0 : nbox == 16 ? 1 : nbox == 32 ? 2 : 3];
-                const int steps = kblocks / KS;
-                for (int ks = 0; ks < steps; ++ks) {
-                    const int slot = g % Cfg::STAGES;
-                    const long long tw0 = clock64();
-                    if (g >= (uint32_t)Cfg::STAGES && !mbar_wait(&sh->empty[slot], ((g / Cfg::STAGES) - 1) & 1)) { ok = false; break; }
-                    prof_wait += clock64() - tw0;
-                    if (sh->abort_flag) { ok = false; break; }
-                    uint8_t* st = smem + (size_t)slot * Cfg::STAGE_BYTES;
+        // ------------------------------------------------------------- producer (warp-uniform, see the MMA issuer)
+        const bool leader = elect_one();
+        const int leader_lane = __ffs(__ballot_sync(0xffffffffu, leader)) - 1;
+        const int num_units = p.ws.counters[CNT_TC_UNITS];
+        const long long total = (long long)num_units * p.tiles;
+        const int kblocks = p.K / 256;
+        uint32_t g = 0;
+        bool ok = true;
+        long long prof_wait = 0;
+        // The queue pop and the unit record of the NEXT item are requested before the loads of
+        // the current one are issued, so their L2 round trips never stall the stream.
+        auto pop = [&]() -> long long {
+            long long v = 0;
+            if (leader) v = atomicAdd(&p.ws.counters[p.queue], 1);
+            return __shfl_sync(0xffffffffu, v, leader_lane);
+        };
+        long long next = pop();
+        int4 next_u = (next < total) ? p.ws.tc_units[next / p.tiles] : make_int4(0, 0, 0, 8);
+        while (ok) {
+            const long long item = next;
+            if (item >= total) break;
+            // unit-major order: consecutive items are the row tiles of one unit
+            const int unit = (int)(item / p.tiles), tile = (int)(item % p.tiles);
+            const int4 u = next_u;
+            next = pop();
+            next_u = (next < total) ? p.ws.tc_units[next / p.tiles] : make_int4(0, 0, 0, 8);
+            const bool shd = u.x >= p.E;
+            const int e = shd ? 0 : u.x;
+            const CUtensorMap* ma = shd ? &p.map_a_shared : &p.map_a_routed;
+            const uint8_t* sfa = shd ? p.sfa_shared : p.sfa_routed;
+            const int nbox = u.w;
+            const CUtensorMap* mb = &p.map_b[nbox == 8 ? 0 : nbox == 16 ? 1 : nbox == 32 ? 2 : 3];
+            const int steps = kblocks / KS;
+            for (int ks = 0; ks < steps; ++ks) {
+                const int slot = g % Cfg::STAGES;
+                const long long tw0 = clock64();
+                bool w = true;
+                if (g >= (uint32_t)Cfg::STAGES) w = mbar_wait(&sh->empty[slot], ((g / Cfg::STAGES) - 1) & 1);
+                w = w && !(*(volatile int*)&sh->abort_flag);
+                if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+                prof_wait += clock64() - tw0;
+                uint8_t* st = smem + (size_t)slot * Cfg::STAGE_BYTES;
+                const uint32_t bytes = Cfg::NT * (TC_A_TILE + TC_SF_TILE) + KS * (nbox * TC_KB_BYTES + TC_SF_TILE);
+                const int kb0 = ks * KS;                       // first k-block of this stage
+                if (leader) {
                     sh->info[slot] = TcStageInfo{u.x, u.y, u.z, nbox, tile, unit, ks, ks == steps - 1};
-                    const uint32_t bytes = Cfg::NT * (TC_A_TILE + TC_SF_TILE) + KS * (nbox * TC_KB_BYTES + TC_SF_TILE);
                     mbar_arrive_expect_tx(&sh->full[slot], bytes);
-                    const int kb0 = ks * KS;                       // first k-block of this stage
+                }
 #pragma unroll
-                    for (int a = 0; a < NA; ++a) {
-                        // gate_up: A0 = rows [tile*128, +128) of the gate half, A1 = same rows of the up half
-                        const int row_in_expert = (NA == 2 ? a * p.N : 0) + tile * TC_ROWS;
-                        const long long row = (long long)e * p.rows + row_in_expert;
-#pragma unroll
-                        for (int kk = 0; kk < KS; ++kk)
-                            tma_load_2d(st + (a * KS + kk) * TC_A_TILE, ma, (kb0 + kk) * TC_KB_BYTES, (int)row, &sh->full[slot]);
-                        // the atoms of consecutive k-blocks of one row tile are contiguous
-                        const size_t atom0 = ((size_t)(row / TC_ROWS) * (p.K / 64) + (size_t)kb0 * 4) * 512;
-                        bulk_g2s(st + Cfg::OFF_SFA + a * KS * TC_SF_TILE, sfa + atom0, KS * TC_SF_TILE, &sh->full[slot]);
-                    }
+                for (int a = 0; a < NA; ++a) {
+                    // gate_up: A0 = rows [tile*128, +128) of the gate half, A1 = same rows of the up half
+                    const int row_in_expert = (NA == 2 ? a * p.N : 0) + tile * TC_ROWS;
+                    const long long row = (long long)e * p.rows + row_in_expert;
+                    // the atoms of consecutive k-blocks of one row tile are contiguous
+                    const uint8_t* sfa_src = sfa + ((size_t)(row / TC_ROWS) * (p.K / 64) + (size_t)kb0 * 4) * 512;
 #pragma unroll
                     for (int kk = 0; kk < KS; ++kk)
-                        tma_load_2d(st + Cfg::OFF_B + kk * Cfg::B_TILE, mb, (kb0 + kk) * TC_KB_BYTES, u.y, &sh->full[slot]);
-                    bulk_g2s(st + Cfg::OFF_SFB, p.sfb + ((size_t)unit * (p.K / 64) + (size_t)kb0 * 4) * 512, KS * TC_SF_TILE, &sh->full[slot]);
-                    ++g;
+                        if (leader) tma_load_2d(st + (a * KS + kk) * TC_A_TILE, ma, (kb0 + kk) * TC_KB_BYTES, (int)row, &sh->full[slot]);
+                    if (leader) bulk_g2s(st + Cfg::OFF_SFA + a * KS * TC_SF_TILE, sfa_src, KS * TC_SF_TILE, &sh->full[slot]);
                 }
+                const uint8_t* sfb_src = p.sfb + ((size_t)unit * (p.K / 64) + (size_t)kb0 * 4) * 512;
+#pragma unroll
+                for (int kk = 0; kk < KS; ++kk)
+                    if (leader) tma_load_2d(st + Cfg::OFF_B + kk * Cfg::B_TILE, mb, (kb0 + kk) * TC_KB_BYTES, u.y, &sh->full[slot]);
+                if (leader) bulk_g2s(st + Cfg::OFF_SFB, sfb_src, KS * TC_SF_TILE, &sh->full[slot]);
+                ++g;
             }
+        }
+        if (leader) {
             if (!ok) tc_timeout(p.ws, sh);
             atomicAdd(&g_tc_prof[5], (unsigned long long)prof_wait);
             atomicAdd(&g_tc_prof[7], (unsigned long long)g);
-            // end marker
-            const int slot = g % Cfg::STAGES;
-            if (g < (uint32_t)Cfg::STAGES || mbar_wait(&sh->empty[slot], ((g / Cfg::STAGES) - 1) & 1)) {
+        }
+        // end marker
+        const int slot = g % Cfg::STAGES;
+        bool w = true;
+        if (g >= (uint32_t)Cfg::STAGES) w = mbar_wait(&sh->empty[slot], ((g / Cfg::STAGES) - 1) & 1);
+        w = __all_sync(0xffffffffu, w);
+        if (leader) {
+            if (w) {
                 sh->info[slot] = TcStageInfo{-1, 0, 0, 0, 0, 0, 0, 1};
                 mbar_arrive(&sh->full[slot]);
             } else {
@@ -298,7 +315,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                         const uint8_t sb = e4m3_encode(fmaxf(gm / 6.0f, 1e-30f));
                         float sc = e4m3_decode(sb);
                         if (sc < 1e-30f) sc = 1e-30f;
-                        const uint32_t nib = e2m1_encode(sw / sc);
+                        const uint32_t nib = e2m1_encode(ScaleDivider(sc)(sw));
                         const uint32_t nb = __shfl_down_sync(0xffffffffu, nib, 1);
                         if (t < inf.ntok) {
                             const size_t srow = (size_t)(inf.slot0 + t);
@@ -371,10 +388,11 @@ permute_quantize_kernel(const __nv_bfloat16* __restrict__ x, int M, int K, int T
     float scale = e4m3_decode(sb);
     if (scale < 1e-30f) scale = 1e-30f;
     uint32_t lo = 0, hi = 0;
+    const ScaleDivider div_scale(scale);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) lo |= e2m1_encode(v[i] / scale) << (4 * i);
+    for (int i = 0; i < 8; ++i) lo |= e2m1_encode(div_scale(v[i])) << (4 * i);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) hi |= e2m1_encode(v[8 + i] / scale) << (4 * i);
+    for (int i = 0; i < 8; ++i) hi |= e2m1_encode(div_scale(v[8 + i])) << (4 * i);
     // token-order copy (stage-wise checks and the GEMV path read it)
     reinterpret_cast<uint2*>(ws.act_q)[b] = make_uint2(lo, hi);
     ws.act_sf[b] = sb;

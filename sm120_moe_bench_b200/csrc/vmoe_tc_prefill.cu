@@ -63,6 +63,7 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 // [3] epilogue warp 2: waiting for the accumulator, [4] epilogue warp 2: working, [5] producer: waiting for a slot,
 // [6] items, [7] stages.
 static __device__ unsigned long long g_pf_prof[8];
+static __device__ unsigned long long g_pf_prof2[4];   // epilogue warp 2: [0] TMEM loads, [1] arithmetic, [2] stores
 
 template <int GU>
 __global__ void __launch_bounds__(PF_THREADS, 1)
@@ -218,7 +219,7 @@ pf_kernel(const __grid_constant__ PfParams p) {
         const int half = (warp - 2) >> 2;                   // 0: first half of the chunks, 1: second half
         const int t = quad * 32 + lane;                     // token row inside the unit
         uint32_t it = 0;
-        long long pe_wait = 0, pe_work = 0;
+        long long pe_wait = 0, pe_work = 0, pe_ld = 0, pe_math = 0, pe_st = 0;
         while (true) {
             const long long c0 = clock64();
             if (!mbar_wait(&sh->tmem_full[0], it & 1)) { if (lane == 0) tc_timeout(p.ws, sh); break; }
@@ -236,9 +237,12 @@ pf_kernel(const __grid_constant__ PfParams p) {
 #pragma unroll 1
                 for (int c = half * 4; c < half * 4 + 4; ++c) {     // scale blocks of 16 n; 8 per item
                     uint32_t gr[16], ur[16];
+                    const long long q0 = clock64();
                     tc_ld16(tacc + c * 16, gr);
                     tc_ld16(tacc + TC_ROWS + c * 16, ur);
                     tc_ld_wait();
+                    const long long q1 = clock64();
+                    pe_ld += q1 - q0;
                     float sw[16];
                     float gm = 0.f;
 #pragma unroll
@@ -251,16 +255,20 @@ pf_kernel(const __grid_constant__ PfParams p) {
                     float sc = e4m3_decode(sb);
                     if (sc < 1e-30f) sc = 1e-30f;
                     uint32_t lo = 0, hi = 0;
+                    const ScaleDivider div_sc(sc);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) lo |= e2m1_encode(sw[i] / sc) << (4 * i);
+                    for (int i = 0; i < 8; ++i) lo |= e2m1_encode(div_sc(sw[i])) << (4 * i);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) hi |= e2m1_encode(sw[8 + i] / sc) << (4 * i);
+                    for (int i = 0; i < 8; ++i) hi |= e2m1_encode(div_sc(sw[8 + i])) << (4 * i);
+                    const long long q2 = clock64();
+                    pe_math += q2 - q1;
                     if (valid) {
                         const int n0 = inf.tile * TC_ROWS + c * 16;
                         *reinterpret_cast<uint2*>(p.ws.inter_q + srow * (p.N / 2) + n0 / 2) = make_uint2(lo, hi);
                         p.ws.inter_sf[srow * (p.N / 16) + (n0 >> 4)] = sb;
                         p.ws.inter_sf_atoms[((size_t)inf.unit * (p.N / 64) + (n0 >> 6)) * 512 + (t & 31) * 16 + (t >> 5) * 4 + ((n0 >> 4) & 3)] = sb;
                     }
+                    pe_st += clock64() - q2;
                 }
             } else {
                 const float scale = valid ? p.ws.scatter_weights[srow] * alpha : 0.f;
@@ -288,6 +296,9 @@ pf_kernel(const __grid_constant__ PfParams p) {
         if (warp == 2 && lane == 0) {
             atomicAdd(&g_pf_prof[3], (unsigned long long)pe_wait);
             atomicAdd(&g_pf_prof[4], (unsigned long long)pe_work);
+            atomicAdd(&g_pf_prof2[0], (unsigned long long)pe_ld);
+            atomicAdd(&g_pf_prof2[1], (unsigned long long)pe_math);
+            atomicAdd(&g_pf_prof2[2], (unsigned long long)pe_st);
         }
     }
     tc_fence_before();
@@ -349,14 +360,20 @@ int debug_read_pf_profile(unsigned long long* out8) {
     unsigned long long zero[8] = {0};
     return cuda_status(cudaMemcpyToSymbol(g_pf_prof, zero, sizeof(zero)));
 }
+int debug_read_pf_profile2(unsigned long long* out4) {
+    if (cudaMemcpyFromSymbol(out4, g_pf_prof2, sizeof(g_pf_prof2)) != cudaSuccess) return VMOE_ERR_CUDA;
+    unsigned long long zero[4] = {0};
+    return cuda_status(cudaMemcpyToSymbol(g_pf_prof2, zero, sizeof(zero)));
+}
 
 }  // namespace vmoe
 
 // Development aid: role cycle counters of the tensor-core kernels (see g_pf_prof / g_tc_prof), summed over
 // CTAs since the last call.  Synchronises the device.  Not part of the operator surface.
 namespace vmoe { int debug_read_tc_profile(unsigned long long* out8); }
-extern "C" int vmoe_debug_read_profile(unsigned long long* out16) {
+extern "C" int vmoe_debug_read_profile(unsigned long long* out16) {   // 20 values
     if (!out16) return VMOE_ERR_NULL;
-    const int rc = vmoe::debug_read_pf_profile(out16);          // [0..7]  large-batch kernels
-    return rc ? rc : vmoe::debug_read_tc_profile(out16 + 8);    // [8..15] decode kernels
+    int rc = vmoe::debug_read_pf_profile(out16);                // [0..7]  large-batch kernels
+    if (!rc) rc = vmoe::debug_read_tc_profile(out16 + 8);       // [8..15] decode kernels
+    return rc ? rc : vmoe::debug_read_pf_profile2(out16 + 16);  // [16..19] large-batch epilogue split
 }
