@@ -27,6 +27,8 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC",
     "-Xptxas", "-v",
 ]
+if os.environ.get("VMOE_PROFILE", "0") == "1":     # role cycle counters in the tcgen05 kernels (development aid)
+    NVCC_FLAGS.append("-DVMOE_PROFILE")
 
 
 def _sources():

@@ -301,7 +301,8 @@ int vmoe_forward(const vmoe_shape* shape, const vmoe_weights* routed, const vmoe
     }
     int path;
     if ((rc = pick_path(shape, routed, shared, &path))) return rc;
-    if ((rc = launch_tables(*shape, topk_ids, topk_weights, expert_map, M, ws, st, tc_unit_cap(*shape, M)))) return rc;
+    if ((rc = launch_tables(*shape, topk_ids, topk_weights, expert_map, M, ws, st, tc_unit_cap(*shape, M),
+                            path != VMOE_PATH_TC))) return rc;
     if (path == VMOE_PATH_TC) {
         const PreparedSet prep = to_prep(routed, shape->has_shared ? shared : nullptr);
         if ((rc = launch_permute_quantize(*shape, static_cast<const __nv_bfloat16*>(hidden_bf16), topk_ids,

@@ -391,7 +391,7 @@ int vmoe_ep_forward(const vmoe_ep_ctx* ctx, const vmoe_shape* shape, const vmoe_
     vmoe_shape est = lt;
     est.topk = 1;
     const int cap = tc_unit_cap(est, M * (T + 1));
-    if ((rc = launch_tables(lt, ep.flat_ids, ep.flat_w, nullptr, Mr, ws, st, cap))) return rc;
+    if ((rc = launch_tables(lt, ep.flat_ids, ep.flat_w, nullptr, Mr, ws, st, cap, false))) return rc;
     {
         const long long nb = (long long)rows * (K / SF_BLOCK);
         ep_permute_kernel<<<(unsigned)((nb + 255) / 256), 256, 0, st>>>(ep, K, cap, ws);

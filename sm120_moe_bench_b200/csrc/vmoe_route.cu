@@ -84,6 +84,7 @@ struct TableArgs {
     const int32_t* ids; const float* w; const int32_t* expert_map;
     int M, T, E, has_shared, words;   // words = ceil(M / 32)
     int tc_cap;                       // tokens per tensor-core unit
+    int gemv_units;                   // also emit the 4-token work units of the CUDA-core path
     Workspace ws;
 };
 
@@ -152,7 +153,7 @@ __device__ void phase_scan(const TableArgs& a, int tid, int nthr, const int32_t*
             cb += __shfl_sync(0xffffffffu, ci, 31); ub += __shfl_sync(0xffffffffu, ui, 31); tb += __shfl_sync(0xffffffffu, ti, 31);
         }
         if (tid == 0) {
-            a.ws.counters[CNT_UNITS] = ub; a.ws.counters[CNT_SLOTS] = cb; a.ws.counters[CNT_TC_UNITS] = tb;
+            a.ws.counters[CNT_UNITS] = a.gemv_units ? ub : 0; a.ws.counters[CNT_SLOTS] = cb; a.ws.counters[CNT_TC_UNITS] = tb;
             a.ws.expert_offsets[n] = cb;
             if (!a.has_shared) a.ws.expert_offsets[n + 1] = cb;
         }
@@ -164,8 +165,9 @@ __device__ void phase_scan(const TableArgs& a, int tid, int nthr, const int32_t*
         if (e < n) {
             const int cnt = (e < a.E) ? s_count[e] : a.M;
             a.ws.expert_offsets[e] = c;
-            for (int s = 0; s < cnt; s += TOK_PER_UNIT)
-                a.ws.units[u++] = make_int4(e, c + s, min(TOK_PER_UNIT, cnt - s), 0);
+            if (a.gemv_units)
+                for (int s = 0; s < cnt; s += TOK_PER_UNIT)
+                    a.ws.units[u++] = make_int4(e, c + s, min(TOK_PER_UNIT, cnt - s), 0);
             if (a.ws.tc_units) {
                 a.ws.tc_unit_base[e] = t;
                 for (int s = 0; s < cnt; s += a.tc_cap) {
@@ -232,9 +234,10 @@ __global__ void __launch_bounds__(TABLE_THREADS) tables_scan_kernel(TableArgs a)
 __global__ void tables_place_kernel(TableArgs a) { phase_place(a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x); }
 
 int launch_tables(const vmoe_shape& s, const int32_t* ids, const float* w, const int32_t* expert_map,
-                  int M, const Workspace& ws, cudaStream_t st, int tc_cap) {
+                  int M, const Workspace& ws, cudaStream_t st, int tc_cap, bool gemv_units) {
     TableArgs a;
     a.tc_cap = tc_cap;
+    a.gemv_units = gemv_units ? 1 : 0;
     a.ids = ids; a.w = w; a.expert_map = expert_map;
     a.M = M; a.T = s.topk; a.E = s.num_experts; a.has_shared = s.has_shared; a.words = (M + 31) / 32;
     a.ws = ws;
@@ -337,6 +340,7 @@ extern "C" int vmoe_permute_noalloc(const int32_t* topk_ids, const float* topk_w
     a.ids = topk_ids; a.w = topk_weights; a.expert_map = expert_map;
     a.M = M; a.T = T; a.E = E; a.has_shared = has_shared ? 1 : 0; a.words = (M + 31) / 32;
     a.tc_cap = TC_UNIT_TOK;
+    a.gemv_units = 1;
     a.ws = Workspace{};
     a.ws.expert_offsets = expert_offsets; a.ws.sorted_pair = sorted_pair; a.ws.pair_slot = pair_slot;
     a.ws.gather_idx = gather_idx; a.ws.scatter_weights = scatter_weights;

@@ -129,12 +129,12 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
             const int steps = kblocks / KS;
             for (int ks = 0; ks < steps; ++ks) {
                 const int slot = g % Cfg::STAGES;
-                const long long tw0 = clock64();
+                const long long tw0 = prof_clock();
                 bool w = true;
                 if (g >= (uint32_t)Cfg::STAGES) w = mbar_wait(&sh->empty[slot], ((g / Cfg::STAGES) - 1) & 1);
                 w = w && !(*(volatile int*)&sh->abort_flag);
                 if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
-                prof_wait += clock64() - tw0;
+                prof_wait += prof_clock() - tw0;
                 uint8_t* st = smem + (size_t)slot * Cfg::STAGE_BYTES;
                 const uint32_t bytes = Cfg::NT * (TC_A_TILE + TC_SF_TILE) + KS * (nbox * TC_KB_BYTES + TC_SF_TILE);
                 const int kb0 = ks * KS;                       // first k-block of this stage
@@ -164,8 +164,8 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
         }
         if (leader) {
             if (!ok) tc_timeout(p.ws, sh);
-            atomicAdd(&g_tc_prof[5], (unsigned long long)prof_wait);
-            atomicAdd(&g_tc_prof[7], (unsigned long long)g);
+            VMOE_PROF_ADD(&g_tc_prof[5], prof_wait);
+            VMOE_PROF_ADD(&g_tc_prof[7], g);
         }
         // end marker
         const int slot = g % Cfg::STAGES;
@@ -197,21 +197,18 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
             bool end = false;
             while (true) {
                 const int slot = g % Cfg::STAGES;
-                const long long c0 = clock64();
+                const long long c0 = prof_clock();
                 if (!__all_sync(0xffffffffu, mbar_wait(&sh->full[slot], (g / Cfg::STAGES) & 1))) { ok = false; break; }
-                const long long c1 = clock64();
+                const long long c1 = prof_clock();
                 pw_full += c1 - c0;
                 tc_fence_after();
-                const volatile int* ip = reinterpret_cast<const volatile int*>(&sh->info[slot]);
-                TcStageInfo inf;
-                inf.expert = ip[0]; inf.slot0 = ip[1]; inf.ntok = ip[2]; inf.nbox = ip[3];
-                inf.tile = ip[4]; inf.unit = ip[5]; inf.kb = ip[6]; inf.last = ip[7];
+                const TcStageInfo inf = ld_info(&sh->info[slot]);
                 if (first) {
                     // the accumulator buffer must have been drained by the epilogue NBUF items ago
                     bool w = true;
                     if (it >= (uint32_t)Cfg::NBUF) w = mbar_wait(&sh->tmem_empty[buf], ((it / Cfg::NBUF) - 1) & 1);
                     if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
-                    pw_acc += clock64() - c1;
+                    pw_acc += prof_clock() - c1;
                     tc_fence_after();
                     first = false;
                 }
@@ -220,7 +217,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                     end = true;
                     break;
                 }
-                const long long c2 = clock64();
+                const long long c2 = prof_clock();
                 // descriptors: only the 14-bit start-address field (bytes >> 4) differs between
                 // tiles, so each one is a single add on a per-stage base
                 const uint32_t st16 = smem16 + slot * (Cfg::STAGE_BYTES >> 4);
@@ -254,7 +251,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                                                sfcol + Cfg::NT * 16 + kk * 16 + j * 4, acc);
                         }
                 if (leader) tc_commit(&sh->empty[slot]);       // stage (and its scale columns) reusable when these finish
-                p_issue += clock64() - c2;
+                p_issue += prof_clock() - c2;
                 ++g;
                 if (inf.last) { if (leader) sh->epi[buf] = inf; break; }
             }
@@ -267,10 +264,10 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
             if (end) break;
         }
         if (leader) {
-            atomicAdd(&g_tc_prof[0], (unsigned long long)pw_full);
-            atomicAdd(&g_tc_prof[1], (unsigned long long)pw_acc);
-            atomicAdd(&g_tc_prof[2], (unsigned long long)p_issue);
-            atomicAdd(&g_tc_prof[6], (unsigned long long)it);
+            VMOE_PROF_ADD(&g_tc_prof[0], pw_full);
+            VMOE_PROF_ADD(&g_tc_prof[1], pw_acc);
+            VMOE_PROF_ADD(&g_tc_prof[2], p_issue);
+            VMOE_PROF_ADD(&g_tc_prof[6], it);
         }
         if (!ok && leader) {
             tc_timeout(p.ws, sh);
@@ -287,9 +284,9 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
         long long pe_wait = 0, pe_work = 0;
         while (true) {
             const int buf = it % Cfg::NBUF;
-            const long long c0 = clock64();
+            const long long c0 = prof_clock();
             if (!mbar_wait(&sh->tmem_full[buf], (it / Cfg::NBUF) & 1)) { if (lane == 0) tc_timeout(p.ws, sh); break; }
-            const long long c1 = clock64();
+            const long long c1 = prof_clock();
             pe_wait += c1 - c0;
             tc_fence_after();
             const TcStageInfo inf = sh->epi[buf];
@@ -348,12 +345,12 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sh->tmem_empty[buf]);
-            pe_work += clock64() - c1;
+            pe_work += prof_clock() - c1;
             ++it;
         }
         if (warp == 2 && lane == 0) {
-            atomicAdd(&g_tc_prof[3], (unsigned long long)pe_wait);
-            atomicAdd(&g_tc_prof[4], (unsigned long long)pe_work);
+            VMOE_PROF_ADD(&g_tc_prof[3], pe_wait);
+            VMOE_PROF_ADD(&g_tc_prof[4], pe_work);
         }
     }
     tc_fence_before();

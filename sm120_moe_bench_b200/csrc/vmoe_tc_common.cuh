@@ -18,7 +18,17 @@ constexpr int TC_SF_COL0 = 256;              // first TMEM column of the scale-f
 
 constexpr int TC_SMEM_BUDGET = 227 * 1024 - 3 * 1024;     // dynamic shared memory minus control block and alignment slack
 
-struct TcStageInfo { int expert, slot0, ntok, nbox, tile, unit, kb, last; };   // kb = step index within the item
+struct alignas(16) TcStageInfo { int expert, slot0, ntok, nbox, tile, unit, kb, last; };   // kb = step index within the item
+
+// Role cycle counters are a development aid: compiled in only with -DVMOE_PROFILE (the debug read-out then
+// returns them; otherwise it returns zeros and the clock reads vanish from the kernels).
+#ifdef VMOE_PROFILE
+__device__ __forceinline__ long long prof_clock() { return clock64(); }
+#define VMOE_PROF_ADD(ptr, v) atomicAdd((ptr), (unsigned long long)(v))
+#else
+__device__ __forceinline__ long long prof_clock() { return 0; }
+#define VMOE_PROF_ADD(ptr, v) ((void)0)
+#endif
 
 struct TcShared {
     uint64_t full[12], empty[12];
@@ -33,6 +43,17 @@ struct TcShared {
 // ---------------------------------------------------------------------------------
 // PTX wrappers
 // ---------------------------------------------------------------------------------
+// Stage record written by the producer lane and read by every lane of the MMA warp after the stage's
+// mbarrier completed: two 16-byte volatile loads.
+__device__ __forceinline__ TcStageInfo ld_info(const TcStageInfo* src) {
+    TcStageInfo r;
+    const uint32_t a = smem_u32(src);
+    asm volatile("ld.volatile.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.expert), "=r"(r.slot0), "=r"(r.ntok), "=r"(r.nbox) : "r"(a) : "memory");
+    asm volatile("ld.volatile.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.tile), "=r"(r.unit), "=r"(r.kb), "=r"(r.last) : "r"(a + 16) : "memory");
+    return r;
+}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"

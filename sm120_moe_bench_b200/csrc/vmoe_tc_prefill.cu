@@ -25,7 +25,8 @@
 
 namespace vmoe {
 
-constexpr int PF_THREADS = 320;              // producer warp, MMA warp, 8 epilogue warps
+constexpr int PF_EPI_WARPS = 16;             // four per TMEM lane quadrant, 64 accumulator columns each
+constexpr int PF_THREADS = 64 + 32 * PF_EPI_WARPS;   // producer warp, MMA warp, epilogue warps
 constexpr int PF_N = 256;                    // weight rows per item (UMMA N)
 
 template <int GU> struct PfCfg {
@@ -76,7 +77,7 @@ pf_kernel(const __grid_constant__ PfParams p) {
 
     if (tid == 0) {
         for (int i = 0; i < Cfg::STAGES; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], 1); }
-        for (int i = 0; i < Cfg::NBUF; ++i) { mbar_init(&sh->tmem_full[i], 2); mbar_init(&sh->tmem_empty[i], 8); }
+        for (int i = 0; i < Cfg::NBUF; ++i) { mbar_init(&sh->tmem_full[i], 2); mbar_init(&sh->tmem_empty[i], PF_EPI_WARPS); }
         sh->abort_flag = 0;
         mbar_fence_init();
     }
@@ -91,56 +92,72 @@ pf_kernel(const __grid_constant__ PfParams p) {
     pdl_wait();
 
     if (warp == 0) {
-        // ------------------------------------------------------------- producer
-        if (lane == 0) {
-            const int num_units = p.ws.counters[CNT_TC_UNITS];
-            const long long total = (long long)num_units * p.tiles;
-            const int kblocks = p.K / 256;
-            const int atoms_k = p.K / 64;
-            uint32_t g = 0;
-            bool ok = true;
-            long long prof_wait = 0;
-            long long next = atomicAdd(&p.ws.counters[p.queue], 1);
-            int4 next_u = (next < total) ? p.ws.tc_units[next / p.tiles] : make_int4(0, 0, 0, 8);
-            while (ok) {
-                const long long item = next;
-                if (item >= total) break;
-                const int unit = (int)(item / p.tiles), tile = (int)(item % p.tiles);
-                const int4 u = next_u;
-                next = atomicAdd(&p.ws.counters[p.queue], 1);
-                next_u = (next < total) ? p.ws.tc_units[next / p.tiles] : make_int4(0, 0, 0, 8);
-                const bool shd = u.x >= p.E;
-                const int e = shd ? 0 : u.x;
-                const CUtensorMap* mw = shd ? &p.map_w_shared : &p.map_w_routed;
-                const uint8_t* sfw = shd ? p.sfw_shared : p.sfw_routed;
-                // the two 128-row weight tiles of this item and their scale tiles
-                long long row0, row1;
-                if (GU) { row0 = (long long)e * 2 * p.N + tile * TC_ROWS; row1 = row0 + p.N; }       // gate rows, up rows
-                else    { row0 = (long long)e * p.hidden + tile * PF_N;   row1 = row0 + TC_ROWS; }
-                const long long sft0 = row0 / TC_ROWS, sft1 = row1 / TC_ROWS;
-                for (int kb = 0; kb < kblocks; ++kb) {
-                    const int slot = g % Cfg::STAGES;
-                    const long long tw0 = clock64();
-                    if (g >= (uint32_t)Cfg::STAGES && !mbar_wait(&sh->empty[slot], ((g / Cfg::STAGES) - 1) & 1)) { ok = false; break; }
-                    prof_wait += clock64() - tw0;
-                    if (sh->abort_flag) { ok = false; break; }
-                    uint8_t* st = smem + (size_t)slot * Cfg::STAGE_BYTES;
+        // ------------------------------------------------------------- producer (warp-uniform loop, one
+        // elected lane issues the copies)
+        const bool leader = elect_one();
+        const int num_units = p.ws.counters[CNT_TC_UNITS];
+        const long long total = (long long)num_units * p.tiles;
+        const int kblocks = p.K / 256;
+        const int atoms_k = p.K / 64;
+        uint32_t g = 0;
+        bool ok = true;
+        long long prof_wait = 0;
+        auto grab = [&]() -> long long {
+            int v = 0;
+            if (lane == 0) v = atomicAdd(&p.ws.counters[p.queue], 1);
+            return (long long)__shfl_sync(0xffffffffu, v, 0);
+        };
+        long long next = grab();
+        int4 next_u = (next < total) ? p.ws.tc_units[next / p.tiles] : make_int4(0, 0, 0, 8);
+        while (ok) {
+            const long long item = next;
+            if (item >= total) break;
+            const int unit = (int)(item / p.tiles), tile = (int)(item % p.tiles);
+            const int4 u = next_u;
+            next = grab();
+            next_u = (next < total) ? p.ws.tc_units[next / p.tiles] : make_int4(0, 0, 0, 8);
+            const bool shd = u.x >= p.E;
+            const int e = shd ? 0 : u.x;
+            const CUtensorMap* mw = shd ? &p.map_w_shared : &p.map_w_routed;
+            const uint8_t* sfw = shd ? p.sfw_shared : p.sfw_routed;
+            // the two 128-row weight tiles of this item and their scale tiles
+            long long row0, row1;
+            if (GU) { row0 = (long long)e * 2 * p.N + tile * TC_ROWS; row1 = row0 + p.N; }       // gate rows, up rows
+            else    { row0 = (long long)e * p.hidden + tile * PF_N;   row1 = row0 + TC_ROWS; }
+            const long long sft0 = row0 / TC_ROWS, sft1 = row1 / TC_ROWS;
+            for (int kb = 0; kb < kblocks; ++kb) {
+                const int slot = g % Cfg::STAGES;
+                const long long tw0 = prof_clock();
+                bool w = true;
+                if (g >= (uint32_t)Cfg::STAGES) w = mbar_wait(&sh->empty[slot], ((g / Cfg::STAGES) - 1) & 1);
+                if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+                prof_wait += prof_clock() - tw0;
+                if (*reinterpret_cast<volatile int*>(&sh->abort_flag)) { ok = false; break; }
+                uint8_t* st = smem + (size_t)slot * Cfg::STAGE_BYTES;
+                if (leader) {
                     sh->info[slot] = TcStageInfo{u.x, u.y, u.z, 0, tile, unit, kb, kb == kblocks - 1};
                     mbar_arrive_expect_tx(&sh->full[slot], Cfg::STAGE_BYTES);
-                    tma_load_2d(st, &p.map_tok, kb * TC_KB_BYTES, u.y, &sh->full[slot]);
-                    bulk_g2s(st + Cfg::OFF_SFA, p.sf_tok + ((size_t)unit * atoms_k + (size_t)kb * 4) * 512, TC_SF_TILE, &sh->full[slot]);
-                    tma_load_2d(st + Cfg::OFF_B, mw, kb * TC_KB_BYTES, (int)row0, &sh->full[slot]);
-                    tma_load_2d(st + Cfg::OFF_B + TC_A_TILE, mw, kb * TC_KB_BYTES, (int)row1, &sh->full[slot]);
-                    bulk_g2s(st + Cfg::OFF_SFB, sfw + ((size_t)sft0 * atoms_k + (size_t)kb * 4) * 512, TC_SF_TILE, &sh->full[slot]);
-                    bulk_g2s(st + Cfg::OFF_SFB + TC_SF_TILE, sfw + ((size_t)sft1 * atoms_k + (size_t)kb * 4) * 512, TC_SF_TILE, &sh->full[slot]);
-                    ++g;
                 }
+                if (leader) tma_load_2d(st, &p.map_tok, kb * TC_KB_BYTES, u.y, &sh->full[slot]);
+                if (leader) bulk_g2s(st + Cfg::OFF_SFA, p.sf_tok + ((size_t)unit * atoms_k + (size_t)kb * 4) * 512, TC_SF_TILE, &sh->full[slot]);
+                if (leader) tma_load_2d(st + Cfg::OFF_B, mw, kb * TC_KB_BYTES, (int)row0, &sh->full[slot]);
+                if (leader) tma_load_2d(st + Cfg::OFF_B + TC_A_TILE, mw, kb * TC_KB_BYTES, (int)row1, &sh->full[slot]);
+                if (leader) bulk_g2s(st + Cfg::OFF_SFB, sfw + ((size_t)sft0 * atoms_k + (size_t)kb * 4) * 512, TC_SF_TILE, &sh->full[slot]);
+                if (leader) bulk_g2s(st + Cfg::OFF_SFB + TC_SF_TILE, sfw + ((size_t)sft1 * atoms_k + (size_t)kb * 4) * 512, TC_SF_TILE, &sh->full[slot]);
+                ++g;
             }
-            if (!ok) tc_timeout(p.ws, sh);
-            atomicAdd(&g_pf_prof[5], (unsigned long long)prof_wait);
-            atomicAdd(&g_pf_prof[7], (unsigned long long)g);
-            const int slot = g % Cfg::STAGES;
-            if (g < (uint32_t)Cfg::STAGES || mbar_wait(&sh->empty[slot], ((g / Cfg::STAGES) - 1) & 1)) {
+        }
+        if (!ok && leader) tc_timeout(p.ws, sh);
+        if (leader) {
+            VMOE_PROF_ADD(&g_pf_prof[5], prof_wait);
+            VMOE_PROF_ADD(&g_pf_prof[7], g);
+        }
+        const int slot = g % Cfg::STAGES;
+        bool w = true;
+        if (g >= (uint32_t)Cfg::STAGES) w = mbar_wait(&sh->empty[slot], ((g / Cfg::STAGES) - 1) & 1);
+        w = __all_sync(0xffffffffu, w);
+        if (leader) {
+            if (w) {
                 sh->info[slot] = TcStageInfo{-1, 0, 0, 0, 0, 0, 0, 1};
                 mbar_arrive(&sh->full[slot]);
             } else {
@@ -148,82 +165,94 @@ pf_kernel(const __grid_constant__ PfParams p) {
             }
         }
     } else if (warp == 1) {
-        // ------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
-            uint32_t g = 0, it = 0;
-            const uint32_t smem16 = smem_u32(smem) >> 4;
-            const uint32_t idesc = idesc_nvf4(PF_N);
-            bool ok = true;
-            long long pw_full = 0, pw_acc = 0, p_issue = 0;
-            while (ok) {
-                const int buf = 0;
-                bool first = true, end = false;
-                while (true) {
-                    const int slot = g % Cfg::STAGES;
-                    const long long c0 = clock64();
-                    if (!mbar_wait(&sh->full[slot], (g / Cfg::STAGES) & 1)) { ok = false; break; }
-                    const long long c1 = clock64();
-                    pw_full += c1 - c0;
+        // ------------------------------------------------------------- MMA issuer (warp-uniform loop, one
+        // elected lane issues: see the decode kernel)
+        const bool leader = elect_one();
+        uint32_t g = 0, it = 0;
+        const uint32_t smem16 = smem_u32(smem) >> 4;
+        const uint32_t idesc = idesc_nvf4(PF_N);
+        bool ok = true;
+        long long pw_full = 0, pw_acc = 0, p_issue = 0;
+        while (ok) {
+            bool first = true, end = false;
+            while (true) {
+                const int slot = g % Cfg::STAGES;
+                const long long c0 = prof_clock();
+                if (!__all_sync(0xffffffffu, mbar_wait(&sh->full[slot], (g / Cfg::STAGES) & 1))) { ok = false; break; }
+                const long long c1 = prof_clock();
+                pw_full += c1 - c0;
+                tc_fence_after();
+                const TcStageInfo inf = ld_info(&sh->info[slot]);
+                if (first) {
+                    // single accumulator: the epilogue of the previous item must have drained it
+                    bool w = true;
+                    if (it >= 1) w = mbar_wait(&sh->tmem_empty[0], (it - 1) & 1);
+                    if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
+                    pw_acc += prof_clock() - c1;
                     tc_fence_after();
-                    const TcStageInfo inf = sh->info[slot];
-                    if (first) {
-                        // single accumulator: the epilogue of the previous item must have drained it
-                        if (it >= 1 && !mbar_wait(&sh->tmem_empty[buf], (it - 1) & 1)) { ok = false; break; }
-                        pw_acc += clock64() - c1;
-                        tc_fence_after();
-                        first = false;
-                    }
-                    const long long c2 = clock64();
-                    if (inf.expert < 0) { sh->epi[buf] = inf; end = true; break; }
-                    const uint32_t st16 = smem16 + slot * (Cfg::STAGE_BYTES >> 4);
-                    const uint32_t sfcol = tmem + TC_SF_COL0 + (g & 1) * Cfg::SF_COLS;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)      // token scales
-                        tc_cp_sf(sfcol + j * 4, make_desc(st16 + ((Cfg::OFF_SFA + j * 512) >> 4), DESC_SF_HI));
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {    // weight scales of k-step j: first tile -> columns +0..3, second -> +4..7
-                        tc_cp_sf(sfcol + 16 + j * 8, make_desc(st16 + ((Cfg::OFF_SFB + j * 512) >> 4), DESC_SF_HI));
-                        tc_cp_sf(sfcol + 16 + j * 8 + 4, make_desc(st16 + ((Cfg::OFF_SFB + TC_SF_TILE + j * 512) >> 4), DESC_SF_HI));
-                    }
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        tc_mma(tmem, make_desc(st16 + ((j * 32) >> 4) + DESC_SW128_LBO, DESC_SW128_HI),
-                               make_desc(st16 + ((Cfg::OFF_B + j * 32) >> 4) + DESC_SW128_LBO, DESC_SW128_HI),
-                               idesc, sfcol + j * 4, sfcol + 16 + j * 8, (inf.kb > 0 || j > 0) ? 1u : 0u);
-                    tc_commit(&sh->empty[slot]);
-                    p_issue += clock64() - c2;
-                    ++g;
-                    if (inf.last) { sh->epi[buf] = inf; break; }
+                    first = false;
                 }
-                if (!ok) break;
-                tc_commit(&sh->tmem_full[buf]);
-                mbar_arrive(&sh->tmem_full[buf]);
-                ++it;
-                if (end) break;
+                if (inf.expert < 0) { if (leader) sh->epi[0] = inf; end = true; break; }
+                const long long c2 = prof_clock();
+                const uint32_t st16 = smem16 + slot * (Cfg::STAGE_BYTES >> 4);
+                const uint32_t sfcol = tmem + TC_SF_COL0 + (g & 1) * Cfg::SF_COLS;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {    // token scales
+                    const uint64_t d = make_desc(st16 + ((Cfg::OFF_SFA + j * 512) >> 4), DESC_SF_HI);
+                    if (leader) tc_cp_sf(sfcol + j * 4, d);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {    // weight scales of k-step j: first tile -> columns +0..3, second -> +4..7
+                    const uint64_t d0 = make_desc(st16 + ((Cfg::OFF_SFB + j * 512) >> 4), DESC_SF_HI);
+                    const uint64_t d1 = make_desc(st16 + ((Cfg::OFF_SFB + TC_SF_TILE + j * 512) >> 4), DESC_SF_HI);
+                    if (leader) tc_cp_sf(sfcol + 16 + j * 8, d0);
+                    if (leader) tc_cp_sf(sfcol + 16 + j * 8 + 4, d1);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint64_t da = make_desc(st16 + ((j * 32) >> 4) + DESC_SW128_LBO, DESC_SW128_HI);
+                    const uint64_t db = make_desc(st16 + ((Cfg::OFF_B + j * 32) >> 4) + DESC_SW128_LBO, DESC_SW128_HI);
+                    const uint32_t acc = (inf.kb > 0 || j > 0) ? 1u : 0u;
+                    if (leader) tc_mma(tmem, da, db, idesc, sfcol + j * 4, sfcol + 16 + j * 8, acc);
+                }
+                if (leader) tc_commit(&sh->empty[slot]);
+                p_issue += prof_clock() - c2;
+                ++g;
+                if (inf.last) { if (leader) sh->epi[0] = inf; break; }
             }
-            atomicAdd(&g_pf_prof[0], (unsigned long long)pw_full);
-            atomicAdd(&g_pf_prof[1], (unsigned long long)pw_acc);
-            atomicAdd(&g_pf_prof[2], (unsigned long long)p_issue);
-            atomicAdd(&g_pf_prof[6], (unsigned long long)it);
+            if (!ok) break;
+            if (leader) {
+                tc_commit(&sh->tmem_full[0]);
+                mbar_arrive(&sh->tmem_full[0]);
+            }
+            ++it;
+            if (end) break;
+        }
+        if (leader) {
+            VMOE_PROF_ADD(&g_pf_prof[0], pw_full);
+            VMOE_PROF_ADD(&g_pf_prof[1], pw_acc);
+            VMOE_PROF_ADD(&g_pf_prof[2], p_issue);
+            VMOE_PROF_ADD(&g_pf_prof[6], it);
             if (!ok) {
                 tc_timeout(p.ws, sh);
-                sh->epi[it % Cfg::NBUF] = TcStageInfo{-1, 0, 0, 0, 0, 0, 0, 1};
-                tc_commit(&sh->tmem_full[it % Cfg::NBUF]);
-                mbar_arrive(&sh->tmem_full[it % Cfg::NBUF]);
+                sh->epi[0] = TcStageInfo{-1, 0, 0, 0, 0, 0, 0, 1};
+                tc_commit(&sh->tmem_full[0]);
+                mbar_arrive(&sh->tmem_full[0]);
             }
         }
     } else {
         // ------------------------------------------------------------- epilogue: one token row per thread,
-        // two warps per TMEM lane quadrant, each draining half of the 16-column chunks
+        // four warps per TMEM lane quadrant.  Each thread copies its 64 accumulator columns to registers and
+        // hands the accumulator back at once, so the next item's MMAs run under this item's arithmetic.
         const int quad = warp & 3;
-        const int half = (warp - 2) >> 2;                   // 0: first half of the chunks, 1: second half
+        const int sub = (warp - 2) >> 2;                    // which quarter of the columns
         const int t = quad * 32 + lane;                     // token row inside the unit
         uint32_t it = 0;
         long long pe_wait = 0, pe_work = 0, pe_ld = 0, pe_math = 0, pe_st = 0;
         while (true) {
-            const long long c0 = clock64();
+            const long long c0 = prof_clock();
             if (!mbar_wait(&sh->tmem_full[0], it & 1)) { if (lane == 0) tc_timeout(p.ws, sh); break; }
-            const long long c1 = clock64();
+            const long long c1 = prof_clock();
             pe_wait += c1 - c0;
             tc_fence_after();
             const TcStageInfo inf = sh->epi[0];
@@ -234,20 +263,26 @@ pf_kernel(const __grid_constant__ PfParams p) {
             const bool valid = t < inf.ntok;
             const size_t srow = (size_t)(inf.slot0 + (valid ? t : 0));
             if (GU) {
-#pragma unroll 1
-                for (int c = half * 4; c < half * 4 + 4; ++c) {     // scale blocks of 16 n; 8 per item
-                    uint32_t gr[16], ur[16];
-                    const long long q0 = clock64();
-                    tc_ld16(tacc + c * 16, gr);
-                    tc_ld16(tacc + TC_ROWS + c * 16, ur);
-                    tc_ld_wait();
-                    const long long q1 = clock64();
-                    pe_ld += q1 - q0;
+                // scale blocks 2*sub and 2*sub+1 of the item's 8: gate columns c*16.., up columns 128 + c*16..
+                uint32_t gr[2][16], ur[2][16];
+                tc_ld16(tacc + (sub * 2) * 16, gr[0]);
+                tc_ld16(tacc + TC_ROWS + (sub * 2) * 16, ur[0]);
+                tc_ld16(tacc + (sub * 2 + 1) * 16, gr[1]);
+                tc_ld16(tacc + TC_ROWS + (sub * 2 + 1) * 16, ur[1]);
+                tc_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh->tmem_empty[0]);
+                const long long q1 = prof_clock();
+                pe_ld += q1 - c1;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int c = sub * 2 + h;
                     float sw[16];
                     float gm = 0.f;
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const float gate = __uint_as_float(gr[i]) * alpha, up = __uint_as_float(ur[i]) * alpha;
+                        const float gate = __uint_as_float(gr[h][i]) * alpha, up = __uint_as_float(ur[h][i]) * alpha;
                         sw[i] = up * silu(gate);
                         gm = fmaxf(gm, fabsf(sw[i]));
                     }
@@ -260,45 +295,51 @@ pf_kernel(const __grid_constant__ PfParams p) {
                     for (int i = 0; i < 8; ++i) lo |= e2m1_encode(div_sc(sw[i])) << (4 * i);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) hi |= e2m1_encode(div_sc(sw[8 + i])) << (4 * i);
-                    const long long q2 = clock64();
-                    pe_math += q2 - q1;
                     if (valid) {
                         const int n0 = inf.tile * TC_ROWS + c * 16;
                         *reinterpret_cast<uint2*>(p.ws.inter_q + srow * (p.N / 2) + n0 / 2) = make_uint2(lo, hi);
                         p.ws.inter_sf[srow * (p.N / 16) + (n0 >> 4)] = sb;
                         p.ws.inter_sf_atoms[((size_t)inf.unit * (p.N / 64) + (n0 >> 6)) * 512 + (t & 31) * 16 + (t >> 5) * 4 + ((n0 >> 4) & 3)] = sb;
                     }
-                    pe_st += clock64() - q2;
                 }
+                pe_math += prof_clock() - q1;
             } else {
                 const float scale = valid ? p.ws.scatter_weights[srow] * alpha : 0.f;
-                float* orow = (p.ws.row_dst ? p.ws.row_dst[srow] : p.ws.pair_out + srow * p.hidden) + inf.tile * PF_N;
-#pragma unroll 1
-                for (int c = half * 8; c < half * 8 + 8; ++c) {
-                    uint32_t yr[16];
-                    tc_ld16(tacc + c * 16, yr);
-                    tc_ld_wait();
-                    if (valid) {
+                float* orow = (p.ws.row_dst ? p.ws.row_dst[srow] : p.ws.pair_out + srow * p.hidden) + inf.tile * PF_N + sub * 64;
+                uint32_t yr[4][16];
 #pragma unroll
-                        for (int i = 0; i < 16; i += 4)
-                            *reinterpret_cast<float4*>(orow + c * 16 + i) =
-                                make_float4(scale * __uint_as_float(yr[i]), scale * __uint_as_float(yr[i + 1]),
-                                            scale * __uint_as_float(yr[i + 2]), scale * __uint_as_float(yr[i + 3]));
-                    }
+                for (int c = 0; c < 4; ++c) tc_ld16(tacc + sub * 64 + c * 16, yr[c]);
+                tc_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sh->tmem_empty[0]);
+                const long long q1 = prof_clock();
+                pe_ld += q1 - c1;
+                if (valid) {
+                    // 32-byte stores: every lane writes whole sectors of its own row
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int i = 0; i < 16; i += 8)
+                            asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                                         ::"l"(orow + c * 16 + i),
+                                           "f"(scale * __uint_as_float(yr[c][i])), "f"(scale * __uint_as_float(yr[c][i + 1])),
+                                           "f"(scale * __uint_as_float(yr[c][i + 2])), "f"(scale * __uint_as_float(yr[c][i + 3])),
+                                           "f"(scale * __uint_as_float(yr[c][i + 4])), "f"(scale * __uint_as_float(yr[c][i + 5])),
+                                           "f"(scale * __uint_as_float(yr[c][i + 6])), "f"(scale * __uint_as_float(yr[c][i + 7]))
+                                         : "memory");
                 }
+                pe_st += prof_clock() - q1;
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sh->tmem_empty[0]);
-            pe_work += clock64() - c1;
+            pe_work += prof_clock() - c1;
             ++it;
         }
         if (warp == 2 && lane == 0) {
-            atomicAdd(&g_pf_prof[3], (unsigned long long)pe_wait);
-            atomicAdd(&g_pf_prof[4], (unsigned long long)pe_work);
-            atomicAdd(&g_pf_prof2[0], (unsigned long long)pe_ld);
-            atomicAdd(&g_pf_prof2[1], (unsigned long long)pe_math);
-            atomicAdd(&g_pf_prof2[2], (unsigned long long)pe_st);
+            VMOE_PROF_ADD(&g_pf_prof[3], pe_wait);
+            VMOE_PROF_ADD(&g_pf_prof[4], pe_work);
+            VMOE_PROF_ADD(&g_pf_prof2[0], pe_ld);
+            VMOE_PROF_ADD(&g_pf_prof2[1], pe_math);
+            VMOE_PROF_ADD(&g_pf_prof2[2], pe_st);
         }
     }
     tc_fence_before();
