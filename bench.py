@@ -392,7 +392,7 @@ def run_prefill(args, dev):
             "config": {"workload": "single-GPU prefill MoE layer (BASELINE config 3)", "tokens": M, "zipf_s": args.zipf,
                        "hidden": K, "inter": N, "experts": cfg.num_experts, "topk": T, "shared_experts": 1},
             "tokens_per_s": M / (ms * 1e-3),
-            "roofline": {"bound": "tensor", "kernel": "tc_gemm_kernel<2,1,64> (gate_up, tcgen05)",
+            "roofline": {"bound": "tensor", "kernel": "pf_kernel<1> (gate_up, tcgen05, 128-token x 256-row items)",
                          "achieved": gu_flops / (stage_ms["gate_up"] * 1e-3) / 1e12, "peak": NOMINAL_FP4_TFLOPS,
                          "peak_source": "nominal dense FP4 (no measured FP4 peak available)", "unit": "TFLOP/s",
                          "frac": gu_flops / (stage_ms["gate_up"] * 1e-3) / 1e12 / NOMINAL_FP4_TFLOPS, "traffic": None,

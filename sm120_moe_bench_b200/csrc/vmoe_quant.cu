@@ -69,27 +69,44 @@ int launch_dequantize(const uint8_t* packed, const uint8_t* sf, const float* gs,
 }
 
 // out[m, :] = bf16( sum_j pair_out[slot(m, j), :]  (ascending j, fp32)  + shared row )
-// one thread per 4 consecutive columns.
+// one thread per 4 consecutive columns.  BATCHED (small launches, bound by load latency): the slot numbers and
+// then all rows of a token are requested at once; otherwise (large launches, bound by bandwidth) row by row.
+template <bool BATCHED>
 __global__ void __launch_bounds__(256)
 combine_kernel(const float* __restrict__ pair_out, const int32_t* __restrict__ pair_slot,
                const int32_t* __restrict__ expert_offsets, int M, int K, int T, int E, int has_shared,
                __nv_bfloat16* __restrict__ out) {
+    pdl_begin();
     const int k4 = K / 4;
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)M * k4) return;
     const int m = (int)(i / k4), c = (int)(i % k4);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int j = 0; j < T; ++j) {
-        const int slot = pair_slot[m * T + j];
-        if (slot >= 0) {
+    if (BATCHED) {
+        int slot[MAX_TOPK + 1];
+#pragma unroll
+        for (int j = 0; j < MAX_TOPK; ++j) slot[j] = (j < T) ? pair_slot[m * T + j] : -1;
+        slot[MAX_TOPK] = has_shared ? expert_offsets[E] + m : -1;
+        float4 v[MAX_TOPK + 1];
+#pragma unroll
+        for (int j = 0; j <= MAX_TOPK; ++j)
+            if (slot[j] >= 0) v[j] = reinterpret_cast<const float4*>(pair_out + (size_t)slot[j] * K)[c];
+#pragma unroll
+        for (int j = 0; j <= MAX_TOPK; ++j)        // ascending pair order, shared expert last
+            if (slot[j] >= 0) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
+    } else {
+        for (int j = 0; j < T; ++j) {
+            const int slot = pair_slot[m * T + j];
+            if (slot >= 0) {
+                const float4 v = reinterpret_cast<const float4*>(pair_out + (size_t)slot * K)[c];
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+        }
+        if (has_shared) {
+            const int slot = expert_offsets[E] + m;
             const float4 v = reinterpret_cast<const float4*>(pair_out + (size_t)slot * K)[c];
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
-    }
-    if (has_shared) {
-        const int slot = expert_offsets[E] + m;
-        const float4 v = reinterpret_cast<const float4*>(pair_out + (size_t)slot * K)[c];
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
     __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
     uint2 o; o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
@@ -99,8 +116,13 @@ combine_kernel(const float* __restrict__ pair_out, const int32_t* __restrict__ p
 int launch_combine(const vmoe_shape& s, int M, const Workspace& ws, __nv_bfloat16* out, cudaStream_t st) {
     const long long n = (long long)M * (s.hidden / 4);
     if (n == 0) return VMOE_OK;
-    combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
-        ws.pair_out, ws.pair_slot, ws.expert_offsets, M, s.hidden, s.topk, s.num_experts, s.has_shared, out);
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (blocks <= 4096)
+        launch_pdl(combine_kernel<true>, blocks, 256u, 0, st,
+            ws.pair_out, ws.pair_slot, ws.expert_offsets, M, s.hidden, s.topk, s.num_experts, s.has_shared, out);
+    else
+        launch_pdl(combine_kernel<false>, blocks, 256u, 0, st,
+            ws.pair_out, ws.pair_slot, ws.expert_offsets, M, s.hidden, s.topk, s.num_experts, s.has_shared, out);
     return cuda_status(cudaGetLastError());
 }
 

@@ -18,6 +18,7 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 route_kernel(const float* __restrict__ logits, int M, int E, int T,
              int32_t* __restrict__ topk_ids, float* __restrict__ topk_w) {
     extern __shared__ float s_prob[];            // [ROUTE_WARPS][E]
+    pdl_begin();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m = blockIdx.x * ROUTE_WARPS + warp;
     if (m >= M) return;
@@ -64,7 +65,7 @@ int launch_route(const float* logits, int M, int E, int T, int32_t* ids, float* 
     if (smem > 200 * 1024) return VMOE_ERR_SHAPE;
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    route_kernel<<<(M + ROUTE_WARPS - 1) / ROUTE_WARPS, ROUTE_WARPS * 32, smem, st>>>(logits, M, E, T, ids, w);
+    launch_pdl(route_kernel, (unsigned)((M + ROUTE_WARPS - 1) / ROUTE_WARPS), ROUTE_WARPS * 32, smem, st, logits, M, E, T, ids, w);
     return cuda_status(cudaGetLastError());
 }
 
@@ -106,8 +107,25 @@ __device__ void phase_mark(const TableArgs& a, int tid, int nthr) {
         if (e >= 0) { const int m = p / a.T; atomicOr(&a.ws.bitmap[(size_t)e * a.words + (m >> 5)], 1u << (m & 31)); }
     }
 }
-// one warp per expert: running popcount per word; returns the expert's pair count to lane 0
+// Running popcount per bitmap word and the pair count per expert.  A warp takes 32 / wp experts at a
+// time (wp = words rounded up to a power of two) with a segmented shuffle scan over each expert's
+// words; experts with more than 32 words are walked 32 words at a time by a whole warp.
 __device__ void phase_count(const TableArgs& a, int warp, int nwarps, int lane, int32_t* s_count) {
+    if (a.words <= 32) {
+        int wp = 1;
+        while (wp < a.words) wp <<= 1;
+        const int gpw = 32 / wp, sub = lane / wp, wl = lane % wp;
+        for (int e0 = warp * gpw; e0 < a.E; e0 += nwarps * gpw) {
+            const int e = e0 + sub;
+            const bool valid = e < a.E && wl < a.words;
+            const int c = valid ? __popc(a.ws.bitmap[(size_t)e * a.words + wl]) : 0;
+            int incl = c;
+            for (int o = 1; o < wp; o <<= 1) { const int t = __shfl_up_sync(0xffffffffu, incl, o, wp); if (wl >= o) incl += t; }
+            if (valid) a.ws.word_prefix[(size_t)e * a.words + wl] = incl - c;
+            if (wl == wp - 1 && e < a.E) s_count[e] = incl;
+        }
+        return;
+    }
     for (int e = warp; e < a.E; e += nwarps) {
         int running = 0;
         for (int w0 = 0; w0 < a.words; w0 += 32) {
@@ -136,30 +154,33 @@ __device__ void phase_scan(const TableArgs& a, int tid, int nthr, const int32_t*
             csum += c; usum += (c + TOK_PER_UNIT - 1) / TOK_PER_UNIT; tsum += (c + a.tc_cap - 1) / a.tc_cap;
         }
     }
-    s_scan[tid] = csum; s_scan[nthr + tid] = usum; s_scan[2 * nthr + tid] = tsum;
-    __syncthreads();
-    if (tid < 32) {   // warp 0: exclusive scan of the per-thread partial sums, 32 at a time
-        int cb = 0, ub = 0, tb = 0;
-        for (int i0 = 0; i0 < nthr; i0 += 32) {
-            const int i = i0 + tid;
-            const int c = i < nthr ? s_scan[i] : 0, u = i < nthr ? s_scan[nthr + i] : 0, t = i < nthr ? s_scan[2 * nthr + i] : 0;
-            int ci = c, ui = u, ti = t;
+    // two-level exclusive scan of the per-thread sums: inside each warp, then over the warp totals
+    const int lane = tid & 31, wid = tid >> 5, nw = (nthr + 31) >> 5;
+    int ci = csum, ui = usum, ti = tsum;
 #pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int c2 = __shfl_up_sync(0xffffffffu, ci, o), u2 = __shfl_up_sync(0xffffffffu, ui, o), t2 = __shfl_up_sync(0xffffffffu, ti, o);
-                if (tid >= o) { ci += c2; ui += u2; ti += t2; }
-            }
-            if (i < nthr) { s_scan[i] = cb + ci - c; s_scan[nthr + i] = ub + ui - u; s_scan[2 * nthr + i] = tb + ti - t; }
-            cb += __shfl_sync(0xffffffffu, ci, 31); ub += __shfl_sync(0xffffffffu, ui, 31); tb += __shfl_sync(0xffffffffu, ti, 31);
+    for (int o = 1; o < 32; o <<= 1) {
+        const int c2 = __shfl_up_sync(0xffffffffu, ci, o), u2 = __shfl_up_sync(0xffffffffu, ui, o), t2 = __shfl_up_sync(0xffffffffu, ti, o);
+        if (lane >= o) { ci += c2; ui += u2; ti += t2; }
+    }
+    if (lane == 31) { s_scan[wid] = ci; s_scan[32 + wid] = ui; s_scan[64 + wid] = ti; }
+    __syncthreads();
+    if (tid < 32) {
+        const int c0 = tid < nw ? s_scan[tid] : 0, u0 = tid < nw ? s_scan[32 + tid] : 0, t0 = tid < nw ? s_scan[64 + tid] : 0;
+        int cw = c0, uw = u0, tw = t0;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int c2 = __shfl_up_sync(0xffffffffu, cw, o), u2 = __shfl_up_sync(0xffffffffu, uw, o), t2 = __shfl_up_sync(0xffffffffu, tw, o);
+            if (tid >= o) { cw += c2; uw += u2; tw += t2; }
         }
-        if (tid == 0) {
-            a.ws.counters[CNT_UNITS] = a.gemv_units ? ub : 0; a.ws.counters[CNT_SLOTS] = cb; a.ws.counters[CNT_TC_UNITS] = tb;
-            a.ws.expert_offsets[n] = cb;
-            if (!a.has_shared) a.ws.expert_offsets[n + 1] = cb;
+        s_scan[tid] = cw - c0; s_scan[32 + tid] = uw - u0; s_scan[64 + tid] = tw - t0;     // exclusive warp bases
+        if (tid == 31) {
+            a.ws.counters[CNT_UNITS] = a.gemv_units ? uw : 0; a.ws.counters[CNT_SLOTS] = cw; a.ws.counters[CNT_TC_UNITS] = tw;
+            a.ws.expert_offsets[n] = cw;
+            if (!a.has_shared) a.ws.expert_offsets[n + 1] = cw;
         }
     }
     __syncthreads();
-    int c = s_scan[tid], u = s_scan[nthr + tid], t = s_scan[2 * nthr + tid];
+    int c = s_scan[wid] + ci - csum, u = s_scan[32 + wid] + ui - usum, t = s_scan[64 + wid] + ti - tsum;
     for (int k = 0; k < per; ++k) {
         const int e = tid * per + k;
         if (e < n) {
@@ -211,6 +232,7 @@ __global__ void __launch_bounds__(TABLE_THREADS) tables_fused_kernel(TableArgs a
     extern __shared__ int32_t s_mem[];          // [E] counts + [3 * nthr] scan (+ bitmap and running popcounts)
     int32_t* s_count = s_mem; int32_t* s_scan = s_mem + a.E;
     const int tid = threadIdx.x, nthr = blockDim.x;
+    pdl_begin();
     if (tables_in_smem) {
         // the bitmap and its popcounts are touched by every phase: keep them on chip when they fit
         a.ws.bitmap = reinterpret_cast<uint32_t*>(s_scan + 3 * nthr);
@@ -223,15 +245,19 @@ __global__ void __launch_bounds__(TABLE_THREADS) tables_fused_kernel(TableArgs a
     phase_place(a, tid, nthr);
 }
 // large problems: grid-wide phases as separate launches
-__global__ void tables_clear_kernel(TableArgs a) { phase_clear(a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x); }
-__global__ void tables_mark_kernel(TableArgs a)  { phase_mark(a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x); }
-__global__ void __launch_bounds__(TABLE_THREADS) tables_scan_kernel(TableArgs a) {
-    extern __shared__ int32_t s_mem[];
-    int32_t* s_count = s_mem; int32_t* s_scan = s_mem + a.E;
-    phase_count(a, threadIdx.x >> 5, blockDim.x >> 5, threadIdx.x & 31, s_count); __syncthreads();
-    phase_scan(a, threadIdx.x, blockDim.x, s_count, s_scan);
+__global__ void tables_clear_kernel(TableArgs a) { pdl_begin(); phase_clear(a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x); }
+__global__ void tables_mark_kernel(TableArgs a)  { pdl_begin(); phase_mark(a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x); }
+// counts go through expert_offsets (each entry is read by its owner before the scan overwrites it)
+__global__ void __launch_bounds__(256) tables_count_kernel(TableArgs a) {
+    pdl_begin();
+    phase_count(a, (blockIdx.x * blockDim.x + threadIdx.x) >> 5, (gridDim.x * blockDim.x) >> 5, threadIdx.x & 31, a.ws.expert_offsets);
 }
-__global__ void tables_place_kernel(TableArgs a) { phase_place(a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x); }
+__global__ void __launch_bounds__(TABLE_THREADS) tables_scan_kernel(TableArgs a) {
+    __shared__ int32_t s_scan[96];
+    pdl_begin();
+    phase_scan(a, threadIdx.x, blockDim.x, a.ws.expert_offsets, s_scan);
+}
+__global__ void tables_place_kernel(TableArgs a) { pdl_begin(); phase_place(a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x); }
 
 int launch_tables(const vmoe_shape& s, const int32_t* ids, const float* w, const int32_t* expert_map,
                   int M, const Workspace& ws, cudaStream_t st, int tc_cap, bool gemv_units) {
@@ -248,17 +274,17 @@ int launch_tables(const vmoe_shape& s, const int32_t* ids, const float* w, const
     static bool attr_done = false;
     if (!attr_done) {
         cudaFuncSetAttribute(tables_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        cudaFuncSetAttribute(tables_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         attr_done = true;
     }
     if ((long long)M * s.topk <= 16384) {
-        tables_fused_kernel<<<1, TABLE_THREADS, in_smem ? smem_tab : smem, st>>>(a, in_smem ? 1 : 0);
+        launch_pdl(tables_fused_kernel, 1u, (unsigned)TABLE_THREADS, in_smem ? smem_tab : smem, st, a, in_smem ? 1 : 0);
     } else {
         const int blocks = 296;
-        tables_clear_kernel<<<blocks, 256, 0, st>>>(a);
-        tables_mark_kernel<<<blocks, 256, 0, st>>>(a);
-        tables_scan_kernel<<<1, TABLE_THREADS, smem, st>>>(a);
-        tables_place_kernel<<<blocks, 256, 0, st>>>(a);
+        launch_pdl(tables_clear_kernel, (unsigned)blocks, 256u, 0, st, a);
+        launch_pdl(tables_mark_kernel, (unsigned)blocks, 256u, 0, st, a);
+        launch_pdl(tables_count_kernel, (unsigned)((a.E + 7) / 8), 256u, 0, st, a);
+        launch_pdl(tables_scan_kernel, 1u, (unsigned)TABLE_THREADS, 0, st, a);
+        launch_pdl(tables_place_kernel, (unsigned)blocks, 256u, 0, st, a);
     }
     return cuda_status(cudaGetLastError());
 }

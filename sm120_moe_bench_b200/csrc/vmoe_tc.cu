@@ -91,7 +91,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = sh->tmem_base;
-    pdl_wait();
+    pdl_begin();
 
     if (warp == 0) {
         // ------------------------------------------------------------- producer (warp-uniform, see the MMA issuer)
@@ -367,13 +367,38 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
 // atom layout of the tensor-core B operand, relative to the first slot of the row's work unit.
 // Same arithmetic as quantize_kernel (…tma_ext.cu:249-279).
 // ---------------------------------------------------------------------------------
+template <bool BATCHED>
 __global__ void __launch_bounds__(256)
 permute_quantize_kernel(const __nv_bfloat16* __restrict__ x, int M, int K, int T, int E, int has_shared, int tc_cap,
                         const int32_t* __restrict__ topk_ids, const int32_t* __restrict__ expert_map, Workspace ws) {
+    pdl_begin();
     const int bpr = K / SF_BLOCK;
     const long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= (long long)M * bpr) return;
     const int m = (int)(b / bpr), kb = (int)(b % bpr);
+    // Destinations of the row: one per routed pair plus the shared expert.  BATCHED (small launches, bound by
+    // load latency): all table reads of one level are issued together, three dependent round trips for the
+    // whole row instead of four per pair.  Large launches walk the pairs one by one with fewer registers.
+    constexpr int MAXJ = MAX_TOPK + 1;
+    int slot[BATCHED ? MAXJ : 1], ex[BATCHED ? MAXJ : 1], off[BATCHED ? MAXJ : 1], ub[BATCHED ? MAXJ : 1];
+    if (BATCHED) {
+#pragma unroll
+        for (int j = 0; j < MAXJ; ++j) {
+            slot[j] = -1; ex[j] = -1;
+            if (j < T) { slot[j] = ws.pair_slot[m * T + j]; ex[j] = topk_ids[m * T + j]; }
+        }
+        const int shared_base = has_shared ? ws.expert_offsets[E] : 0;
+        if (expert_map) {
+#pragma unroll
+            for (int j = 0; j < MAXJ; ++j) if (j < T && slot[j] >= 0) ex[j] = expert_map[ex[j]];
+        }
+#pragma unroll
+        for (int j = 0; j < MAXJ; ++j) {
+            if (j == T && has_shared) { slot[j] = shared_base + m; ex[j] = E; }
+            off[j] = 0; ub[j] = 0;
+            if (slot[j] >= 0) { off[j] = ws.expert_offsets[ex[j]]; ub[j] = ws.tc_unit_base[ex[j]]; }
+        }
+    }
     const uint4* src = reinterpret_cast<const uint4*>(x + b * SF_BLOCK);
     uint4 raw[2] = {src[0], src[1]};
     const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(raw);
@@ -393,23 +418,32 @@ permute_quantize_kernel(const __nv_bfloat16* __restrict__ x, int M, int K, int T
     // token-order copy (stage-wise checks and the GEMV path read it)
     reinterpret_cast<uint2*>(ws.act_q)[b] = make_uint2(lo, hi);
     ws.act_sf[b] = sb;
-    for (int j = 0; j <= T; ++j) {
-        int e, slot;
-        if (j < T) {
-            slot = ws.pair_slot[m * T + j];
-            if (slot < 0) continue;
-            e = topk_ids[m * T + j];
-            if (expert_map) e = expert_map[e];
-        } else {
-            if (!has_shared) break;
-            e = E;
-            slot = ws.expert_offsets[E] + m;
-        }
-        const int rank = slot - ws.expert_offsets[e];
-        const int unit = ws.tc_unit_base[e] + rank / tc_cap;
+    auto put = [&](int sl, int o, int u0) {
+        const int rank = sl - o;
+        const int unit = u0 + rank / tc_cap;
         const int r = rank % tc_cap;
-        reinterpret_cast<uint2*>(ws.act_q_sorted + (size_t)slot * (K / 2))[kb] = make_uint2(lo, hi);
+        reinterpret_cast<uint2*>(ws.act_q_sorted + (size_t)sl * (K / 2))[kb] = make_uint2(lo, hi);
         ws.act_sf_atoms[((size_t)unit * (K / 64) + (kb >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = sb;
+    };
+    if (BATCHED) {
+#pragma unroll
+        for (int j = 0; j < MAXJ; ++j)
+            if (slot[j] >= 0) put(slot[j], off[j], ub[j]);
+    } else {
+        for (int j = 0; j <= T; ++j) {
+            int e, sl;
+            if (j < T) {
+                sl = ws.pair_slot[m * T + j];
+                if (sl < 0) continue;
+                e = topk_ids[m * T + j];
+                if (expert_map) e = expert_map[e];
+            } else {
+                if (!has_shared) break;
+                e = E;
+                sl = ws.expert_offsets[E] + m;
+            }
+            put(sl, ws.expert_offsets[e], ws.tc_unit_base[e]);
+        }
     }
 }
 
@@ -482,8 +516,13 @@ int launch_permute_quantize(const vmoe_shape& s, const __nv_bfloat16* x, const i
                             int M, const Workspace& ws, cudaStream_t st) {
     const long long nblocks = (long long)M * (s.hidden / SF_BLOCK);
     if (nblocks == 0) return VMOE_OK;
-    permute_quantize_kernel<<<(unsigned)((nblocks + 255) / 256), 256, 0, st>>>(x, M, s.hidden, s.topk, s.num_experts,
-                                                                               s.has_shared, tc_unit_cap(s, M), ids, expert_map, ws);
+    const unsigned blocks = (unsigned)((nblocks + 255) / 256);
+    if (blocks <= 1024)
+        launch_pdl(permute_quantize_kernel<true>, blocks, 256u, 0, st, x, M, s.hidden, s.topk, s.num_experts,
+                                                              s.has_shared, tc_unit_cap(s, M), ids, expert_map, ws);
+    else
+        launch_pdl(permute_quantize_kernel<false>, blocks, 256u, 0, st, x, M, s.hidden, s.topk, s.num_experts,
+                                                               s.has_shared, tc_unit_cap(s, M), ids, expert_map, ws);
     return cuda_status(cudaGetLastError());
 }
 
@@ -534,7 +573,7 @@ static int launch_tc(const vmoe_shape& s, const WeightSet& routed, const WeightS
     const long long units_hint = min((long long)M * s.topk + (s.has_shared ? M : 0), (long long)max_tc_units(&s));
     long long grid = min((long long)tc_sm_count(), units_hint * p.tiles);
     if (grid < 1) grid = 1;
-    tc_gemm_kernel<NA, KS, UT><<<(unsigned)grid, TC_THREADS, smem, st>>>(p);
+    launch_pdl(tc_gemm_kernel<NA, KS, UT>, (unsigned)grid, (unsigned)TC_THREADS, smem, st, p);
     return cuda_status(cudaGetLastError());
 }
 

@@ -89,7 +89,7 @@ pf_kernel(const __grid_constant__ PfParams p) {
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = sh->tmem_base;
-    pdl_wait();
+    pdl_begin();
 
     if (warp == 0) {
         // ------------------------------------------------------------- producer (warp-uniform loop, one
@@ -383,7 +383,7 @@ static int launch_pf(const vmoe_shape& s, const WeightSet& routed, const WeightS
         if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
     (void)M;
-    pf_kernel<GU><<<(unsigned)tc_sm_count(), PF_THREADS, smem, st>>>(p);
+    launch_pdl(pf_kernel<GU>, (unsigned)tc_sm_count(), (unsigned)PF_THREADS, smem, st, p);
     return cuda_status(cudaGetLastError());
 }
 
