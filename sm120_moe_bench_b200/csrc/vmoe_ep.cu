@@ -84,32 +84,39 @@ __device__ __forceinline__ bool wait_flag(const int32_t* p, int32_t want) {
 // ---------------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024)
 ep_plan_kernel(const int32_t* __restrict__ topk_ids, int M, int T, int has_shared, EpDev ep) {
-    __shared__ int32_t s_warp[32];
-    __shared__ int32_t s_base;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __shared__ int32_t s_cnt[32][EP_MAX_RANKS];     // pairs per (warp, destination) in the current chunk
+    __shared__ int32_t s_base[EP_MAX_RANKS];        // pairs per destination in earlier chunks
+    pdl_begin();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     const int P = M * T + (has_shared ? M : 0);
-    for (int d = 0; d < ep.world; ++d) {
-        if (tid == 0) s_base = 0;
-        __syncthreads();
-        for (int p0 = 0; p0 < P; p0 += blockDim.x) {
-            const int p = p0 + tid;
-            int dest = -1;
-            if (p < P) dest = (p < M * T) ? topk_ids[p] / ep.e_local : ep.rank;
-            const bool mine = dest == d;
-            const unsigned bal = __ballot_sync(0xffffffffu, mine);
-            const int wcount = __popc(bal), wrank = __popc(bal & ((1u << lane) - 1u));
-            if (lane == 0) s_warp[warp] = wcount;
-            __syncthreads();
-            int wbase = 0, total = 0;
-            for (int w = 0; w < (int)(blockDim.x >> 5); ++w) { const int c = s_warp[w]; if (w < warp) wbase += c; total += c; }
-            if (mine) { ep.plan_dest[p] = d; ep.plan_pos[p] = s_base + wbase + wrank; }
-            __syncthreads();
-            if (tid == 0) s_base += total;
-            __syncthreads();
+    if (tid < ep.world) s_base[tid] = 0;
+    __syncthreads();
+    for (int p0 = 0; p0 < P; p0 += blockDim.x) {
+        const int p = p0 + tid;
+        int dest = -1;
+        if (p < P) dest = (p < M * T) ? topk_ids[p] / ep.e_local : ep.rank;
+        int wrank = 0;
+        for (int d = 0; d < ep.world; ++d) {
+            const unsigned bal = __ballot_sync(0xffffffffu, dest == d);
+            if (lane == 0) s_cnt[warp][d] = __popc(bal);
+            if (dest == d) wrank = __popc(bal & ((1u << lane) - 1u));
         }
-        if (tid == 0) ep.send_count[d] = s_base;
+        __syncthreads();
+        if (dest >= 0) {
+            int wbase = 0;
+            for (int w = 0; w < warp; ++w) wbase += s_cnt[w][dest];
+            ep.plan_dest[p] = dest;
+            ep.plan_pos[p] = s_base[dest] + wbase + wrank;
+        }
+        __syncthreads();
+        if (tid < ep.world) {
+            int total = 0;
+            for (int w = 0; w < nwarps; ++w) total += s_cnt[w][tid];
+            s_base[tid] += total;
+        }
         __syncthreads();
     }
+    if (tid < ep.world) ep.send_count[tid] = s_base[tid];
     if (tid == 0) *ep.ticket = 0;
 }
 
@@ -121,10 +128,22 @@ __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ topk_ids,
                    const float* __restrict__ topk_w, int M, int K, int T, int has_shared, EpDev ep,
                    int32_t* status) {
+    pdl_begin();
     const int bpr = K / SF_BLOCK;
     const long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (b < (long long)M * bpr) {
         const int m = (int)(b / bpr), kb = (int)(b % bpr);
+        // destinations of the row: all plan entries are requested at once, ahead of the arithmetic
+        constexpr int MAXJ = MAX_TOPK + 1;
+        int dst[MAXJ], pos[MAXJ];
+#pragma unroll
+        for (int j = 0; j < MAXJ; ++j) {
+            dst[j] = -1; pos[j] = 0;
+            if (j < T || (j == T && has_shared)) {
+                const int p = (j < T) ? m * T + j : M * T + m;
+                dst[j] = ep.plan_dest[p]; pos[j] = ep.plan_pos[p];
+            }
+        }
         const uint4* src = reinterpret_cast<const uint4*>(x + b * SF_BLOCK);
         uint4 raw[2] = {src[0], src[1]};
         const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(raw);
@@ -141,13 +160,13 @@ ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restric
         for (int i = 0; i < 8; ++i) lo |= e2m1_encode(div_scale(v[i])) << (4 * i);
 #pragma unroll
         for (int i = 0; i < 8; ++i) hi |= e2m1_encode(div_scale(v[8 + i])) << (4 * i);
-        for (int j = 0; j <= T; ++j) {
-            if (j == T && !has_shared) break;
+#pragma unroll
+        for (int j = 0; j < MAXJ; ++j) {
+            if (dst[j] < 0) continue;
+            if (pos[j] >= ep.capacity) { if (kb == 0) atomicExch(status, VMOE_ERR_LIMIT); continue; }
             const int p = (j < T) ? m * T + j : M * T + m;
-            const int d = ep.plan_dest[p], pos = ep.plan_pos[p];
-            if (pos >= ep.capacity) { if (kb == 0) atomicExch(status, VMOE_ERR_LIMIT); continue; }
-            uint8_t* slab = ep.slab[d];
-            const size_t row = (size_t)ep.rank * ep.capacity + pos;
+            uint8_t* slab = ep.slab[dst[j]];
+            const size_t row = (size_t)ep.rank * ep.capacity + pos[j];
             reinterpret_cast<uint2*>(slab + ep.L.recv_q + row * (K / 2))[kb] = make_uint2(lo, hi);
             (slab + ep.L.recv_sf + row * (K / 16))[kb] = sb;
             if (kb == 0) {
@@ -181,6 +200,7 @@ ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restric
 __global__ void __launch_bounds__(256)
 ep_gather_kernel(EpDev ep, int32_t* status) {
     __shared__ int s_ok;
+    pdl_begin();
     const EpFlags* f = reinterpret_cast<const EpFlags*>(ep.slab[ep.rank] + ep.L.flags);
     if (threadIdx.x == 0) s_ok = 1;
     __syncthreads();
@@ -205,6 +225,7 @@ ep_gather_kernel(EpDev ep, int32_t* status) {
 // ---------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 ep_permute_kernel(EpDev ep, int K, int tc_cap, Workspace ws) {
+    pdl_begin();
     const int bpr = K / SF_BLOCK;
     const long long total = (long long)ep.world * ep.capacity * bpr;
     const long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -229,6 +250,7 @@ ep_permute_kernel(EpDev ep, int K, int tc_cap, Workspace ws) {
 }
 
 __global__ void ep_signal_kernel(EpDev ep) {
+    pdl_begin();
     __threadfence_system();
     if (threadIdx.x < ep.world) {
         EpFlags* f = reinterpret_cast<EpFlags*>(ep.slab[threadIdx.x] + ep.L.flags);
@@ -241,6 +263,7 @@ __global__ void ep_signal_kernel(EpDev ep) {
 __global__ void __launch_bounds__(256)
 ep_combine_kernel(EpDev ep, int M, int K, int T, int has_shared, __nv_bfloat16* __restrict__ out, int32_t* status) {
     __shared__ int s_ok;
+    pdl_begin();
     const EpFlags* f = reinterpret_cast<const EpFlags*>(ep.slab[ep.rank] + ep.L.flags);
     if (threadIdx.x == 0) s_ok = 1;
     __syncthreads();
@@ -377,14 +400,14 @@ int vmoe_ep_forward(const vmoe_ep_ctx* ctx, const vmoe_shape* shape, const vmoe_
     const int has_shared = shape->has_shared ? 1 : 0;
 
     if ((rc = launch_route(router_logits, M, shape->num_global_experts, T, loc_ids, loc_w, st))) return rc;
-    ep_plan_kernel<<<1, 1024, 0, st>>>(loc_ids, M, T, has_shared, ep);
+    launch_pdl(ep_plan_kernel, 1u, 1024u, 0, st, loc_ids, M, T, has_shared, ep);
     {
         const long long nb = (long long)M * (K / SF_BLOCK);
         const unsigned grid = (unsigned)((nb + 255) / 256 > 0 ? (nb + 255) / 256 : 1);
-        ep_dispatch_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(hidden_bf16), loc_ids, loc_w, M, K, T,
-                                                 has_shared, ep, status);
+        launch_pdl(ep_dispatch_kernel, grid, 256u, 0, st, static_cast<const __nv_bfloat16*>(hidden_bf16), loc_ids, loc_w,
+                   M, K, T, has_shared, ep, status);
     }
-    ep_gather_kernel<<<64, 256, 0, st>>>(ep, status);
+    launch_pdl(ep_gather_kernel, 64u, 256u, 0, st, ep, status);
     const int Mr = (int)rows;
     // Tokens per work unit: the slab is sized for the worst case, so the choice is made from the rows a
     // rank receives under balanced routing (about its own M * (T + 1)), not from the slab capacity.
@@ -394,7 +417,7 @@ int vmoe_ep_forward(const vmoe_ep_ctx* ctx, const vmoe_shape* shape, const vmoe_
     if ((rc = launch_tables(lt, ep.flat_ids, ep.flat_w, nullptr, Mr, ws, st, cap, false))) return rc;
     {
         const long long nb = (long long)rows * (K / SF_BLOCK);
-        ep_permute_kernel<<<(unsigned)((nb + 255) / 256), 256, 0, st>>>(ep, K, cap, ws);
+        launch_pdl(ep_permute_kernel, (unsigned)((nb + 255) / 256), 256u, 0, st, ep, K, cap, ws);
     }
     const WeightSet r{routed->w13, routed->w13_sf, routed->w13_gs, routed->w2, routed->w2_sf, routed->w2_gs};
     const WeightSet sh = shape->has_shared ? WeightSet{shared->w13, shared->w13_sf, shared->w13_gs, shared->w2, shared->w2_sf, shared->w2_gs}
@@ -405,8 +428,8 @@ int vmoe_ep_forward(const vmoe_ep_ctx* ctx, const vmoe_shape* shape, const vmoe_
     ws.row_dst = ep.row_dst;
     if ((rc = launch_tc_gate_up(lk, r, sh, prep, Mr, ws, st, cap, Mr))) return rc;
     if ((rc = launch_tc_down(lk, r, sh, prep, Mr, ws, st, cap, Mr))) return rc;
-    ep_signal_kernel<<<1, 32, 0, st>>>(ep);
-    ep_combine_kernel<<<296, 256, 0, st>>>(ep, M, K, T, has_shared, static_cast<__nv_bfloat16*>(out_bf16), status);
+    launch_pdl(ep_signal_kernel, 1u, 32u, 0, st, ep);
+    launch_pdl(ep_combine_kernel, 296u, 256u, 0, st, ep, M, K, T, has_shared, static_cast<__nv_bfloat16*>(out_bf16), status);
     return cuda_status(cudaGetLastError());
 }
 
