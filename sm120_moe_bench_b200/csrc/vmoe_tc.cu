@@ -103,21 +103,28 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
         uint32_t g = 0;
         bool ok = true;
         long long prof_wait = 0;
-        // The queue pop and the unit record of the NEXT item are requested before the loads of
-        // the current one are issued, so their L2 round trips never stall the stream.
+        // The first item of a CTA is its block index, so its unit record is requested together with the
+        // unit count (no queue pop, no dependent round trip in front of the first copy); the queue hands
+        // out the items from gridDim.x on.  The pop and the unit record of the NEXT item are requested
+        // before the loads of the current one are issued.
         auto pop = [&]() -> long long {
             long long v = 0;
-            if (leader) v = atomicAdd(&p.ws.counters[p.queue], 1);
+            if (leader) v = (long long)atomicAdd(&p.ws.counters[p.queue], 1) + gridDim.x;
             return __shfl_sync(0xffffffffu, v, leader_lane);
         };
-        long long next = pop();
-        int4 next_u = (next < total) ? p.ws.tc_units[next / p.tiles] : make_int4(0, 0, 0, 8);
+        long long next = blockIdx.x;
+        int4 next_u = p.ws.tc_units[next / p.tiles];         // in range: the grid never exceeds (unit capacity) x tiles
+        if (next >= total) next_u = make_int4(0, 0, 0, 8);
+        // the expert's global scale travels to the epilogue with the item's last stage record; like the unit
+        // record it is requested one item ahead (after the current item's copies are out)
+        float next_alpha = (next_u.x >= p.E) ? p.gs_shared[0] : p.gs_routed[next_u.x];
         while (ok) {
             const long long item = next;
             if (item >= total) break;
             // unit-major order: consecutive items are the row tiles of one unit
             const int unit = (int)(item / p.tiles), tile = (int)(item % p.tiles);
             const int4 u = next_u;
+            const float alpha = next_alpha;
             next = pop();
             next_u = (next < total) ? p.ws.tc_units[next / p.tiles] : make_int4(0, 0, 0, 8);
             const bool shd = u.x >= p.E;
@@ -139,7 +146,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                 const uint32_t bytes = Cfg::NT * (TC_A_TILE + TC_SF_TILE) + KS * (nbox * TC_KB_BYTES + TC_SF_TILE);
                 const int kb0 = ks * KS;                       // first k-block of this stage
                 if (leader) {
-                    sh->info[slot] = TcStageInfo{u.x, u.y, u.z, nbox, tile, unit, ks, ks == steps - 1};
+                    sh->info[slot] = TcStageInfo{u.x, u.y, u.z, nbox, tile, unit, ks, ks == steps - 1, ks == steps - 1 ? alpha : 0.f, {0, 0, 0}};
                     mbar_arrive_expect_tx(&sh->full[slot], bytes);
                 }
 #pragma unroll
@@ -161,6 +168,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                 if (leader) bulk_g2s(st + Cfg::OFF_SFB, sfb_src, KS * TC_SF_TILE, &sh->full[slot]);
                 ++g;
             }
+            next_alpha = (next_u.x >= p.E) ? p.gs_shared[0] : p.gs_routed[next_u.x];
         }
         if (leader) {
             if (!ok) tc_timeout(p.ws, sh);
@@ -291,8 +299,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
             tc_fence_after();
             const TcStageInfo inf = sh->epi[buf];
             if (inf.expert < 0) break;
-            const bool shd = inf.expert >= p.E;
-            const float alpha = shd ? p.gs_shared[0] : p.gs_routed[inf.expert];
+            const float alpha = inf.alpha;
             const uint32_t tacc = tmem + ((uint32_t)(quad * 32) << 16) + buf * Cfg::ACC_STRIDE;
             if (NA == 2) {
                 const int n = inf.tile * TC_ROWS + row;       // intermediate index of this lane
@@ -304,6 +311,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {
                         const int t = c0 + c;
+                        if (t >= inf.ntok) break;                  // warp-uniform: columns past the unit's tokens hold nothing
                         const float gate = __uint_as_float(gr[c]) * alpha, up = __uint_as_float(ur[c]) * alpha;
                         const float sw = up * silu(gate);
                         float gm = fabsf(sw);
@@ -314,7 +322,7 @@ tc_gemm_kernel(const __grid_constant__ TcParams p) {
                         if (sc < 1e-30f) sc = 1e-30f;
                         const uint32_t nib = e2m1_encode(ScaleDivider(sc)(sw));
                         const uint32_t nb = __shfl_down_sync(0xffffffffu, nib, 1);
-                        if (t < inf.ntok) {
+                        {
                             const size_t srow = (size_t)(inf.slot0 + t);
                             if ((lane & 1) == 0) p.ws.inter_q[srow * (p.N / 2) + (n >> 1)] = (uint8_t)(nib | (nb << 4));
                             if ((lane & 15) == 0) p.ws.inter_sf[srow * (p.N / 16) + (n >> 4)] = sb;   // linear copy (stage checks)

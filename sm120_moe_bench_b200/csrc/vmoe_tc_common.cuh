@@ -18,7 +18,10 @@ constexpr int TC_SF_COL0 = 256;              // first TMEM column of the scale-f
 
 constexpr int TC_SMEM_BUDGET = 227 * 1024 - 3 * 1024;     // dynamic shared memory minus control block and alignment slack
 
-struct alignas(16) TcStageInfo { int expert, slot0, ntok, nbox, tile, unit, kb, last; };   // kb = step index within the item
+struct alignas(16) TcStageInfo {   // kb = step index within the item; alpha = the expert's global scale (valid on the last step)
+    int expert, slot0, ntok, nbox, tile, unit, kb, last;
+    float alpha; int pad[3];
+};
 
 // Role cycle counters are a development aid: compiled in only with -DVMOE_PROFILE (the debug read-out then
 // returns them; otherwise it returns zeros and the clock reads vanish from the kernels).
@@ -44,7 +47,7 @@ struct TcShared {
 // PTX wrappers
 // ---------------------------------------------------------------------------------
 // Stage record written by the producer lane and read by every lane of the MMA warp after the stage's
-// mbarrier completed: two 16-byte volatile loads.
+// mbarrier completed: three 16-byte volatile loads.
 __device__ __forceinline__ TcStageInfo ld_info(const TcStageInfo* src) {
     TcStageInfo r;
     const uint32_t a = smem_u32(src);
@@ -52,6 +55,8 @@ __device__ __forceinline__ TcStageInfo ld_info(const TcStageInfo* src) {
                  : "=r"(r.expert), "=r"(r.slot0), "=r"(r.ntok), "=r"(r.nbox) : "r"(a) : "memory");
     asm volatile("ld.volatile.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r.tile), "=r"(r.unit), "=r"(r.kb), "=r"(r.last) : "r"(a + 16) : "memory");
+    asm volatile("ld.volatile.shared.v4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(r.alpha), "=r"(r.pad[0]), "=r"(r.pad[1]), "=r"(r.pad[2]) : "r"(a + 32) : "memory");
     return r;
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
