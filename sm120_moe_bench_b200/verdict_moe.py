@@ -167,6 +167,16 @@ class _VerdictCommon:
             self._weights_key = key
         return self._weights
 
+    def process_weights_after_loading(self, layer) -> None:
+        """vLLM's per-backend hook, called once after the checkpoint is on the device.  Binds the layer's
+        ``w13_weight`` / ``w2_weight`` (checkpoint layout, linear block scales from the quant config) and builds
+        the 128-row scale atoms of the tensor-core kernels here, so that no forward call allocates."""
+        w1 = getattr(layer, "w13_weight", None)
+        w2 = getattr(layer, "w2_weight", None)
+        if w1 is None or w2 is None:
+            return
+        self._bind_weights(w1.data if hasattr(w1, "data") else w1, w2.data if hasattr(w2, "data") else w2)
+
     def _ensure_ws(self, m, topk, k, n_half, e_local, e_global, device):
         ws = self._ws
         if ws is None or ws.shape.max_tokens < m or ws.shape.topk != topk or ws.shape.hidden != k \

@@ -95,3 +95,15 @@ def test_classes_derive_from_vllm_bases_when_available():
     res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=600)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     assert "OK" in res.stdout or "NOVLLM" in res.stdout
+
+
+def test_vllm_backend_registration_without_editing_vllm():
+    """The reference patches vLLM's NVFP4 oracle as text (fused-moe/patches/nvfp4_oracle_verdict.py); the plug-in
+    makes the same changes in memory.  Runs in a child process so that this session keeps vLLM unloaded."""
+    import subprocess
+    import sys
+    env = dict(os.environ, VMOE_NO_VLLM="0", PYTHONPATH=ROOT)
+    res = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "vllm_plugin_check.py")],
+                         capture_output=True, text=True, env=env, timeout=900)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    assert "OK" in res.stdout or "NOVLLM" in res.stdout

@@ -145,3 +145,52 @@ def test_monolithic_router_logits_in(setup):
     with pytest.raises(ValueError):
         op.apply(hidden.cuda(), routed.w13, routed.w2, logits.cuda(), "SILU", cfg.num_experts, None, None, False,
                  num_expert_group=4)
+
+
+def test_apply_inside_cuda_graph_after_weight_hook(setup):
+    """What a serving engine does with the class: ``process_weights_after_loading`` once (binds the weights and
+    builds the scale atoms), one warm-up call (sizes the workspace), then ``apply`` captured in a CUDA graph and
+    replayed with new inputs in the same buffers.  Replays equal eager calls bit for bit and allocate nothing
+    (the buffer pre-allocation property of fused-moe/test_cuda_graph_safety.py:325-386)."""
+    vm, cfg, layer, routed = setup
+    import types
+
+    from oracle import moe as omoe
+    from sm120_moe_bench_b200 import synth
+    from sm120_moe_bench_b200.verdict_moe import VerdictMoEExperts
+    M = 4
+    op = VerdictMoEExperts(_MoeCfg(), _Quant(routed, "weight"))
+    op.alpha_convention = "weight"
+    op.kernel_path = 2
+    op.process_weights_after_loading(types.SimpleNamespace(w13_weight=routed.w13, w2_weight=routed.w2))
+    assert op._weights is not None and op._weights.w13_sf_atoms is not None
+    hidden = torch.zeros(M, cfg.hidden, dtype=torch.bfloat16, device="cuda")
+    wts = torch.zeros(M, cfg.topk, dtype=torch.float32, device="cuda")
+    ids = torch.zeros(M, cfg.topk, dtype=torch.int32, device="cuda")
+    out = torch.zeros(M, cfg.hidden, dtype=torch.bfloat16, device="cuda")
+    args = (out, hidden, routed.w13, routed.w2, wts, ids, "SILU", cfg.num_experts, None, None, None, None, None, None, False)
+
+    def load(seed):
+        h, logits = synth.make_inputs(cfg, M, seed=seed)
+        i, w = omoe.route(logits.numpy(), cfg.topk)
+        hidden.copy_(h.cuda()); ids.copy_(torch.from_numpy(i).cuda()); wts.copy_(torch.from_numpy(w).cuda())
+
+    load(1)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        op.apply(*args)                                   # warm-up on the capture stream: workspace, tensor maps
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        op.apply(*args)
+    for seed in (2, 3):
+        load(seed)
+        torch.cuda.synchronize()
+        before = torch.cuda.memory_allocated()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.cuda.memory_allocated() == before
+        replayed = out.clone()
+        op.apply(*args)
+        torch.cuda.synchronize()
+        assert torch.equal(out, replayed)
