@@ -186,6 +186,8 @@ def run_ours(args):
     from sm120_moe_bench_b200 import ops, synth
     from sm120_moe_bench_b200.verdict_moe import VerdictMoEMonolithic
 
+    if world > 1 and args.workload == "stack":
+        return run_stack_expert_parallel(args, world, rank, local, dev)
     if world > 1:
         return run_expert_parallel(args, world, rank, local, dev)
     if args.workload == "prefill":
@@ -201,7 +203,7 @@ def run_ours(args):
     path = 2 if args.path == "tc" else 1
     shape = vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, max(M, 1), has_shared=True, path=path)
     ws = vm.Workspace(shape, dev)
-    sets = [synth.make_inputs(cfg, M, seed=100 * rank + i, device=dev) for i in range(max(args.rotate, 1))]
+    sets = [synth.make_inputs(cfg, M, seed=100 * rank + i, device=dev, zipf_s=args.zipf) for i in range(max(args.rotate, 1))]
     out = torch.empty(M, cfg.hidden, dtype=torch.bfloat16, device=dev)
 
     def step(i):
@@ -481,6 +483,77 @@ def run_stack(args, dev):
     print(json.dumps(line), flush=True)
 
 
+def run_stack_expert_parallel(args, world, rank, local, dev):
+    """BASELINE config 5: ``--layers`` consecutive MoE layers (independent seeded weights, ``x <- x + moe(x)``)
+    at a decode batch of 32 tokens over all ranks (``--tokens`` per rank, default 32 / N), experts split over the
+    ranks, dispatch and combine as peer-memory kernels.  Reports the latency of one pass = per-token latency,
+    device-timed, max over ranks.  Eager launches: the exchange epoch is a kernel argument, so the pass is not
+    replayed from a CUDA graph."""
+    import torch
+    import torch.distributed as dist
+
+    from sm120_moe_bench_b200 import ep, ops, synth
+    cfg = synth.CONFIG_LARGE
+    M = args.tokens if args.tokens != 64 else max(32 // world, 1)
+    L = args.layers
+    first, per = ep.expert_partition(cfg.num_experts, world, rank)
+    moes = []
+    for li in range(L):
+        lay = synth.make_layer(cfg, seed=li, device=dev)                  # identical on every rank (same seed)
+        mine = ops.MoEWeights(*[t[first:first + per].contiguous() for t in lay["routed"]]).prepare()
+        shared = ops.MoEWeights(*lay["shared"]).prepare()
+        del lay
+        torch.cuda.empty_cache()
+        moes.append(ep.ExpertParallelMoE(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, mine, shared, max_local_tokens=M))
+    x0, _ = synth.make_inputs(cfg, M, seed=100 * rank, device=dev)
+    logits = [synth.make_inputs(cfg, M, seed=1000 + 100 * rank + li, device=dev)[1] for li in range(L)]
+    x = x0.clone()
+    y = torch.empty_like(x)
+
+    def one_pass():
+        x.copy_(x0)
+        for li in range(L):
+            moes[li].forward(x, logits[li], out=y)
+            x.add_(y)                                   # residual
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    for _ in range(max(args.warmup, 3)):
+        one_pass()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        one_pass()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    status = max(m.status() for m in moes)
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms, float(status)], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        ms = t[0].item()
+        line = {"metric": "moe_stack_latency_ms", "value": ms, "unit": "ms per pass (per-token latency)", "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": False,
+                "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4(w4a4)->f32", "data": "synthetic",
+                "config": {"workload": f"stack of MoE layers, config-2 shape, residual add, expert parallel over {world} GPUs "
+                                       "(BASELINE config 5), eager launches",
+                           "layers": L, "tokens_per_gpu": M, "tokens": M * world, "experts_per_gpu": per},
+                "us_per_layer": ms * 1e3 / L, "tokens_per_s": M * world / (ms * 1e-3), "clocks": clocks,
+                "device_status": int(t[1].item())}
+        print(json.dumps(line), flush=True)
+    for m in moes:
+        m.close()
+    dist.destroy_process_group()
+
+
 def run_expert_parallel(args, world, rank, local, dev):
     """N > 1: the same layer with its 512 experts split evenly over the ranks (64 per GPU at N = 8),
     every rank bringing ``--tokens`` tokens of its own (weak scaling); dispatch and combine run as
@@ -577,6 +650,7 @@ def run_expert_parallel(args, world, rank, local, dev):
         config = workload_config(M, world)
         config["parallelism"] = f"expert parallel over {world} GPUs ({per} routed experts per GPU, shared expert replicated), dispatch/combine as NVLink peer-memory kernels"
         config["kernel_path"] = "tc"
+        config["zipf_s"] = args.zipf
         line = {
             "metric": METRIC, "value": tokens_total / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
