@@ -434,13 +434,11 @@ def run_stack(args, dev):
     x0, _ = synth.make_inputs(cfg, M, seed=0, device=dev)
     logits = [synth.make_inputs(cfg, M, seed=1000 + li, device=dev)[1] for li in range(L)]
     x = x0.clone()
-    y = torch.empty_like(x)
-
     def one_pass():
         x.copy_(x0)
         for li in range(L):
-            vm.fused_moe(x, layers[li][0], ws, router_logits=logits[li], shared=layers[li][1], out=y)
-            x.add_(y)                                   # residual
+            # residual add fused into the combine kernel, in place: x <- x + moe(x)
+            vm.fused_moe(x, layers[li][0], ws, router_logits=logits[li], shared=layers[li][1], out=x, residual=x)
 
     one_pass()                                          # warm: tensor maps, attributes
     torch.cuda.synchronize()

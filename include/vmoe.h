@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define VMOE_ABI_VERSION 2
+#define VMOE_ABI_VERSION 3
 
 enum vmoe_status {
     VMOE_OK = 0,
@@ -166,6 +166,31 @@ int vmoe_forward(const vmoe_shape* shape, const vmoe_weights* routed,
                  const float* topk_weights, const int32_t* expert_map,
                  void* out_bf16, int32_t M, void* workspace, size_t workspace_bytes,
                  void* stream);
+
+/* Optional neighbours of the layer, fused around it (all pointers may be NULL = not used). */
+typedef struct vmoe_extras {
+    const void* gate_weight;     /* router matrix [num_global_experts, hidden]; logits = hidden @ gate_weight^T in
+                                    f32 on the device, then routed.  Used when router_logits, topk_ids are NULL.
+                                    Replaces moe_gate_distributed (fused-moe/csrc/megakernel_v1.cu:455-489). */
+    int32_t     gate_dtype;      /* 0 = f32 (the reference's type), 1 = bf16 */
+    const void* residual_bf16;   /* [M, hidden]: out = bf16(residual + bf16(layer output)), the residual add the
+                                    reference's whole-model kernel performs after the MoE block
+                                    (fused-moe/csrc/megakernel_v1.cu:1431-1505); may alias out_bf16 */
+} vmoe_extras;
+
+/* vmoe_forward with the optional neighbours above.  extras == NULL behaves exactly like vmoe_forward. */
+int vmoe_forward_ex(const vmoe_shape* shape, const vmoe_weights* routed,
+                    const vmoe_weights* shared, const void* hidden_bf16,
+                    const float* router_logits, const int32_t* topk_ids,
+                    const float* topk_weights, const int32_t* expert_map,
+                    void* out_bf16, int32_t M, void* workspace, size_t workspace_bytes,
+                    const vmoe_extras* extras, void* stream);
+
+/* Router projection alone: logits[M, E] (f32) = hidden[M, K] (bf16) @ gate_weight[E, K]^T, f32 accumulation in a
+ * fixed order (deterministic).  K a multiple of 256.  Replaces moe_gate_distributed
+ * (fused-moe/csrc/megakernel_v1.cu:455-489). */
+int vmoe_router_gemv(const void* hidden_bf16, const void* gate_weight, int32_t gate_dtype,
+                     int32_t M, int32_t K, int32_t E, float* logits, void* stream);
 
 /* Individual stages of vmoe_forward over an already built workspace (tables and
  * quantised activations present).  For stage-wise parity checks and per-kernel

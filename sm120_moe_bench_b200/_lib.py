@@ -40,6 +40,10 @@ class VmoeWsLayout(C.Structure):
     _fields_ = [(n, C.c_size_t) for n in _LAYOUT_FIELDS]
 
 
+class VmoeExtras(C.Structure):
+    _fields_ = [("gate_weight", C.c_void_p), ("gate_dtype", C.c_int32), ("residual_bf16", C.c_void_p)]
+
+
 # name -> (restype, argtypes); exactly the entry points of include/vmoe.h
 _P = C.c_void_p
 SIGNATURES = {
@@ -54,6 +58,9 @@ SIGNATURES = {
     "vmoe_dequantize": (C.c_int, [_P, _P, _P, C.c_int64, C.c_int32, C.c_int64, _P, _P]),
     "vmoe_forward": (C.c_int, [C.POINTER(VmoeShape), C.POINTER(VmoeWeights), C.POINTER(VmoeWeights),
                                _P, _P, _P, _P, _P, _P, C.c_int32, _P, C.c_size_t, _P]),
+    "vmoe_forward_ex": (C.c_int, [C.POINTER(VmoeShape), C.POINTER(VmoeWeights), C.POINTER(VmoeWeights),
+                                  _P, _P, _P, _P, _P, _P, C.c_int32, _P, C.c_size_t, C.POINTER(VmoeExtras), _P]),
+    "vmoe_router_gemv": (C.c_int, [_P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P]),
     "vmoe_stage_gate_up": (C.c_int, [C.POINTER(VmoeShape), C.POINTER(VmoeWeights), C.POINTER(VmoeWeights),
                                      C.c_int32, _P, _P]),
     "vmoe_stage_down": (C.c_int, [C.POINTER(VmoeShape), C.POINTER(VmoeWeights), C.POINTER(VmoeWeights),

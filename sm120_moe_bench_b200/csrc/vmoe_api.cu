@@ -283,17 +283,46 @@ int vmoe_forward(const vmoe_shape* shape, const vmoe_weights* routed, const vmoe
                  const void* hidden_bf16, const float* router_logits, const int32_t* topk_ids,
                  const float* topk_weights, const int32_t* expert_map, void* out_bf16, int32_t M,
                  void* workspace, size_t workspace_bytes, void* stream) {
+    return vmoe_forward_ex(shape, routed, shared, hidden_bf16, router_logits, topk_ids, topk_weights, expert_map,
+                           out_bf16, M, workspace, workspace_bytes, nullptr, stream);
+}
+
+int vmoe_router_gemv(const void* hidden_bf16, const void* gate_weight, int32_t gate_dtype,
+                     int32_t M, int32_t K, int32_t E, float* logits, void* stream) {
+    if (!hidden_bf16 || !gate_weight || !logits) return M == 0 ? VMOE_OK : VMOE_ERR_NULL;
+    if (M < 0) return VMOE_ERR_SHAPE;
+    if (!aligned16(hidden_bf16) || !aligned16(gate_weight)) return VMOE_ERR_ALIGN;
+    return launch_router_gemv(static_cast<const __nv_bfloat16*>(hidden_bf16), gate_weight, gate_dtype, M, K, E, logits,
+                              static_cast<cudaStream_t>(stream));
+}
+
+int vmoe_forward_ex(const vmoe_shape* shape, const vmoe_weights* routed, const vmoe_weights* shared,
+                    const void* hidden_bf16, const float* router_logits, const int32_t* topk_ids,
+                    const float* topk_weights, const int32_t* expert_map, void* out_bf16, int32_t M,
+                    void* workspace, size_t workspace_bytes, const vmoe_extras* extras, void* stream) {
     int rc = check_call(shape, routed, shared, M, workspace);
     if (rc) return rc;
     if (!hidden_bf16 || !out_bf16) return VMOE_ERR_NULL;
-    if (!router_logits && !(topk_ids && topk_weights)) return VMOE_ERR_NULL;
-    if (!aligned16(hidden_bf16) || !aligned16(out_bf16)) return VMOE_ERR_ALIGN;
+    const void* gate_weight = extras ? extras->gate_weight : nullptr;
+    const __nv_bfloat16* residual = extras ? static_cast<const __nv_bfloat16*>(extras->residual_bf16) : nullptr;
+    const bool own_logits = !router_logits && !(topk_ids && topk_weights) && gate_weight;
+    if (!router_logits && !(topk_ids && topk_weights) && !gate_weight) return VMOE_ERR_NULL;
+    if (!aligned16(hidden_bf16) || !aligned16(out_bf16) || (residual && !aligned16(residual))) return VMOE_ERR_ALIGN;
+    if (own_logits && !aligned16(gate_weight)) return VMOE_ERR_ALIGN;
+    if (own_logits && shape->num_global_experts > (shape->topk + 1) * shape->hidden) return VMOE_ERR_SHAPE;   // logits scratch
     if (workspace_bytes < vmoe_workspace_bytes(shape)) return VMOE_ERR_WORKSPACE;
     if (M == 0) return VMOE_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     Workspace ws;
     if ((rc = resolve_workspace(shape, workspace, &ws))) return rc;
     const WeightSet r = to_set(routed), sh = to_set(shape->has_shared ? shared : nullptr);
+    if (own_logits) {
+        // the logits live in the (still unused) down-projection output buffer until the router has read them
+        float* lg = ws.pair_out;
+        if ((rc = launch_router_gemv(static_cast<const __nv_bfloat16*>(hidden_bf16), gate_weight, extras->gate_dtype, M,
+                                     shape->hidden, shape->num_global_experts, lg, st))) return rc;
+        router_logits = lg;
+    }
     if (router_logits) {
         if ((rc = launch_route(router_logits, M, shape->num_global_experts, shape->topk, ws.topk_ids,
                                ws.topk_weights, st))) return rc;
@@ -315,7 +344,7 @@ int vmoe_forward(const vmoe_shape* shape, const vmoe_weights* routed, const vmoe
         if ((rc = launch_gate_up(*shape, r, sh, M, ws, st))) return rc;
         if ((rc = launch_down(*shape, r, sh, M, ws, st))) return rc;
     }
-    return launch_combine(*shape, M, ws, static_cast<__nv_bfloat16*>(out_bf16), st);
+    return launch_combine(*shape, M, ws, static_cast<__nv_bfloat16*>(out_bf16), st, residual);
 }
 
 int vmoe_read_status(void* workspace, const vmoe_shape* shape, void* stream) {

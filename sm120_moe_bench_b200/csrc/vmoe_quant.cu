@@ -75,7 +75,7 @@ template <bool BATCHED>
 __global__ void __launch_bounds__(256)
 combine_kernel(const float* __restrict__ pair_out, const int32_t* __restrict__ pair_slot,
                const int32_t* __restrict__ expert_offsets, int M, int K, int T, int E, int has_shared,
-               __nv_bfloat16* __restrict__ out) {
+               const __nv_bfloat16* residual, __nv_bfloat16* out) {      // residual may alias out
     pdl_begin();
     const int k4 = K / 4;
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -109,21 +109,98 @@ combine_kernel(const float* __restrict__ pair_out, const int32_t* __restrict__ p
         }
     }
     __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+    if (residual) {
+        // x + moe(x) with the layer output rounded to bf16 first: the same bits as a separate bf16 add
+        const uint2 r = reinterpret_cast<const uint2*>(residual + (size_t)m * K)[c];
+        const __nv_bfloat162 r0 = *reinterpret_cast<const __nv_bfloat162*>(&r.x), r1 = *reinterpret_cast<const __nv_bfloat162*>(&r.y);
+        lo = __floats2bfloat162_rn(__bfloat162float(r0.x) + __bfloat162float(lo.x), __bfloat162float(r0.y) + __bfloat162float(lo.y));
+        hi = __floats2bfloat162_rn(__bfloat162float(r1.x) + __bfloat162float(hi.x), __bfloat162float(r1.y) + __bfloat162float(hi.y));
+    }
     uint2 o; o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
     reinterpret_cast<uint2*>(out + (size_t)m * K)[c] = o;
 }
 
-int launch_combine(const vmoe_shape& s, int M, const Workspace& ws, __nv_bfloat16* out, cudaStream_t st) {
+int launch_combine(const vmoe_shape& s, int M, const Workspace& ws, __nv_bfloat16* out, cudaStream_t st,
+                   const __nv_bfloat16* residual) {
     const long long n = (long long)M * (s.hidden / 4);
     if (n == 0) return VMOE_OK;
     const unsigned blocks = (unsigned)((n + 255) / 256);
     if (blocks <= 4096)
         launch_pdl(combine_kernel<true>, blocks, 256u, 0, st,
-            ws.pair_out, ws.pair_slot, ws.expert_offsets, M, s.hidden, s.topk, s.num_experts, s.has_shared, out);
+            ws.pair_out, ws.pair_slot, ws.expert_offsets, M, s.hidden, s.topk, s.num_experts, s.has_shared, residual, out);
     else
         launch_pdl(combine_kernel<false>, blocks, 256u, 0, st,
-            ws.pair_out, ws.pair_slot, ws.expert_offsets, M, s.hidden, s.topk, s.num_experts, s.has_shared, out);
+            ws.pair_out, ws.pair_slot, ws.expert_offsets, M, s.hidden, s.topk, s.num_experts, s.has_shared, residual, out);
     return cuda_status(cudaGetLastError());
+}
+
+// ---------------------------------------------------------------------------------
+// Router projection: logits[m, e] = sum_k hidden[m, k] * gate_weight[e, k]  (f32 accumulation).
+// Follows moe_gate_distributed (fused-moe/csrc/megakernel_v1.cu:455-489): one dot product per (token,
+// expert).  One warp per expert and chunk of 8 tokens; a lane owns 8 consecutive k out of every 256 and
+// sums them in ascending order, then the 32 lane sums go through an xor-shuffle tree: a fixed order,
+// so the logits (and the routing that follows) are reproducible.
+// ---------------------------------------------------------------------------------
+constexpr int GEMV_TOK = 8;
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __bfloat162float(h[i]);
+}
+template <typename W>
+__global__ void __launch_bounds__(256)
+router_gemv_kernel(const __nv_bfloat16* __restrict__ x, const W* __restrict__ gw, int M, int K, int E, float* __restrict__ logits) {
+    pdl_begin();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e = blockIdx.x * 8 + warp;
+    const int m0 = blockIdx.y * GEMV_TOK;
+    if (e >= E) return;
+    float acc[GEMV_TOK];
+#pragma unroll
+    for (int t = 0; t < GEMV_TOK; ++t) acc[t] = 0.f;
+    for (int k = lane * 8; k < K; k += 256) {
+        float w[8];
+        load8(gw + (size_t)e * K + k, w);
+#pragma unroll
+        for (int t = 0; t < GEMV_TOK; ++t) {
+            if (m0 + t < M) {
+                float h[8];
+                load8(x + (size_t)(m0 + t) * K + k, h);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[t] = fmaf(h[i], w[i], acc[t]);
+            }
+        }
+    }
+#pragma unroll
+    for (int t = 0; t < GEMV_TOK; ++t) {
+#pragma unroll
+        for (int o = 16; o; o >>= 1) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], o);
+        if (lane == 0 && m0 + t < M) logits[(size_t)(m0 + t) * E + e] = acc[t];
+    }
+}
+
+int launch_router_gemv(const __nv_bfloat16* x, const void* gate_weight, int gate_dtype, int M, int K, int E,
+                       float* logits, cudaStream_t st) {
+    if (M == 0) return VMOE_OK;
+    if (K % 256 || E <= 0 || (gate_dtype != 0 && gate_dtype != 1)) return VMOE_ERR_SHAPE;
+    const dim3 grid((unsigned)((E + 7) / 8), (unsigned)((M + GEMV_TOK - 1) / GEMV_TOK));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cudaError_t err;
+    if (gate_dtype == 0)
+        err = cudaLaunchKernelEx(&cfg, router_gemv_kernel<float>, x, static_cast<const float*>(gate_weight), M, K, E, logits);
+    else
+        err = cudaLaunchKernelEx(&cfg, router_gemv_kernel<__nv_bfloat16>, x, static_cast<const __nv_bfloat16*>(gate_weight), M, K, E, logits);
+    return cuda_status(err != cudaSuccess ? err : cudaGetLastError());
 }
 
 }  // namespace vmoe

@@ -10,7 +10,7 @@ from dataclasses import dataclass
 import torch
 
 from . import _lib
-from ._lib import VmoeShape, VmoeWeights, VmoeWsLayout, check, lib
+from ._lib import VmoeExtras, VmoeShape, VmoeWeights, VmoeWsLayout, check, lib
 
 
 def _stream() -> int:
@@ -191,30 +191,57 @@ def fused_moe(hidden: torch.Tensor, weights: MoEWeights, ws: Workspace, *,
               router_logits: torch.Tensor | None = None,
               topk_ids: torch.Tensor | None = None, topk_weights: torch.Tensor | None = None,
               shared: MoEWeights | None = None, expert_map: torch.Tensor | None = None,
-              out: torch.Tensor | None = None) -> torch.Tensor:
+              out: torch.Tensor | None = None, gate_weight: torch.Tensor | None = None,
+              residual: torch.Tensor | None = None) -> torch.Tensor:
     """The fused NVFP4 MoE expert layer: bf16 hidden states + router logits (or pre-routed
-    ids / weights) + packed expert weights in, combined bf16 out."""
+    ids / weights, or the router matrix ``gate_weight [E, K]`` f32 / bf16 for the projection to run
+    on the device too) + packed expert weights in, combined bf16 out.  With ``residual`` the result
+    is ``residual + layer(hidden)`` (may be the same tensor as ``out``)."""
     _need(hidden, torch.bfloat16, "hidden")
     M, K = hidden.shape
     if out is None:
         out = torch.empty_like(hidden)
     else:
         _need(out, torch.bfloat16, "out")
+    extras = None
     if router_logits is not None:
         _need(router_logits, torch.float32, "router_logits")
+    elif gate_weight is not None and topk_ids is None:
+        if gate_weight.dtype not in (torch.float32, torch.bfloat16) or not gate_weight.is_contiguous():
+            raise TypeError("gate_weight must be a contiguous f32 or bf16 tensor [E, K]")
+        extras = VmoeExtras(gate_weight.data_ptr(), 0 if gate_weight.dtype == torch.float32 else 1, None)
     else:
         _need(topk_ids, torch.int32, "topk_ids")
         _need(topk_weights, torch.float32, "topk_weights")
+    if residual is not None:
+        _need(residual, torch.bfloat16, "residual")
+        if extras is None:
+            extras = VmoeExtras(None, 0, None)
+        extras.residual_bf16 = residual.data_ptr()
     if expert_map is not None:
         _need(expert_map, torch.int32, "expert_map")
     if ws.shape.has_shared and shared is None:
         raise ValueError("shape has a shared expert but no shared weights were given")
-    check(lib.vmoe_forward(C.byref(ws._cshape), C.byref(weights.cstruct()),
-                           C.byref(shared.cstruct()) if shared is not None else None,
-                           hidden.data_ptr(), _ptr(router_logits), _ptr(topk_ids), _ptr(topk_weights),
-                           _ptr(expert_map), out.data_ptr(), M, ws.buf.data_ptr(), ws.nbytes, _stream()),
-          "vmoe_forward")
+    check(lib.vmoe_forward_ex(C.byref(ws._cshape), C.byref(weights.cstruct()),
+                              C.byref(shared.cstruct()) if shared is not None else None,
+                              hidden.data_ptr(), _ptr(router_logits), _ptr(topk_ids), _ptr(topk_weights),
+                              _ptr(expert_map), out.data_ptr(), M, ws.buf.data_ptr(), ws.nbytes,
+                              C.byref(extras) if extras is not None else None, _stream()),
+          "vmoe_forward_ex")
     return out
+
+
+def router_gemv(hidden: torch.Tensor, gate_weight: torch.Tensor) -> torch.Tensor:
+    """``hidden [M, K] bf16 @ gate_weight [E, K]^T`` -> f32 logits ``[M, E]`` (fixed summation order)."""
+    _need(hidden, torch.bfloat16, "hidden")
+    if gate_weight.dtype not in (torch.float32, torch.bfloat16) or not gate_weight.is_contiguous():
+        raise TypeError("gate_weight must be a contiguous f32 or bf16 tensor [E, K]")
+    M, K = hidden.shape
+    E = gate_weight.shape[0]
+    logits = torch.empty(M, E, dtype=torch.float32, device=hidden.device)
+    check(lib.vmoe_router_gemv(hidden.data_ptr(), gate_weight.data_ptr(), 0 if gate_weight.dtype == torch.float32 else 1,
+                               M, K, E, logits.data_ptr(), _stream()), "vmoe_router_gemv")
+    return logits
 
 
 def run_stage(name: str, ws: Workspace, weights: MoEWeights, shared: MoEWeights | None, M: int,
