@@ -28,7 +28,7 @@ def _logits(M, E, seed, zipf=None):
 
 @pytest.mark.parametrize("M,E,T,zipf", [(4, 8, 2, None), (1, 512, 10, None), (64, 512, 10, None),
                                         (1536, 512, 10, 1.2), (8192, 512, 10, None), (33, 160, 6, None),
-                                        (7, 40, 16, None)])
+                                        (7, 40, 16, None), (9, 1000, 8, None), (5, 2048, 10, None)])
 def test_route_matches_oracle(vm, M, E, T, zipf):
     l = _logits(M, E, 1234 + M, zipf)
     assert omoe.route_ids_are_unambiguous(l.numpy(), T)
