@@ -36,7 +36,6 @@ __device__ __forceinline__ long long prof_clock() { return 0; }
 struct TcShared {
     uint64_t full[12], empty[12];
     uint64_t tmem_full[4], tmem_empty[4];
-    uint64_t sf_ready[12];                    // large-batch kernel: scale atoms of a stage are in TMEM
     TcStageInfo info[12];
     TcStageInfo epi[4];
     uint32_t tmem_base;

@@ -12,8 +12,11 @@
 //   pf_kernel<0> down:    B = 256 rows of w2; the epilogue scales by (router weight x alpha2) and
 //                stores 256 consecutive floats per token.
 // The scale atoms are the standard 128-row atoms of the weight matrices: two per k-step, copied to
-// eight consecutive TMEM columns.  The 256-column accumulator is single-buffered (the other half of
-// TMEM holds the scale columns), so eight epilogue warps (two per TMEM lane quadrant) drain it.
+// eight consecutive TMEM columns.  Roles per CTA (18 warps): producer (TMA), MMA issuer (scale copies and
+// MMAs), 16 epilogue warps (four per TMEM lane quadrant).  The 256-column accumulator is single-buffered
+// (the other half of TMEM holds the scale columns): each epilogue thread copies its 64 columns to
+// registers and hands the accumulator back before it does the arithmetic.  (A separate warp for the scale
+// copies was measured and changed nothing: the MMA warp's issue rate is not what bounds the kernel.)
 //
 // Same math as fused-moe/csrc/verdict_fused_cooperative_tma_ext.cu:323-538 of the reference; the
 // reference has no large-batch kernel (it loops token by token above 4 tokens,
@@ -26,8 +29,7 @@
 namespace vmoe {
 
 constexpr int PF_EPI_WARPS = 16;             // four per TMEM lane quadrant, 64 accumulator columns each
-constexpr int PF_SF_WARP = 2 + PF_EPI_WARPS;          // the warp after the epilogue warps copies scale atoms to TMEM
-constexpr int PF_THREADS = 96 + 32 * PF_EPI_WARPS;   // producer warp, MMA warp, epilogue warps, scale-copy warp
+constexpr int PF_THREADS = 64 + 32 * PF_EPI_WARPS;   // producer warp, MMA warp, epilogue warps
 constexpr int PF_N = 256;                    // weight rows per item (UMMA N)
 
 template <int GU> struct PfCfg {
@@ -38,8 +40,7 @@ template <int GU> struct PfCfg {
     static constexpr int OFF_B = TC_A_TILE;
     static constexpr int OFF_SFA = OFF_B + B_BYTES;
     static constexpr int OFF_SFB = OFF_SFA + TC_SF_TILE;
-    static constexpr int SF_COLS = 16 + 32;                          // per ring slot: one scale area per stage
-    static_assert(TC_SF_COL0 + STAGES * SF_COLS <= TC_TMEM_COLS, "scale columns do not fit");
+    static constexpr int SF_COLS = 16 + 32;
     static constexpr int NBUF = 1;
 };
 
@@ -78,7 +79,7 @@ pf_kernel(const __grid_constant__ PfParams p) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
     if (tid == 0) {
-        for (int i = 0; i < Cfg::STAGES; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], 1); mbar_init(&sh->sf_ready[i], 1); }
+        for (int i = 0; i < Cfg::STAGES; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], 1); }
         for (int i = 0; i < Cfg::NBUF; ++i) { mbar_init(&sh->tmem_full[i], 2); mbar_init(&sh->tmem_empty[i], PF_EPI_WARPS); }
         sh->abort_flag = 0;
         mbar_fence_init();
@@ -180,7 +181,7 @@ pf_kernel(const __grid_constant__ PfParams p) {
             while (true) {
                 const int slot = g % Cfg::STAGES;
                 const long long c0 = prof_clock();
-                if (!__all_sync(0xffffffffu, mbar_wait(&sh->sf_ready[slot], (g / Cfg::STAGES) & 1))) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait(&sh->full[slot], (g / Cfg::STAGES) & 1))) { ok = false; break; }
                 const long long c1 = prof_clock();
                 pw_full += c1 - c0;
                 tc_fence_after();
@@ -197,7 +198,19 @@ pf_kernel(const __grid_constant__ PfParams p) {
                 if (inf.expert < 0) { if (leader) sh->epi[0] = inf; end = true; break; }
                 const long long c2 = prof_clock();
                 const uint32_t st16 = smem16 + slot * (Cfg::STAGE_BYTES >> 4);
-                const uint32_t sfcol = tmem + TC_SF_COL0 + slot * Cfg::SF_COLS;
+                const uint32_t sfcol = tmem + TC_SF_COL0 + (g & 1) * Cfg::SF_COLS;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {    // token scales
+                    const uint64_t d = make_desc(st16 + ((Cfg::OFF_SFA + j * 512) >> 4), DESC_SF_HI);
+                    if (leader) tc_cp_sf(sfcol + j * 4, d);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {    // weight scales of k-step j: first tile -> columns +0..3, second -> +4..7
+                    const uint64_t d0 = make_desc(st16 + ((Cfg::OFF_SFB + j * 512) >> 4), DESC_SF_HI);
+                    const uint64_t d1 = make_desc(st16 + ((Cfg::OFF_SFB + TC_SF_TILE + j * 512) >> 4), DESC_SF_HI);
+                    if (leader) tc_cp_sf(sfcol + 16 + j * 8, d0);
+                    if (leader) tc_cp_sf(sfcol + 16 + j * 8 + 4, d1);
+                }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const uint64_t da = make_desc(st16 + ((j * 32) >> 4) + DESC_SW128_LBO, DESC_SW128_HI);
@@ -230,46 +243,12 @@ pf_kernel(const __grid_constant__ PfParams p) {
                 mbar_arrive(&sh->tmem_full[0]);
             }
         }
-    } else if (warp == PF_SF_WARP) {
-        // ------------------------------------------------------------- scale-copy warp: as soon as a stage has
-        // landed, its 12 scale atoms go from shared memory to the slot's TMEM columns (tcgen05.cp), and the
-        // commit tells the MMA warp.  Taking these 12 instructions per stage off the MMA warp roughly halves
-        // what that warp has to issue while it shares its scheduler with four busy epilogue warps.
-        const bool leader = elect_one();
-        const uint32_t smem16 = smem_u32(smem) >> 4;
-        uint32_t g = 0;
-        while (true) {
-            const int slot = g % Cfg::STAGES;
-            if (!__all_sync(0xffffffffu, mbar_wait(&sh->full[slot], (g / Cfg::STAGES) & 1))) {
-                if (leader) { tc_timeout(p.ws, sh); mbar_arrive(&sh->sf_ready[slot]); }
-                break;
-            }
-            tc_fence_after();
-            const TcStageInfo inf = ld_info(&sh->info[slot]);
-            if (inf.expert < 0) { if (leader) mbar_arrive(&sh->sf_ready[slot]); break; }     // end marker: pass it on
-            const uint32_t st16 = smem16 + slot * (Cfg::STAGE_BYTES >> 4);
-            const uint32_t sfcol = tmem + TC_SF_COL0 + slot * Cfg::SF_COLS;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {    // token scales
-                const uint64_t d = make_desc(st16 + ((Cfg::OFF_SFA + j * 512) >> 4), DESC_SF_HI);
-                if (leader) tc_cp_sf(sfcol + j * 4, d);
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {    // weight scales of k-step j: first tile -> columns +0..3, second -> +4..7
-                const uint64_t d0 = make_desc(st16 + ((Cfg::OFF_SFB + j * 512) >> 4), DESC_SF_HI);
-                const uint64_t d1 = make_desc(st16 + ((Cfg::OFF_SFB + TC_SF_TILE + j * 512) >> 4), DESC_SF_HI);
-                if (leader) tc_cp_sf(sfcol + 16 + j * 8, d0);
-                if (leader) tc_cp_sf(sfcol + 16 + j * 8 + 4, d1);
-            }
-            if (leader) tc_commit(&sh->sf_ready[slot]);
-            ++g;
-        }
     } else {
         // ------------------------------------------------------------- epilogue: one token row per thread,
         // four warps per TMEM lane quadrant.  Each thread copies its 64 accumulator columns to registers and
         // hands the accumulator back at once, so the next item's MMAs run under this item's arithmetic.
         const int quad = warp & 3;
-        const int sub = (warp - 2) >> 2;                    // which quarter of the columns (warps 2 .. 17)
+        const int sub = (warp - 2) >> 2;                    // which quarter of the columns
         const int t = quad * 32 + lane;                     // token row inside the unit
         uint32_t it = 0;
         long long pe_wait = 0, pe_work = 0, pe_ld = 0, pe_math = 0, pe_st = 0;

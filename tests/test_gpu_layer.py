@@ -235,3 +235,31 @@ def test_expert_parallel_halves_sum_to_whole(vm):
     torch.cuda.synchronize()
     err = (parts[0] + parts[1] - full).abs().max().item()
     assert err <= 2 ** -7 * full.abs().max().item()
+
+
+def test_back_to_back_calls_of_different_sizes_do_not_interfere(vm):
+    """Calls are queued without synchronisation, alternating batch sizes (and with them the small-unit,
+    64-token-unit and 128-token-unit kernels) over ONE workspace.  The kernels of consecutive calls overlap
+    their prologues (programmatic dependent launch), so each result is compared with the same call made
+    alone: bit-identical."""
+    from sm120_moe_bench_b200 import ops, synth
+    cfg = synth.LayerConfig("mid", 512, 256, 12, 3, True)
+    layer = synth.make_layer(cfg, seed=5)
+    routed = ops.MoEWeights(*[t.cuda() for t in layer["routed"]]).prepare()
+    shared = ops.MoEWeights(*[t.cuda() for t in layer["shared"]]).prepare()
+    sizes = [64, 1, 300, 7, 150, 2, 300, 33]
+    Mmax = max(sizes)
+    ws = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, Mmax, has_shared=True, path=2))
+    inputs = [tuple(t.cuda() for t in synth.make_inputs(cfg, M, seed=100 + i)) for i, M in enumerate(sizes)]
+    alone = []
+    for h, l in inputs:
+        alone.append(vm.fused_moe(h, routed, ws, router_logits=l, shared=shared).clone())
+        torch.cuda.synchronize()
+    for rep in range(3):
+        outs = [torch.empty_like(h) for h, _ in inputs]
+        for (h, l), o in zip(inputs, outs):
+            vm.fused_moe(h, routed, ws, router_logits=l, shared=shared, out=o)        # no synchronisation in between
+        torch.cuda.synchronize()
+        for o, a in zip(outs, alone):
+            assert torch.equal(o, a)
+    assert ws.status() == 0
