@@ -1,0 +1,325 @@
+// Device functions of the small stages of the layer (router, permutation tables, permuting activation
+// quantiser, combine), shared by their stand-alone kernels and by the fused small-batch kernel.
+//
+// Router semantics: fused-moe/csrc/megakernel_v1.cu:491-537 of the reference; permutation:
+// fused-moe/csrc/verdict_fused_grouped.cu:655-691; quantiser: fused-moe/csrc/verdict_fused_cooperative_tma_ext.cu
+// :249-279; combine: the same file, :549-563.
+#pragma once
+#include "vmoe_common.cuh"
+
+namespace vmoe {
+
+// One warp routes one token: p = the warp's E floats of shared memory, l = the token's logits.
+// fp32 softmax, T rounds of arg-max under (probability desc, expert id asc), renormalise.
+__device__ __forceinline__ void route_token(const float* l, float* p, int E, int T, int lane,
+                                            int32_t* ids_out, float* w_out) {
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) { float v = l[e]; p[e] = v; mx = fmaxf(mx, v); }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) { float v = expf(p[e] - mx); p[e] = v; sum += v; }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float inv = 1.0f / sum;
+    for (int e = lane; e < E; e += 32) p[e] *= inv;
+    __syncwarp();
+
+    float sel_w = 0.f; int sel_id = 0; float wsum = 0.f;   // lane j keeps the j-th selection
+    for (int j = 0; j < T; ++j) {
+        float bv = -1.0f; int bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) { float v = p[e]; if (v > bv) { bv = v; bi = e; } }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            int   oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == j) { sel_w = bv; sel_id = bi; }
+        if (lane == 0) p[bi] = -2.0f;            // taken
+        wsum += bv;                              // same value in every lane, rank order
+        __syncwarp();
+    }
+    const float winv = 1.0f / wsum;
+    if (lane < T) {
+        ids_out[lane] = sel_id;
+        w_out[lane] = sel_w * winv;
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// Permutation tables (see vmoe_route.cu for the description of the phases)
+// ---------------------------------------------------------------------------------
+struct TableArgs {
+    const int32_t* ids; const float* w; const int32_t* expert_map;
+    int M, T, E, has_shared, words;   // words = ceil(M / 32)
+    int tc_cap;                       // tokens per tensor-core unit
+    int gemv_units;                   // also emit the 4-token work units of the CUDA-core path
+    Workspace ws;
+};
+
+__device__ __forceinline__ int local_expert(const TableArgs& a, int p) {
+    int e = a.ids[p];
+    if (a.expert_map) e = a.expert_map[e];
+    return (e >= 0 && e < a.E) ? e : -1;
+}
+
+__device__ inline void phase_clear(const TableArgs& a, int tid, int nthr) {
+    const int n = a.E * a.words;
+    for (int i = tid; i < n; i += nthr) a.ws.bitmap[i] = 0u;
+    if (tid < CNT_N && tid != CNT_STATUS && tid != CNT_BARRIER) a.ws.counters[tid] = 0;
+}
+__device__ inline void phase_mark(const TableArgs& a, int tid, int nthr) {
+    const int P = a.M * a.T;
+    for (int p = tid; p < P; p += nthr) {
+        const int e = local_expert(a, p);
+        if (e >= 0) { const int m = p / a.T; atomicOr(&a.ws.bitmap[(size_t)e * a.words + (m >> 5)], 1u << (m & 31)); }
+    }
+}
+// Running popcount per bitmap word and the pair count per expert.  A warp takes 32 / wp experts at a
+// time (wp = words rounded up to a power of two) with a segmented shuffle scan over each expert's
+// words; experts with more than 32 words are walked 32 words at a time by a whole warp.
+__device__ inline void phase_count(const TableArgs& a, int warp, int nwarps, int lane, int32_t* s_count) {
+    if (a.words <= 32) {
+        int wp = 1;
+        while (wp < a.words) wp <<= 1;
+        const int gpw = 32 / wp, sub = lane / wp, wl = lane % wp;
+        for (int e0 = warp * gpw; e0 < a.E; e0 += nwarps * gpw) {
+            const int e = e0 + sub;
+            const bool valid = e < a.E && wl < a.words;
+            const int c = valid ? __popc(a.ws.bitmap[(size_t)e * a.words + wl]) : 0;
+            int incl = c;
+            for (int o = 1; o < wp; o <<= 1) { const int t = __shfl_up_sync(0xffffffffu, incl, o, wp); if (wl >= o) incl += t; }
+            if (valid) a.ws.word_prefix[(size_t)e * a.words + wl] = incl - c;
+            if (wl == wp - 1 && e < a.E) s_count[e] = incl;
+        }
+        return;
+    }
+    for (int e = warp; e < a.E; e += nwarps) {
+        int running = 0;
+        for (int w0 = 0; w0 < a.words; w0 += 32) {
+            const int w = w0 + lane;
+            const int c = (w < a.words) ? __popc(a.ws.bitmap[(size_t)e * a.words + w]) : 0;
+            int incl = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
+            if (w < a.words) a.ws.word_prefix[(size_t)e * a.words + w] = running + incl - c;
+            running += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) s_count[e] = running;
+    }
+}
+// single CTA: exclusive scan of counts -> expert_offsets, GEMV unit list, tensor-core unit list
+__device__ __forceinline__ int tc_box(int n) { return n <= 8 ? 8 : n <= 16 ? 16 : n <= 32 ? 32 : 64; }
+__device__ inline void phase_scan(const TableArgs& a, int tid, int nthr, const int32_t* s_count, int32_t* s_scan) {
+    // chunked serial-per-thread scan: thread i owns experts [i*per, (i+1)*per)
+    const int n = a.E + (a.has_shared ? 1 : 0);
+    const int per = (n + nthr - 1) / nthr;
+    int csum = 0, usum = 0, tsum = 0;
+    for (int k = 0; k < per; ++k) {
+        const int e = tid * per + k;
+        if (e < n) {
+            const int c = (e < a.E) ? s_count[e] : a.M;
+            csum += c; usum += (c + TOK_PER_UNIT - 1) / TOK_PER_UNIT; tsum += (c + a.tc_cap - 1) / a.tc_cap;
+        }
+    }
+    // two-level exclusive scan of the per-thread sums: inside each warp, then over the warp totals
+    const int lane = tid & 31, wid = tid >> 5, nw = (nthr + 31) >> 5;
+    int ci = csum, ui = usum, ti = tsum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int c2 = __shfl_up_sync(0xffffffffu, ci, o), u2 = __shfl_up_sync(0xffffffffu, ui, o), t2 = __shfl_up_sync(0xffffffffu, ti, o);
+        if (lane >= o) { ci += c2; ui += u2; ti += t2; }
+    }
+    if (lane == 31) { s_scan[wid] = ci; s_scan[32 + wid] = ui; s_scan[64 + wid] = ti; }
+    __syncthreads();
+    if (tid < 32) {
+        const int c0 = tid < nw ? s_scan[tid] : 0, u0 = tid < nw ? s_scan[32 + tid] : 0, t0 = tid < nw ? s_scan[64 + tid] : 0;
+        int cw = c0, uw = u0, tw = t0;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int c2 = __shfl_up_sync(0xffffffffu, cw, o), u2 = __shfl_up_sync(0xffffffffu, uw, o), t2 = __shfl_up_sync(0xffffffffu, tw, o);
+            if (tid >= o) { cw += c2; uw += u2; tw += t2; }
+        }
+        s_scan[tid] = cw - c0; s_scan[32 + tid] = uw - u0; s_scan[64 + tid] = tw - t0;     // exclusive warp bases
+        if (tid == 31) {
+            a.ws.counters[CNT_UNITS] = a.gemv_units ? uw : 0; a.ws.counters[CNT_SLOTS] = cw; a.ws.counters[CNT_TC_UNITS] = tw;
+            a.ws.expert_offsets[n] = cw;
+            if (!a.has_shared) a.ws.expert_offsets[n + 1] = cw;
+        }
+    }
+    __syncthreads();
+    int c = s_scan[wid] + ci - csum, u = s_scan[32 + wid] + ui - usum, t = s_scan[64 + wid] + ti - tsum;
+    for (int k = 0; k < per; ++k) {
+        const int e = tid * per + k;
+        if (e < n) {
+            const int cnt = (e < a.E) ? s_count[e] : a.M;
+            a.ws.expert_offsets[e] = c;
+            if (a.gemv_units)
+                for (int s = 0; s < cnt; s += TOK_PER_UNIT)
+                    a.ws.units[u++] = make_int4(e, c + s, min(TOK_PER_UNIT, cnt - s), 0);
+            if (a.ws.tc_units) {
+                a.ws.tc_unit_base[e] = t;
+                for (int s = 0; s < cnt; s += a.tc_cap) {
+                    const int nt = min(a.tc_cap, cnt - s);
+                    a.ws.tc_units[t++] = make_int4(e, c + s, nt, tc_box(nt));
+                }
+            }
+            c += cnt;
+        }
+    }
+}
+__device__ inline void phase_place(const TableArgs& a, int tid, int nthr) {
+    const int P = a.M * a.T;
+    for (int p = tid; p < P; p += nthr) {
+        const int e = local_expert(a, p);
+        int slot = -1;
+        if (e >= 0) {
+            const int m = p / a.T;
+            const size_t wi = (size_t)e * a.words + (m >> 5);
+            slot = a.ws.expert_offsets[e] + a.ws.word_prefix[wi] + __popc(a.ws.bitmap[wi] & ((1u << (m & 31)) - 1u));
+            a.ws.sorted_pair[slot] = p;
+            a.ws.gather_idx[slot] = m;
+            a.ws.scatter_weights[slot] = a.w[p];
+        }
+        a.ws.pair_slot[p] = slot;
+    }
+    if (a.has_shared) {
+        const int base = a.ws.expert_offsets[a.E];
+        for (int m = tid; m < a.M; m += nthr) {
+            a.ws.sorted_pair[base + m] = P + m;
+            a.ws.gather_idx[base + m] = m;
+            a.ws.scatter_weights[base + m] = 1.0f;
+        }
+    }
+}
+
+
+// Permuting activation quantiser for one 16-element block b of the token-major activations: quantise
+// (same arithmetic as quantize_kernel) and write the codes to the token-order copy and to every sorted slot
+// of the token, the block scale into the per-unit atom layout of the tensor-core B operand.
+template <bool BATCHED>
+__device__ __forceinline__ void permute_quantize_block(long long b, const __nv_bfloat16* __restrict__ x, int M, int K, int T, int E,
+                                                       int has_shared, int tc_cap, const int32_t* topk_ids,
+                                                       const int32_t* expert_map, const Workspace& ws) {
+    const int bpr = K / SF_BLOCK;
+    const int m = (int)(b / bpr), kb = (int)(b % bpr);
+    // Destinations of the row: one per routed pair plus the shared expert.  BATCHED (small launches, bound by
+    // load latency): all table reads of one level are issued together, three dependent round trips for the
+    // whole row instead of four per pair.  Large launches walk the pairs one by one with fewer registers.
+    constexpr int MAXJ = MAX_TOPK + 1;
+    int slot[BATCHED ? MAXJ : 1], ex[BATCHED ? MAXJ : 1], off[BATCHED ? MAXJ : 1], ub[BATCHED ? MAXJ : 1];
+    if (BATCHED) {
+#pragma unroll
+        for (int j = 0; j < MAXJ; ++j) {
+            slot[j] = -1; ex[j] = -1;
+            if (j < T) { slot[j] = ws.pair_slot[m * T + j]; ex[j] = topk_ids[m * T + j]; }
+        }
+        const int shared_base = has_shared ? ws.expert_offsets[E] : 0;
+        if (expert_map) {
+#pragma unroll
+            for (int j = 0; j < MAXJ; ++j) if (j < T && slot[j] >= 0) ex[j] = expert_map[ex[j]];
+        }
+#pragma unroll
+        for (int j = 0; j < MAXJ; ++j) {
+            if (j == T && has_shared) { slot[j] = shared_base + m; ex[j] = E; }
+            off[j] = 0; ub[j] = 0;
+            if (slot[j] >= 0) { off[j] = ws.expert_offsets[ex[j]]; ub[j] = ws.tc_unit_base[ex[j]]; }
+        }
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(x + b * SF_BLOCK);
+    uint4 raw[2] = {src[0], src[1]};
+    const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(raw);
+    float v[SF_BLOCK];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < SF_BLOCK; ++i) { v[i] = __bfloat162float(h[i]); amax = fmaxf(amax, fabsf(v[i])); }
+    const uint8_t sb = e4m3_encode(fmaxf(amax / 6.0f, 1e-30f));
+    float scale = e4m3_decode(sb);
+    if (scale < 1e-30f) scale = 1e-30f;
+    uint32_t lo = 0, hi = 0;
+    const ScaleDivider div_scale(scale);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) lo |= e2m1_encode(div_scale(v[i])) << (4 * i);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) hi |= e2m1_encode(div_scale(v[8 + i])) << (4 * i);
+    // token-order copy (stage-wise checks and the GEMV path read it)
+    reinterpret_cast<uint2*>(ws.act_q)[b] = make_uint2(lo, hi);
+    ws.act_sf[b] = sb;
+    auto put = [&](int sl, int o, int u0) {
+        const int rank = sl - o;
+        const int unit = u0 + rank / tc_cap;
+        const int r = rank % tc_cap;
+        reinterpret_cast<uint2*>(ws.act_q_sorted + (size_t)sl * (K / 2))[kb] = make_uint2(lo, hi);
+        ws.act_sf_atoms[((size_t)unit * (K / 64) + (kb >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = sb;
+    };
+    if (BATCHED) {
+#pragma unroll
+        for (int j = 0; j < MAXJ; ++j)
+            if (slot[j] >= 0) put(slot[j], off[j], ub[j]);
+    } else {
+        for (int j = 0; j <= T; ++j) {
+            int e, sl;
+            if (j < T) {
+                sl = ws.pair_slot[m * T + j];
+                if (sl < 0) continue;
+                e = topk_ids[m * T + j];
+                if (expert_map) e = expert_map[e];
+            } else {
+                if (!has_shared) break;
+                e = E;
+                sl = ws.expert_offsets[E] + m;
+            }
+            put(sl, ws.expert_offsets[e], ws.tc_unit_base[e]);
+        }
+    }
+}
+
+// out[m, 4c .. 4c+3] = bf16( sum_j pair_out[slot(m, j), :]  (ascending j, fp32)  + shared row ) [+ residual],
+// element i = m * (K / 4) + c.  BATCHED: slot numbers and then all rows requested at once (small launches).
+template <bool BATCHED>
+__device__ __forceinline__ void combine_element(long long i, const float* pair_out, const int32_t* pair_slot,
+                                                const int32_t* expert_offsets, int M, int K, int T, int E, int has_shared,
+                                                const __nv_bfloat16* residual, __nv_bfloat16* out) {
+    const int k4 = K / 4;
+    const int m = (int)(i / k4), c = (int)(i % k4);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (BATCHED) {
+        int slot[MAX_TOPK + 1];
+#pragma unroll
+        for (int j = 0; j < MAX_TOPK; ++j) slot[j] = (j < T) ? pair_slot[m * T + j] : -1;
+        slot[MAX_TOPK] = has_shared ? expert_offsets[E] + m : -1;
+        float4 v[MAX_TOPK + 1];
+#pragma unroll
+        for (int j = 0; j <= MAX_TOPK; ++j)
+            if (slot[j] >= 0) v[j] = __ldcg(reinterpret_cast<const float4*>(pair_out + (size_t)slot[j] * K) + c);   // L2: rows written by other SMs
+#pragma unroll
+        for (int j = 0; j <= MAX_TOPK; ++j)        // ascending pair order, shared expert last
+            if (slot[j] >= 0) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
+    } else {
+        for (int j = 0; j < T; ++j) {
+            const int slot = pair_slot[m * T + j];
+            if (slot >= 0) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(pair_out + (size_t)slot * K) + c);
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+        }
+        if (has_shared) {
+            const int slot = expert_offsets[E] + m;
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(pair_out + (size_t)slot * K) + c);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+    if (residual) {
+        // x + moe(x) with the layer output rounded to bf16 first: the same bits as a separate bf16 add
+        const uint2 r = reinterpret_cast<const uint2*>(residual + (size_t)m * K)[c];
+        const __nv_bfloat162 r0 = *reinterpret_cast<const __nv_bfloat162*>(&r.x), r1 = *reinterpret_cast<const __nv_bfloat162*>(&r.y);
+        lo = __floats2bfloat162_rn(__bfloat162float(r0.x) + __bfloat162float(lo.x), __bfloat162float(r0.y) + __bfloat162float(lo.y));
+        hi = __floats2bfloat162_rn(__bfloat162float(r1.x) + __bfloat162float(hi.x), __bfloat162float(r1.y) + __bfloat162float(hi.y));
+    }
+    uint2 o; o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
+    reinterpret_cast<uint2*>(out + (size_t)m * K)[c] = o;
+}
+
+}  // namespace vmoe

@@ -5,6 +5,7 @@
 // decoded scale floored at 1e-30 -> e2m1(x / scale), even element in the low nibble).
 // Combine: …tma_ext.cu:549-563 (fp32 sum over a token's pairs in ascending pair order -> bf16).
 #include "vmoe_common.cuh"
+#include "vmoe_phases.cuh"
 
 namespace vmoe {
 
@@ -77,47 +78,9 @@ combine_kernel(const float* __restrict__ pair_out, const int32_t* __restrict__ p
                const int32_t* __restrict__ expert_offsets, int M, int K, int T, int E, int has_shared,
                const __nv_bfloat16* residual, __nv_bfloat16* out) {      // residual may alias out
     pdl_begin();
-    const int k4 = K / 4;
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (long long)M * k4) return;
-    const int m = (int)(i / k4), c = (int)(i % k4);
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (BATCHED) {
-        int slot[MAX_TOPK + 1];
-#pragma unroll
-        for (int j = 0; j < MAX_TOPK; ++j) slot[j] = (j < T) ? pair_slot[m * T + j] : -1;
-        slot[MAX_TOPK] = has_shared ? expert_offsets[E] + m : -1;
-        float4 v[MAX_TOPK + 1];
-#pragma unroll
-        for (int j = 0; j <= MAX_TOPK; ++j)
-            if (slot[j] >= 0) v[j] = reinterpret_cast<const float4*>(pair_out + (size_t)slot[j] * K)[c];
-#pragma unroll
-        for (int j = 0; j <= MAX_TOPK; ++j)        // ascending pair order, shared expert last
-            if (slot[j] >= 0) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
-    } else {
-        for (int j = 0; j < T; ++j) {
-            const int slot = pair_slot[m * T + j];
-            if (slot >= 0) {
-                const float4 v = reinterpret_cast<const float4*>(pair_out + (size_t)slot * K)[c];
-                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-            }
-        }
-        if (has_shared) {
-            const int slot = expert_offsets[E] + m;
-            const float4 v = reinterpret_cast<const float4*>(pair_out + (size_t)slot * K)[c];
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-        }
-    }
-    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
-    if (residual) {
-        // x + moe(x) with the layer output rounded to bf16 first: the same bits as a separate bf16 add
-        const uint2 r = reinterpret_cast<const uint2*>(residual + (size_t)m * K)[c];
-        const __nv_bfloat162 r0 = *reinterpret_cast<const __nv_bfloat162*>(&r.x), r1 = *reinterpret_cast<const __nv_bfloat162*>(&r.y);
-        lo = __floats2bfloat162_rn(__bfloat162float(r0.x) + __bfloat162float(lo.x), __bfloat162float(r0.y) + __bfloat162float(lo.y));
-        hi = __floats2bfloat162_rn(__bfloat162float(r1.x) + __bfloat162float(hi.x), __bfloat162float(r1.y) + __bfloat162float(hi.y));
-    }
-    uint2 o; o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
-    reinterpret_cast<uint2*>(out + (size_t)m * K)[c] = o;
+    if (i >= (long long)M * (K / 4)) return;
+    combine_element<BATCHED>(i, pair_out, pair_slot, expert_offsets, M, K, T, E, has_shared, residual, out);
 }
 
 int launch_combine(const vmoe_shape& s, int M, const Workspace& ws, __nv_bfloat16* out, cudaStream_t st,

@@ -5,6 +5,7 @@
 // Permutation semantics: fused-moe/csrc/verdict_fused_grouped.cu:655-691 (stable sort of the
 // token-major pairs by expert id, expert offsets, gather indices, scatter weights).
 #include "vmoe_common.cuh"
+#include "vmoe_phases.cuh"
 
 namespace vmoe {
 
@@ -22,41 +23,7 @@ route_kernel(const float* __restrict__ logits, int M, int E, int T,
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m = blockIdx.x * ROUTE_WARPS + warp;
     if (m >= M) return;
-    float* p = s_prob + (size_t)warp * E;
-    const float* l = logits + (size_t)m * E;
-
-    float mx = -INFINITY;
-    for (int e = lane; e < E; e += 32) { float v = l[e]; p[e] = v; mx = fmaxf(mx, v); }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    float sum = 0.f;
-    for (int e = lane; e < E; e += 32) { float v = expf(p[e] - mx); p[e] = v; sum += v; }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    const float inv = 1.0f / sum;
-    for (int e = lane; e < E; e += 32) p[e] *= inv;
-    __syncwarp();
-
-    float sel_w = 0.f; int sel_id = 0; float wsum = 0.f;   // lane j keeps the j-th selection
-    for (int j = 0; j < T; ++j) {
-        float bv = -1.0f; int bi = 0x7fffffff;
-        for (int e = lane; e < E; e += 32) { float v = p[e]; if (v > bv) { bv = v; bi = e; } }
-#pragma unroll
-        for (int o = 16; o; o >>= 1) {
-            float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            int   oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-        }
-        if (lane == j) { sel_w = bv; sel_id = bi; }
-        if (lane == 0) p[bi] = -2.0f;            // taken
-        wsum += bv;                              // same value in every lane, rank order
-        __syncwarp();
-    }
-    const float winv = 1.0f / wsum;
-    if (lane < T) {
-        topk_ids[(size_t)m * T + lane] = sel_id;
-        topk_w[(size_t)m * T + lane] = sel_w * winv;
-    }
+    route_token(logits + (size_t)m * E, s_prob + (size_t)warp * E, E, T, lane, topk_ids + (size_t)m * T, topk_w + (size_t)m * T);
 }
 
 int launch_route(const float* logits, int M, int E, int T, int32_t* ids, float* w, cudaStream_t st) {
@@ -81,150 +48,6 @@ int launch_route(const float* logits, int M, int E, int T, int32_t* ids, float* 
 // The always-on shared expert is expert id E: slot range [offset[E], offset[E] + M),
 // pair index P + m, weight 1.0.
 // ---------------------------------------------------------------------------------
-struct TableArgs {
-    const int32_t* ids; const float* w; const int32_t* expert_map;
-    int M, T, E, has_shared, words;   // words = ceil(M / 32)
-    int tc_cap;                       // tokens per tensor-core unit
-    int gemv_units;                   // also emit the 4-token work units of the CUDA-core path
-    Workspace ws;
-};
-
-__device__ __forceinline__ int local_expert(const TableArgs& a, int p) {
-    int e = a.ids[p];
-    if (a.expert_map) e = a.expert_map[e];
-    return (e >= 0 && e < a.E) ? e : -1;
-}
-
-__device__ void phase_clear(const TableArgs& a, int tid, int nthr) {
-    const int n = a.E * a.words;
-    for (int i = tid; i < n; i += nthr) a.ws.bitmap[i] = 0u;
-    if (tid < CNT_N && tid != CNT_STATUS) a.ws.counters[tid] = 0;
-}
-__device__ void phase_mark(const TableArgs& a, int tid, int nthr) {
-    const int P = a.M * a.T;
-    for (int p = tid; p < P; p += nthr) {
-        const int e = local_expert(a, p);
-        if (e >= 0) { const int m = p / a.T; atomicOr(&a.ws.bitmap[(size_t)e * a.words + (m >> 5)], 1u << (m & 31)); }
-    }
-}
-// Running popcount per bitmap word and the pair count per expert.  A warp takes 32 / wp experts at a
-// time (wp = words rounded up to a power of two) with a segmented shuffle scan over each expert's
-// words; experts with more than 32 words are walked 32 words at a time by a whole warp.
-__device__ void phase_count(const TableArgs& a, int warp, int nwarps, int lane, int32_t* s_count) {
-    if (a.words <= 32) {
-        int wp = 1;
-        while (wp < a.words) wp <<= 1;
-        const int gpw = 32 / wp, sub = lane / wp, wl = lane % wp;
-        for (int e0 = warp * gpw; e0 < a.E; e0 += nwarps * gpw) {
-            const int e = e0 + sub;
-            const bool valid = e < a.E && wl < a.words;
-            const int c = valid ? __popc(a.ws.bitmap[(size_t)e * a.words + wl]) : 0;
-            int incl = c;
-            for (int o = 1; o < wp; o <<= 1) { const int t = __shfl_up_sync(0xffffffffu, incl, o, wp); if (wl >= o) incl += t; }
-            if (valid) a.ws.word_prefix[(size_t)e * a.words + wl] = incl - c;
-            if (wl == wp - 1 && e < a.E) s_count[e] = incl;
-        }
-        return;
-    }
-    for (int e = warp; e < a.E; e += nwarps) {
-        int running = 0;
-        for (int w0 = 0; w0 < a.words; w0 += 32) {
-            const int w = w0 + lane;
-            const int c = (w < a.words) ? __popc(a.ws.bitmap[(size_t)e * a.words + w]) : 0;
-            int incl = c;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) { int t = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += t; }
-            if (w < a.words) a.ws.word_prefix[(size_t)e * a.words + w] = running + incl - c;
-            running += __shfl_sync(0xffffffffu, incl, 31);
-        }
-        if (lane == 0) s_count[e] = running;
-    }
-}
-// single CTA: exclusive scan of counts -> expert_offsets, GEMV unit list, tensor-core unit list
-__device__ __forceinline__ int tc_box(int n) { return n <= 8 ? 8 : n <= 16 ? 16 : n <= 32 ? 32 : 64; }
-__device__ void phase_scan(const TableArgs& a, int tid, int nthr, const int32_t* s_count, int32_t* s_scan) {
-    // chunked serial-per-thread scan: thread i owns experts [i*per, (i+1)*per)
-    const int n = a.E + (a.has_shared ? 1 : 0);
-    const int per = (n + nthr - 1) / nthr;
-    int csum = 0, usum = 0, tsum = 0;
-    for (int k = 0; k < per; ++k) {
-        const int e = tid * per + k;
-        if (e < n) {
-            const int c = (e < a.E) ? s_count[e] : a.M;
-            csum += c; usum += (c + TOK_PER_UNIT - 1) / TOK_PER_UNIT; tsum += (c + a.tc_cap - 1) / a.tc_cap;
-        }
-    }
-    // two-level exclusive scan of the per-thread sums: inside each warp, then over the warp totals
-    const int lane = tid & 31, wid = tid >> 5, nw = (nthr + 31) >> 5;
-    int ci = csum, ui = usum, ti = tsum;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const int c2 = __shfl_up_sync(0xffffffffu, ci, o), u2 = __shfl_up_sync(0xffffffffu, ui, o), t2 = __shfl_up_sync(0xffffffffu, ti, o);
-        if (lane >= o) { ci += c2; ui += u2; ti += t2; }
-    }
-    if (lane == 31) { s_scan[wid] = ci; s_scan[32 + wid] = ui; s_scan[64 + wid] = ti; }
-    __syncthreads();
-    if (tid < 32) {
-        const int c0 = tid < nw ? s_scan[tid] : 0, u0 = tid < nw ? s_scan[32 + tid] : 0, t0 = tid < nw ? s_scan[64 + tid] : 0;
-        int cw = c0, uw = u0, tw = t0;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int c2 = __shfl_up_sync(0xffffffffu, cw, o), u2 = __shfl_up_sync(0xffffffffu, uw, o), t2 = __shfl_up_sync(0xffffffffu, tw, o);
-            if (tid >= o) { cw += c2; uw += u2; tw += t2; }
-        }
-        s_scan[tid] = cw - c0; s_scan[32 + tid] = uw - u0; s_scan[64 + tid] = tw - t0;     // exclusive warp bases
-        if (tid == 31) {
-            a.ws.counters[CNT_UNITS] = a.gemv_units ? uw : 0; a.ws.counters[CNT_SLOTS] = cw; a.ws.counters[CNT_TC_UNITS] = tw;
-            a.ws.expert_offsets[n] = cw;
-            if (!a.has_shared) a.ws.expert_offsets[n + 1] = cw;
-        }
-    }
-    __syncthreads();
-    int c = s_scan[wid] + ci - csum, u = s_scan[32 + wid] + ui - usum, t = s_scan[64 + wid] + ti - tsum;
-    for (int k = 0; k < per; ++k) {
-        const int e = tid * per + k;
-        if (e < n) {
-            const int cnt = (e < a.E) ? s_count[e] : a.M;
-            a.ws.expert_offsets[e] = c;
-            if (a.gemv_units)
-                for (int s = 0; s < cnt; s += TOK_PER_UNIT)
-                    a.ws.units[u++] = make_int4(e, c + s, min(TOK_PER_UNIT, cnt - s), 0);
-            if (a.ws.tc_units) {
-                a.ws.tc_unit_base[e] = t;
-                for (int s = 0; s < cnt; s += a.tc_cap) {
-                    const int nt = min(a.tc_cap, cnt - s);
-                    a.ws.tc_units[t++] = make_int4(e, c + s, nt, tc_box(nt));
-                }
-            }
-            c += cnt;
-        }
-    }
-}
-__device__ void phase_place(const TableArgs& a, int tid, int nthr) {
-    const int P = a.M * a.T;
-    for (int p = tid; p < P; p += nthr) {
-        const int e = local_expert(a, p);
-        int slot = -1;
-        if (e >= 0) {
-            const int m = p / a.T;
-            const size_t wi = (size_t)e * a.words + (m >> 5);
-            slot = a.ws.expert_offsets[e] + a.ws.word_prefix[wi] + __popc(a.ws.bitmap[wi] & ((1u << (m & 31)) - 1u));
-            a.ws.sorted_pair[slot] = p;
-            a.ws.gather_idx[slot] = m;
-            a.ws.scatter_weights[slot] = a.w[p];
-        }
-        a.ws.pair_slot[p] = slot;
-    }
-    if (a.has_shared) {
-        const int base = a.ws.expert_offsets[a.E];
-        for (int m = tid; m < a.M; m += nthr) {
-            a.ws.sorted_pair[base + m] = P + m;
-            a.ws.gather_idx[base + m] = m;
-            a.ws.scatter_weights[base + m] = 1.0f;
-        }
-    }
-}
-
 constexpr int TABLE_THREADS = 1024;
 
 // small problems: everything in one CTA
