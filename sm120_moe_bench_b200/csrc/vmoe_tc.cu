@@ -709,7 +709,7 @@ int launch_fused_small(const vmoe_shape& s, const WeightSet& routed, const Weigh
                        const float* logits, const int32_t* ids, const float* w, const int32_t* expert_map,
                        const __nv_bfloat16* x, const __nv_bfloat16* residual, __nv_bfloat16* out, int M,
                        const Workspace& ws, cudaStream_t st) {
-    static const bool enabled = []() { const char* e = getenv("VMOE_FUSED_SMALL"); return !(e && e[0] == '0'); }();
+    static const bool enabled = []() { const char* e = getenv("VMOE_FUSED_SMALL"); return e && e[0] == '1'; }();   // opt-in
     if (!enabled || M <= 0 || M > FUSED_SMALL_MAX_TOKENS || ws.row_dst) return -1;
     if (tc_unit_cap(s, M) != TC_UNIT_TOK_SMALL) return -1;
     FusedSmallParams fp;
