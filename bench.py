@@ -321,9 +321,7 @@ def run_ours(args):
     line = None
     if rank == 0:
         tokens_total = M * world * args.steps
-        # route, tables, quantise, gate_up, down, combine; up to 16 tokens on the tensor-core path: one fused launch
-        fused_small = path == 2 and M <= 16 and os.environ.get("VMOE_FUSED_SMALL", "0") == "1"
-        launches_per_step = 1 if fused_small else (6 if M * cfg.topk <= 16384 else 10)
+        launches_per_step = 6 if M * cfg.topk <= 16384 else 10   # route, tables (1 or 5), quantise, gate_up, down, combine
         line = {
             "metric": METRIC, "value": tokens_total / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,

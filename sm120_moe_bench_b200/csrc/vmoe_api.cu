@@ -325,14 +325,6 @@ int vmoe_forward_ex(const vmoe_shape* shape, const vmoe_weights* routed, const v
     }
     int path;
     if ((rc = pick_path(shape, routed, shared, &path))) return rc;
-    if (path == VMOE_PATH_TC) {
-        // small batches: the whole layer (router included) in one cooperative launch
-        rc = launch_fused_small(*shape, r, sh, to_prep(routed, shape->has_shared ? shared : nullptr),
-                                router_logits, topk_ids, topk_weights, expert_map,
-                                static_cast<const __nv_bfloat16*>(hidden_bf16), residual,
-                                static_cast<__nv_bfloat16*>(out_bf16), M, ws, st);
-        if (rc >= 0) return rc;
-    }
     if (router_logits) {
         if ((rc = launch_route(router_logits, M, shape->num_global_experts, shape->topk, ws.topk_ids,
                                ws.topk_weights, st))) return rc;

@@ -1,5 +1,5 @@
 // Device functions of the small stages of the layer (router, permutation tables, permuting activation
-// quantiser, combine), shared by their stand-alone kernels and by the fused small-batch kernel.
+// quantiser, combine), shared by their stand-alone kernels.
 //
 // Router semantics: fused-moe/csrc/megakernel_v1.cu:491-537 of the reference; permutation:
 // fused-moe/csrc/verdict_fused_grouped.cu:655-691; quantiser: fused-moe/csrc/verdict_fused_cooperative_tma_ext.cu
@@ -67,7 +67,7 @@ __device__ __forceinline__ int local_expert(const TableArgs& a, int p) {
 __device__ inline void phase_clear(const TableArgs& a, int tid, int nthr) {
     const int n = a.E * a.words;
     for (int i = tid; i < n; i += nthr) a.ws.bitmap[i] = 0u;
-    if (tid < CNT_N && tid != CNT_STATUS && tid != CNT_BARRIER) a.ws.counters[tid] = 0;
+    if (tid < CNT_N && tid != CNT_STATUS) a.ws.counters[tid] = 0;
 }
 __device__ inline void phase_mark(const TableArgs& a, int tid, int nthr) {
     const int P = a.M * a.T;

@@ -17,10 +17,8 @@
 #include "vmoe_tc_common.cuh"
 #include "vmoe_phases.cuh"
 
-#include <stdlib.h>
 #include <string.h>
 
-#include <algorithm>
 #include <mutex>
 #include <vector>
 
@@ -542,193 +540,6 @@ static int launch_tc(const vmoe_shape& s, const WeightSet& routed, const WeightS
     if (grid < 1) grid = 1;
     launch_pdl(tc_gemm_kernel<NA, KS, UT>, (unsigned)grid, (unsigned)TC_THREADS, smem, st, p);
     return cuda_status(cudaGetLastError());
-}
-
-// ---------------------------------------------------------------------------------
-// Small batches: the whole layer in ONE cooperative launch.  The phases are the device functions of the
-// separate kernels, run one after the other by the same 148 CTAs and separated by grid barriers instead
-// of kernel boundaries:
-//   router (one warp per token) | tables (CTA 0) | permuting quantiser | gate_up roles | down roles | combine
-// A grid barrier costs about a microsecond, a kernel boundary two to three plus the prologue and drain
-// of the next kernel (mbarrier init, TMEM allocation, descriptor fetch), so the six-kernel chain that
-// dominates a one-token step shrinks.  Barrier waits are bounded like every other wait in the library; the
-// launch is cooperative, so all CTAs are resident or the launch fails.
-// ---------------------------------------------------------------------------------
-struct FusedSmallParams {
-    TcParams gu, dn;
-    TableArgs tab;
-    const float* logits;             // NULL: pre-routed ids / weights (tab.ids / tab.w)
-    int E_global;
-    const __nv_bfloat16* x;
-    const __nv_bfloat16* residual;
-    __nv_bfloat16* out;
-    int32_t* barrier;                // grid barrier counter, zero at launch
-    int K;
-};
-
-__device__ __forceinline__ int32_t ld_acquire_gpu(const int32_t* p) {
-    int32_t v;
-    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-// All CTAs of the grid; the k-th barrier of a launch waits for k * gridDim.x arrivals.
-__device__ __forceinline__ void grid_barrier(int32_t* ctr, int target, int32_t* status) {
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence();
-        atomicAdd(ctr, 1);
-        const unsigned long long t0 = global_timer_ns();
-        for (uint32_t i = 1; ld_acquire_gpu(ctr) < target; ++i) {
-            if ((i & 63u) == 0 && global_timer_ns() - t0 > MBAR_WAIT_LIMIT_NS) { atomicExch(status, VMOE_ERR_TIMEOUT); break; }
-        }
-        __threadfence();
-    }
-    __syncthreads();
-    asm volatile("fence.proxy.async;" ::: "memory");     // what other CTAs wrote is about to be read by TMA
-}
-__device__ __forceinline__ void mbar_inval(uint64_t* bar) {
-    asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-template <int KSD, int UT>
-__global__ void __launch_bounds__(TC_THREADS, 1)
-fused_small_kernel(const __grid_constant__ FusedSmallParams fp) {
-    using CfgG = TcCfg<2, 1, UT>;
-    using CfgD = TcCfg<1, KSD, UT>;
-    constexpr size_t RING = (size_t)CfgG::STAGES * CfgG::STAGE_BYTES > (size_t)CfgD::STAGES * CfgD::STAGE_BYTES
-                                ? (size_t)CfgG::STAGES * CfgG::STAGE_BYTES : (size_t)CfgD::STAGES * CfgD::STAGE_BYTES;
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    TcShared* sh = reinterpret_cast<TcShared*>(smem + RING);        // same place for both GEMM phases
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nthr = blockDim.x;
-    const TableArgs& a = fp.tab;
-    int32_t* status = a.ws.counters + CNT_STATUS;
-    const int G = (int)gridDim.x;
-
-    if (tid == 0) tc_init_barriers<2, 1, UT>(sh);
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(TC_TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = sh->tmem_base;
-
-    // ---- router: one warp per token, probabilities in the (still unused) ring memory
-    if (fp.logits) {
-        const int m = blockIdx.x * (nthr >> 5) + warp;
-        if (m < a.M)
-            route_token(fp.logits + (size_t)m * fp.E_global, reinterpret_cast<float*>(smem) + (size_t)warp * fp.E_global,
-                        fp.E_global, a.T, lane, a.ws.topk_ids + (size_t)m * a.T, a.ws.topk_weights + (size_t)m * a.T);
-    }
-    grid_barrier(fp.barrier, 1 * G, status);
-    // ---- permutation tables: CTA 0, bitmap and popcounts in shared memory
-    if (blockIdx.x == 0) {
-        TableArgs t = a;
-        int32_t* s_mem = reinterpret_cast<int32_t*>(smem);
-        int32_t* s_count = s_mem; int32_t* s_scan = s_mem + t.E;
-        t.ws.bitmap = reinterpret_cast<uint32_t*>(s_scan + 3 * nthr);
-        t.ws.word_prefix = reinterpret_cast<int32_t*>(t.ws.bitmap + (size_t)t.E * t.words);
-        phase_clear(t, tid, nthr);       __syncthreads();
-        phase_mark(t, tid, nthr);        __syncthreads();
-        phase_count(t, warp, nthr >> 5, lane, s_count); __syncthreads();
-        phase_scan(t, tid, nthr, s_count, s_scan); __syncthreads();
-        phase_place(t, tid, nthr);
-    }
-    grid_barrier(fp.barrier, 2 * G, status);
-    // ---- permuting activation quantiser, spread over the grid
-    {
-        const long long nb = (long long)a.M * (fp.K / SF_BLOCK);
-        for (long long b = (long long)blockIdx.x * nthr + tid; b < nb; b += (long long)G * nthr)
-            permute_quantize_block<true>(b, fp.x, a.M, fp.K, a.T, a.E, a.has_shared, a.tc_cap, a.ids, a.expert_map, a.ws);
-    }
-    grid_barrier(fp.barrier, 3 * G, status);
-    // ---- gate_up
-    tc_roles<2, 1, UT>(fp.gu, smem, sh, tmem, warp, lane);
-    tc_fence_before();
-    grid_barrier(fp.barrier, 4 * G, status);
-    tc_fence_after();
-    // ---- down: the same mbarrier objects, re-initialised for the other ring geometry
-    if (tid == 0) {
-        for (int i = 0; i < CfgG::STAGES; ++i) { mbar_inval(&sh->full[i]); mbar_inval(&sh->empty[i]); }
-        for (int i = 0; i < CfgG::NBUF; ++i) { mbar_inval(&sh->tmem_full[i]); mbar_inval(&sh->tmem_empty[i]); }
-        tc_init_barriers<1, KSD, UT>(sh);
-    }
-    __syncthreads();
-    tc_roles<1, KSD, UT>(fp.dn, smem, sh, tmem, warp, lane);
-    tc_fence_before();
-    grid_barrier(fp.barrier, 5 * G, status);
-    tc_fence_after();
-    // ---- combine, spread over the grid
-    {
-        const long long n = (long long)a.M * (fp.K / 4);
-        for (long long i = (long long)blockIdx.x * nthr + tid; i < n; i += (long long)G * nthr)
-            combine_element<true>(i, a.ws.pair_out, a.ws.pair_slot, a.ws.expert_offsets, a.M, fp.K, a.T, a.E, a.has_shared,
-                                  fp.residual, fp.out);
-    }
-    __syncthreads();
-    if (warp == 1) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_TMEM_COLS) : "memory");
-    }
-}
-
-constexpr int FUSED_SMALL_MAX_TOKENS = 16;
-
-template <int KSD>
-static int launch_fused_small_t(const FusedSmallParams& fp, size_t smem_extra, cudaStream_t st) {
-    constexpr int UT = TC_UNIT_TOK_SMALL;
-    using CfgG = TcCfg<2, 1, UT>;
-    using CfgD = TcCfg<1, KSD, UT>;
-    const size_t ring = std::max((size_t)CfgG::STAGES * CfgG::STAGE_BYTES, (size_t)CfgD::STAGES * CfgD::STAGE_BYTES);
-    const size_t smem = ring + sizeof(TcShared) + 1024;
-    if (smem_extra > ring) return -1;
-    static bool attr_set[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-        if (cudaFuncSetAttribute(fused_small_kernel<KSD, UT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return VMOE_ERR_CUDA;
-        if (dev >= 0 && dev < 64) attr_set[dev] = true;
-    }
-    if (cudaMemsetAsync(fp.barrier, 0, sizeof(int32_t), st) != cudaSuccess) return VMOE_ERR_CUDA;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)tc_sm_count()); cfg.blockDim = dim3(TC_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeCooperative;
-    attr[0].val.cooperative = 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
-    const cudaError_t err = cudaLaunchKernelEx(&cfg, fused_small_kernel<KSD, UT>, fp);
-    return cuda_status(err != cudaSuccess ? err : cudaGetLastError());
-}
-
-// Returns VMOE_OK after launching, -1 when the call is not a small batch of the supported kind (the caller then
-// runs the separate kernels), or an error status.
-int launch_fused_small(const vmoe_shape& s, const WeightSet& routed, const WeightSet& shared, const PreparedSet& prep,
-                       const float* logits, const int32_t* ids, const float* w, const int32_t* expert_map,
-                       const __nv_bfloat16* x, const __nv_bfloat16* residual, __nv_bfloat16* out, int M,
-                       const Workspace& ws, cudaStream_t st) {
-    static const bool enabled = []() { const char* e = getenv("VMOE_FUSED_SMALL"); return e && e[0] == '1'; }();   // opt-in
-    if (!enabled || M <= 0 || M > FUSED_SMALL_MAX_TOKENS || ws.row_dst) return -1;
-    if (tc_unit_cap(s, M) != TC_UNIT_TOK_SMALL) return -1;
-    FusedSmallParams fp;
-    memset(&fp, 0, sizeof(fp));
-    int rc;
-    if ((rc = fill_tc_params<2>(s, routed, shared, prep, ws, -1, TC_UNIT_TOK_SMALL, &fp.gu))) return rc;
-    if ((rc = fill_tc_params<1>(s, routed, shared, prep, ws, -1, TC_UNIT_TOK_SMALL, &fp.dn))) return rc;
-    TableArgs& a = fp.tab;
-    a.tc_cap = TC_UNIT_TOK_SMALL; a.gemv_units = 0;
-    a.ids = logits ? ws.topk_ids : ids; a.w = logits ? ws.topk_weights : w; a.expert_map = expert_map;
-    a.M = M; a.T = s.topk; a.E = s.num_experts; a.has_shared = s.has_shared; a.words = (M + 31) / 32;
-    a.ws = ws;
-    fp.logits = logits; fp.E_global = s.num_global_experts; fp.x = x; fp.residual = residual; fp.out = out;
-    fp.barrier = ws.counters + CNT_BARRIER; fp.K = s.hidden;
-    // scratch the router and the tables take from the ring memory
-    const size_t scratch_route = logits ? (size_t)(TC_THREADS / 32) * s.num_global_experts * sizeof(float) : 0;
-    const size_t scratch_tab = ((size_t)a.E + 3 * TC_THREADS + 2 * (size_t)a.E * a.words) * sizeof(int32_t);
-    const size_t scratch = std::max(scratch_route, scratch_tab);
-    return (s.inter / 256) % 2 == 0 ? launch_fused_small_t<2>(fp, scratch, st) : launch_fused_small_t<1>(fp, scratch, st);
 }
 
 int launch_tc_gate_up(const vmoe_shape& s, const WeightSet& routed, const WeightSet& shared, const PreparedSet& prep,
