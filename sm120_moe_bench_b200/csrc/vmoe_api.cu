@@ -302,6 +302,7 @@ int vmoe_forward_ex(const vmoe_shape* shape, const vmoe_weights* routed, const v
                     void* workspace, size_t workspace_bytes, const vmoe_extras* extras, void* stream) {
     int rc = check_call(shape, routed, shared, M, workspace);
     if (rc) return rc;
+    if (M == 0) return VMOE_OK;                          // an empty batch may come with NULL data pointers
     if (!hidden_bf16 || !out_bf16) return VMOE_ERR_NULL;
     const void* gate_weight = extras ? extras->gate_weight : nullptr;
     const __nv_bfloat16* residual = extras ? static_cast<const __nv_bfloat16*>(extras->residual_bf16) : nullptr;
@@ -311,7 +312,6 @@ int vmoe_forward_ex(const vmoe_shape* shape, const vmoe_weights* routed, const v
     if (own_logits && !aligned16(gate_weight)) return VMOE_ERR_ALIGN;
     if (own_logits && shape->num_global_experts > (shape->topk + 1) * shape->hidden) return VMOE_ERR_SHAPE;   // logits scratch
     if (workspace_bytes < vmoe_workspace_bytes(shape)) return VMOE_ERR_WORKSPACE;
-    if (M == 0) return VMOE_OK;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     Workspace ws;
     if ((rc = resolve_workspace(shape, workspace, &ws))) return rc;
