@@ -180,7 +180,7 @@ class ExpertWeights:
 
 
 def expert_mlp(x_packed, x_sf, ew: ExpertWeights, e: int, accum: str = "f64",
-               return_inter: bool = False):
+               return_inter: bool = False, requant: dict | None = None):
     """One expert on already-quantised token rows: GEMM1 -> x alpha1 -> SwiGLU ->
     requantise -> GEMM2.  Returns the float32 GEMM2 sums ``[m, K]``; the caller
     multiplies them by ``router_weight * alpha2``.
@@ -198,7 +198,9 @@ def expert_mlp(x_packed, x_sf, ew: ExpertWeights, e: int, accum: str = "f64",
     gate = (acc[:, :N] * alpha1).astype(np.float32)
     up = (acc[:, N:] * alpha1).astype(np.float32)
     s = (up * silu(gate)).astype(np.float32)
-    s_packed, s_sf = nvfp4.quantize_act(s)
+    # requant: options of the intermediate quantiser (default: the device rules); the host harness of the
+    # reference uses tie="low", scale_round="ceil" (fused-moe/csrc/verdict_fused_independent.cu:474-496)
+    s_packed, s_sf = nvfp4.quantize_act(s, **(requant or {}))
     sq = nvfp4.dequantize(s_packed, s_sf)                      # [m, N]
     w2 = nvfp4.dequantize(ew.w2[e], ew.w2_sf[e])               # [K, N]
     y = _matmul_t(sq, w2, accum)                               # [m, K], alpha2 not applied

@@ -86,6 +86,23 @@ def e4m3_encode(x: np.ndarray) -> np.ndarray:
     return byte.astype(np.uint8)
 
 
+def e4m3_encode_ceil(x: np.ndarray) -> np.ndarray:
+    """float32 -> E4M3FN byte, rounded UP to the next representable magnitude: the block-scale encoder of the
+    reference's host harness (fused-moe/csrc/verdict_fused_independent.cu:73-84): ``x <= 0`` gives 0x08,
+    ``x >= 448`` gives 0x7E, otherwise the smallest representable value that is ``>= x``.  The device code
+    rounds to nearest instead (``e4m3_encode``); this variant exists to check the oracle against the compiled
+    host reference."""
+    x = np.asarray(x, dtype=np.float32)
+    codes = np.arange(0x7F, dtype=np.uint8)                      # 0x00 .. 0x7E, ascending values
+    values = e4m3_decode(codes)
+    idx = np.searchsorted(values, x, side="left")
+    idx = np.clip(idx, 0, 0x7E)
+    out = codes[idx]
+    out = np.where(x <= 0, np.uint8(0x08), out)
+    out = np.where(x >= np.float32(448.0), np.uint8(0x7E), out)
+    return out.astype(np.uint8)
+
+
 # --------------------------------------------------------------------------
 # E2M1
 # --------------------------------------------------------------------------
@@ -143,7 +160,7 @@ def unpack_nibbles(packed: np.ndarray) -> np.ndarray:
 # --------------------------------------------------------------------------
 # Block quantisers
 # --------------------------------------------------------------------------
-def quantize_act(x: np.ndarray, tie: str = "away", floor: float = 1e-30):
+def quantize_act(x: np.ndarray, tie: str = "away", floor: float = 1e-30, scale_round: str = "rne"):
     """Activation quantiser: float32 [..., K] -> (packed u8 [..., K/2], sf u8 [..., K/16]).
 
     fused-moe/csrc/verdict_fused_cooperative_tma_ext.cu:249-279 (prologue) and
@@ -155,7 +172,8 @@ def quantize_act(x: np.ndarray, tie: str = "away", floor: float = 1e-30):
 
     ``tie="low", floor=1e-12`` reproduces the reference's Python
     ``quantize_nvfp4`` (fused-moe/test_verdict_moe_ext.py:62-100) for inputs
-    whose block scales stay below 448.
+    whose block scales stay below 448.  ``tie="low", scale_round="ceil"`` reproduces the
+    host harness ``quantize_to_nvfp4_e4m3`` (fused-moe/csrc/verdict_fused_independent.cu:474-496).
     """
     x = np.asarray(x, dtype=np.float32)
     K = x.shape[-1]
@@ -164,7 +182,12 @@ def quantize_act(x: np.ndarray, tie: str = "away", floor: float = 1e-30):
     with np.errstate(invalid="ignore"):
         amax = np.max(np.abs(blocks), axis=-1)
     sf_target = np.maximum(amax / np.float32(6.0), np.float32(floor)).astype(np.float32)
-    sf = e4m3_encode(sf_target)
+    if scale_round == "rne":
+        sf = e4m3_encode(sf_target)
+    elif scale_round == "ceil":
+        sf = e4m3_encode_ceil(sf_target)
+    else:
+        raise ValueError(scale_round)
     scale = np.maximum(e4m3_decode(sf), np.float32(1e-30)).astype(np.float32)
     with np.errstate(over="ignore", invalid="ignore"):
         scaled = (blocks / scale[..., None]).astype(np.float32)
