@@ -39,7 +39,7 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rotate", type=int, default=4, help="distinct input sets cycled through")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--cpu-sample-tokens", type=int, default=2)
+    ap.add_argument("--cpu-sample-tokens", type=int, default=8)
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "stack"],
                     help="decode: BASELINE config 2 (default, the headline); prefill: config 3 (8192 tokens, "
                          "FP4 TFLOP/s); stack: config 5 shape on one GPU (15 layers, batch 32, CUDA graph)")
