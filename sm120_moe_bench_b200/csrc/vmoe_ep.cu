@@ -238,8 +238,8 @@ ep_permute_kernel(EpDev ep, int K, int tc_cap, Workspace ws) {
     const uint8_t sb = (slab + ep.L.recv_sf + (size_t)i * (K / 16))[kb];
     const int e = ep.flat_ids[i];
     const int rank_in_e = slot - ws.expert_offsets[e];
-    const int unit = ws.tc_unit_base[e] + rank_in_e / tc_cap;
-    const int r = rank_in_e % tc_cap;
+    const int unit = ws.tc_unit_base[e] + (rank_in_e >> (31 - __clz(tc_cap)));     // tc_cap is 16, 64 or 128
+    const int r = rank_in_e & (tc_cap - 1);
     reinterpret_cast<uint2*>(ws.act_q_sorted + (size_t)slot * (K / 2))[kb] = q;
     ws.act_sf_atoms[((size_t)unit * (K / 64) + (kb >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = sb;
     if (kb == 0) {

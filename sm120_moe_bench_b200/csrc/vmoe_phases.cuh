@@ -203,6 +203,7 @@ __device__ __forceinline__ void permute_quantize_block(long long b, const __nv_b
                                                        int has_shared, int tc_cap, const int32_t* topk_ids,
                                                        const int32_t* expert_map, const Workspace& ws) {
     const int bpr = K / SF_BLOCK;
+    const int cap_shift = 31 - __clz(tc_cap);
     const int m = (int)(b / bpr), kb = (int)(b % bpr);
     // Destinations of the row: one per routed pair plus the shared expert.  BATCHED (small launches, bound by
     // load latency): all table reads of one level are issued together, three dependent round trips for the
@@ -248,8 +249,8 @@ __device__ __forceinline__ void permute_quantize_block(long long b, const __nv_b
     ws.act_sf[b] = sb;
     auto put = [&](int sl, int o, int u0) {
         const int rank = sl - o;
-        const int unit = u0 + rank / tc_cap;
-        const int r = rank % tc_cap;
+        const int unit = u0 + (rank >> cap_shift);          // tc_cap is 16, 64 or 128
+        const int r = rank & (tc_cap - 1);
         reinterpret_cast<uint2*>(ws.act_q_sorted + (size_t)sl * (K / 2))[kb] = make_uint2(lo, hi);
         ws.act_sf_atoms[((size_t)unit * (K / 64) + (kb >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = sb;
     };
