@@ -381,7 +381,7 @@ def run_ours(args):
     line = None
     if rank == 0:
         tokens_total = M * world * args.steps
-        launches_per_step = 6 if M * cfg.topk <= 16384 else 10   # route, tables (1 or 5), quantise, gate_up, down, combine
+        launches_per_step = 6 if M * cfg.topk <= 4096 else 10   # route, tables (1 or 5), quantise, gate_up, down, combine
         line = {
             "metric": METRIC, "value": tokens_total / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,

@@ -88,7 +88,7 @@ int launch_combine(const vmoe_shape& s, int M, const Workspace& ws, __nv_bfloat1
     const long long n = (long long)M * (s.hidden / 4);
     if (n == 0) return VMOE_OK;
     const unsigned blocks = (unsigned)((n + 255) / 256);
-    if (blocks <= 4096)
+    if (blocks <= 1024)
         launch_pdl(combine_kernel<true>, blocks, 256u, 0, st,
             ws.pair_out, ws.pair_slot, ws.expert_offsets, M, s.hidden, s.topk, s.num_experts, s.has_shared, residual, out);
     else

@@ -99,7 +99,7 @@ int launch_tables(const vmoe_shape& s, const int32_t* ids, const float* w, const
         cudaFuncSetAttribute(tables_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         attr_done = true;
     }
-    if ((long long)M * s.topk <= 16384) {
+    if ((long long)M * s.topk <= 4096) {      // one CTA up to ~4 k pairs, grid-wide phases above
         launch_pdl(tables_fused_kernel, 1u, (unsigned)TABLE_THREADS, in_smem ? smem_tab : smem, st, a, in_smem ? 1 : 0);
     } else {
         const int blocks = 296;
