@@ -13,16 +13,16 @@ int max_units(const vmoe_shape* s) {
     return (int)(s->num_experts + 1 + (P + TOK_PER_UNIT - 1) / TOK_PER_UNIT);
 }
 
-// Units carry at most 16 tokens while the batch averages <= 12 tokens per expert (memory-bound:
-// a small token tile leaves shared memory for a deeper weight ring; the few experts above 16 tokens
-// are split and re-read through L2), 128 from 32 tokens per expert on (token-major tiles,
-// compute-bound), else 64.
-constexpr long long TC_SMALL_PER_EXPERT = 12;
+// Units carry at most 16 tokens while the batch averages <= 7 tokens per expert (weights-as-rows kernel: a
+// small token tile leaves shared memory for a deeper weight ring; the few experts above 16 tokens are split
+// and re-read through L2) and 128 tokens above (token-major kernel).  The crossover was measured: the
+// token-major kernel is ahead from about 350 tokens of the 512-expert top-10 layer on, and far ahead of
+// 64-token units of the weights-as-rows kernel everywhere in between (0.79 against 0.58 of the HBM roofline
+// at 1536 tokens).
+constexpr long long TC_SMALL_PER_EXPERT = 7;
 int tc_unit_cap(const vmoe_shape& s, int M) {
     const long long pairs = (long long)M * s.topk;
-    if (pairs <= TC_SMALL_PER_EXPERT * s.num_experts) return TC_UNIT_TOK_SMALL;
-    if (pairs >= 32LL * s.num_experts) return TC_UNIT_TOK_PREFILL;
-    return TC_UNIT_TOK;
+    return pairs <= TC_SMALL_PER_EXPERT * s.num_experts ? TC_UNIT_TOK_SMALL : TC_UNIT_TOK_PREFILL;
 }
 
 int max_tc_units(const vmoe_shape* s) {
