@@ -1,21 +1,32 @@
 #!/usr/bin/env python3
-"""Benchmark of the fused NVFP4 MoE expert layer (decode, large-MoE shape).
+"""Benchmark of the fused NVFP4 MoE expert layer (hidden 4096, 512 routed experts top-10 + 1 shared expert,
+intermediate 1024, NVFP4 weights from seed 0).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens M] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--tokens M] [--impl ours|reference] [--workload ...]
 
-One "step" is one pass of the layer over one batch of M synthetic tokens (hidden 4096, 512 routed
-experts top-10 + 1 shared expert, intermediate 1024, NVFP4 weights from seed 0).  Prints ONE JSON
-line (rank 0).  ``value`` is tokens/s with inputs resident in HBM, timed with CUDA events;
-``e2e`` is the same metric through the operator class with host (pinned) buffers, host<->device
-copies inside the timed region; ``roofline`` is the gate_up kernel's algorithmic bytes over its
-own event-timed launch duration against the measured HBM copy bandwidth; ``cpu_baseline`` is the
-CPU oracle (torch dequantise-then-matmul, all host threads) timed on a bounded sample.
+One "step" is one pass of the layer over one batch of M synthetic tokens.  Prints ONE JSON line (rank 0).
+
+* ``value``: tokens/s of the 64-token decode batch with inputs resident in HBM, timed with CUDA events.  The timed
+  loop of exactly ``--steps`` steps is repeated until at least half a second of device time has passed; the
+  median repeat is reported (``repeats``) and the clocks are sampled over all of them.
+* ``e2e``: the same metric through the operator class with host (pinned) buffers, host<->device copies inside the
+  timed region.
+* ``roofline``: the gate_up kernel's algorithmic bytes over its own event-timed launch against the measured HBM
+  copy bandwidth; ``sweep``: the same figures for decode batches 1, 4, 16, 64; ``prefill``: 8192 tokens, uniform and
+  Zipf(1.2) routing, FP4 TFLOP/s and the HBM fraction beside it.
+* ``parity``: three token rows of the timed batch against the CPU oracle (untimed).
+* ``cpu_baseline``: the reference's compiled host C++ path (``oracle/_ref``) or, where that library is absent, the
+  numpy / torch-CPU restatement (``oracle/``), timed on a bounded sample on this machine's host cores.
+* N > 1 (torchrun): the experts are split over the ranks, every rank brings ``--tokens`` tokens, dispatch and
+  combine run as NVLink peer-memory kernels; the line carries the bit-identity check against the single-GPU layer
+  and the strong-scaling comparison (all tokens on one GPU).
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
+import statistics
 import subprocess
 import sys
 import threading
@@ -28,6 +39,12 @@ os.environ.setdefault("VMOE_NO_VLLM", "1")   # the operator classes do not need 
 METRIC = "moe_layer_decode_tokens_per_s"
 UNIT = "tokens/s"
 FALLBACK_HBM_GBS = 6650.0
+NOMINAL_FP4_TFLOPS = 9000.0     # dense FP4, B200 data sheet
+MIN_TIMED_SECONDS = 0.5
+# DRAM bytes per launch of the gate_up kernel over its algorithmic bytes, from one ncu capture at batch 16
+# (dram__bytes_read.sum + dram__bytes_write.sum); traffic grows with the number of distinct experts like the
+# algorithmic bytes do, so the ratio is applied to other batch sizes.  An estimate, labelled as such in the line.
+TRAFFIC_RATIO = {"tc": 1.044, "gemv": 1.048}
 
 
 def parse():
@@ -39,11 +56,15 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rotate", type=int, default=4, help="distinct input sets cycled through")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true", help="decode: skip the batch sweep and the prefill sub-records")
     ap.add_argument("--cpu-sample-tokens", type=int, default=8)
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "stack"],
                     help="decode: BASELINE config 2 (default, the headline); prefill: config 3 (8192 tokens, "
-                         "FP4 TFLOP/s); stack: config 5 shape on one GPU (15 layers, batch 32, CUDA graph)")
-    ap.add_argument("--zipf", type=float, default=None, help="prefill: Zipf exponent of the routing bias (1.2 = skewed variant)")
+                         "FP4 TFLOP/s); stack: config 5 (15 layers, batch 32, one CUDA graph per rank)")
+    ap.add_argument("--zipf", type=float, default=None, help="Zipf exponent of the routing bias (1.2 = skewed variant)")
+    ap.add_argument("--mtp-corr", type=float, default=0.0,
+                    help="expert parallel: groups of 6 tokens are the positions of one sequence and share this "
+                         "fraction of their logits (0.98 gives the reference's ~71 %% adjacent-token expert reuse)")
     ap.add_argument("--layers", type=int, default=15)
     ap.add_argument("--path", default="tc", choices=["tc", "gemv"],
                     help="tc: tcgen05 block-scaled path (default); gemv: CUDA-core streaming GEMV path")
@@ -73,12 +94,13 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except Exception:  # noqa: BLE001
             self.proc = None
+        return self
 
     def _read(self):
         for line in self.proc.stdout:
@@ -87,7 +109,7 @@ class ClockSampler:
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.12)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=2)
@@ -95,32 +117,65 @@ class ClockSampler:
             self.proc.kill()
         sm = sorted(float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit())
         mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        pw = [float(r[3]) for r in self.rows if len(r) >= 9 and r[3].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = sorted({n for r in self.rows if len(r) >= 9 for n, v in zip(names, r[5:9]) if v.lower().startswith("active")})
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx[0] if mx else None,
-                "reasons": reasons, "samples": len(sm)}
+                "power_w_max": max(pw) if pw else None, "reasons": reasons, "samples": len(sm)}
+
+
+def timed_repeats(step, steps, barrier, min_seconds=MIN_TIMED_SECONDS, max_repeats=200, agree=None):
+    """Runs the loop of exactly ``steps`` steps, bracketed by ``barrier()`` (+ device synchronise) and CUDA events,
+    again and again until ``min_seconds`` of device time have passed.  Returns the per-repeat milliseconds.
+    ``agree`` (multi-rank): maps this rank's elapsed total to the value every rank uses for the stop decision, so
+    that all ranks run the same number of repeats."""
+    import torch
+    out, total, i = [], 0.0, 0
+    while (agree(total) if agree else total) < min_seconds * 1e3 and len(out) < max_repeats:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            step(i)
+            i += 1
+        e1.record()
+        barrier()
+        out.append(e0.elapsed_time(e1))
+        total += out[-1]
+    return out
 
 
 # ---------------------------------------------------------------------------------------------
-# CPU arm: the oracle (torch dequantise-then-matmul restatement of the reference's check,
-# fused-moe/test_verdict_moe_ext.py:196-218) on a bounded sample of the workload.
+# CPU arm: a bounded sample of the decode workload through the reference's host C++ path or the oracle port.
+# Built from the oracle's own quantiser, so this arm never loads the CUDA library.
 # ---------------------------------------------------------------------------------------------
 def cpu_sample_problem(tokens: int, seed: int):
-    """A bounded sample of the decode workload, built on the CPU: ``tokens`` tokens of the batch with
-    only the experts they touch materialised (ids remapped to a dense range)."""
+    """``tokens`` tokens of a decode batch with only the experts they touch materialised (ids remapped to a dense
+    range).  Same shapes and value distributions as the device workload: weights N(0, 0.02) -> NVFP4 with one fp32
+    global scale per expert matrix, activations bf16 N(0, 1), router logits N(0, 1)."""
     import numpy as np
     import torch
     from oracle import moe as omoe
-    from sm120_moe_bench_b200 import synth
-    cfg = synth.CONFIG_LARGE
-    hidden, logits = synth.make_inputs(cfg, tokens, seed=seed)
-    ids, w = omoe.route(logits.numpy(), cfg.topk)
+    from oracle import nvfp4
+    K, N, E, T = 4096, 1024, 512, 10
+    gen = torch.Generator().manual_seed(seed + 1000003)
+    hidden = torch.randn(tokens, K, generator=gen).to(torch.bfloat16).float().numpy()
+    logits = torch.randn(tokens, E, generator=gen).numpy()
+    ids, w = omoe.route(logits, T)
     used, dense = np.unique(ids, return_inverse=True)
-    gen = torch.Generator().manual_seed(seed)
-    routed = synth.make_expert_weights(len(used), cfg.hidden, cfg.inter, gen, "cpu")
-    shared = synth.make_expert_weights(1, cfg.hidden, cfg.inter, gen, "cpu")
-    conv = lambda six: omoe.ExpertWeights(*[t.numpy() for t in six])
-    return hidden.float().numpy(), dense.reshape(ids.shape).astype(np.int32), w, conv(routed), conv(shared), len(used)
+
+    def experts(n):
+        parts = [[] for _ in range(6)]
+        for _ in range(n):
+            w13 = (torch.randn(2 * N, K, generator=gen) * 0.02).numpy()
+            p, s, g = nvfp4.quantize_weight(w13)
+            parts[0].append(p); parts[1].append(s); parts[2].append(g)
+            w2 = (torch.randn(K, N, generator=gen) * 0.02).numpy()
+            p, s, g = nvfp4.quantize_weight(w2)
+            parts[3].append(p); parts[4].append(s); parts[5].append(g)
+        return omoe.ExpertWeights(*[np.stack(x) if i not in (2, 5) else np.asarray(x, np.float32) for i, x in enumerate(parts)])
+
+    return hidden, dense.reshape(ids.shape).astype(np.int32), w, experts(len(used)), experts(1), len(used)
 
 
 def cpu_time_once(problem):
@@ -177,14 +232,16 @@ def run_reference_arm(args):
     times = [time_once(problem) for _ in range(max(args.steps, 1))]
     total = sum(times)
     value = sample_tokens * len(times) / total
-    sample = (f"{sample_tokens} token(s) of the {args.tokens}-token decode batch per step, "
-              f"{problem[5]} routed experts + 1 shared per step, through {what}")
+    sample = (f"each step = {sample_tokens} token of the {args.tokens}-token decode batch "
+              f"({problem[5]} routed experts + 1 shared), through {what}")
+    config = workload_config(args.tokens, args.gpus)
+    config["tokens_timed_per_step"] = sample_tokens
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": len(times), "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4(w4a4)->f32",
         "data": "synthetic",
-        "config": workload_config(args.tokens, args.gpus),
+        "config": config,
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -196,13 +253,153 @@ def workload_config(tokens, gpus):
             f"decode MoE layer, large-MoE shape (BASELINE config 2 layer), expert parallel over {gpus} GPUs",
             "hidden": 4096, "inter": 1024, "experts": 512, "topk": 10, "shared_experts": 1,
             "tokens_per_gpu": tokens, "weights": "NVFP4 (E2M1 + E4M3 per-16 + fp32 global), N(0,0.02), seed 0",
-            "parallelism": "single GPU" if gpus == 1 else f"{gpus} independent replicas",
+            "parallelism": "single GPU" if gpus == 1 else f"expert parallel over {gpus} GPUs",
             "l2": "inputs larger than L2: every step streams > 126 MB of expert weights; input sets rotate"}
 
 
 # ---------------------------------------------------------------------------------------------
+# single GPU
+# ---------------------------------------------------------------------------------------------
+class DecodeBench:
+    """The config-2 layer on one GPU: weights once, one workspace and a few rotating input sets per batch size."""
+
+    def __init__(self, dev, path: str):
+        import sm120_moe_bench_b200 as vm
+        from sm120_moe_bench_b200 import ops, synth
+        self.vm, self.ops, self.synth, self.dev = vm, ops, synth, dev
+        self.cfg = synth.CONFIG_LARGE
+        self.layer = synth.make_layer(self.cfg, seed=0, device=dev)
+        self.routed = ops.MoEWeights(*self.layer["routed"]).prepare()
+        self.shared = ops.MoEWeights(*self.layer["shared"]).prepare()
+        self.path_name = path
+        self.path = 2 if path == "tc" else 1
+        self.peak, self.peak_kind = measured_peak_gbs()
+
+    def case(self, M, steps, warmup, rotate, seed0=0, zipf=None, stage_steps=None):
+        """Times the layer (and its two GEMM kernels alone) at batch M.  Returns a dict of figures."""
+        import numpy as np
+        import torch
+        vm, ops, cfg = self.vm, self.ops, self.cfg
+        ws = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, max(M, 1), has_shared=True, path=self.path), self.dev)
+        sets = [self.synth.make_inputs(cfg, M, seed=seed0 + i, device=self.dev, zipf_s=zipf) for i in range(max(rotate, 1))]
+        out = torch.empty(M, cfg.hidden, dtype=torch.bfloat16, device=self.dev)
+
+        def step(i):
+            h, l = sets[i % len(sets)]
+            vm.fused_moe(h, self.routed, ws, router_logits=l, shared=self.shared, out=out)
+
+        sampler = ClockSampler(self.dev.index or 0).start()
+        for i in range(max(warmup, 3)):
+            step(i)
+        torch.cuda.synchronize()
+        reps = timed_repeats(step, steps, torch.cuda.synchronize)
+        ms_step = statistics.median(reps) / steps
+        status = ws.status()
+        # per-kernel durations: same inputs, each stage bracketed by its own events.  A device-side delay goes first
+        # so that the host has enqueued every launch and event before the GPU reaches them: the intervals then hold
+        # kernel time only, no host launch latency.
+        n = stage_steps or min(steps, 40)
+        gu, dn, distinct = [], [], []
+        for i in range(n):
+            h, l = sets[i % len(sets)]
+            vm.fused_moe(h, self.routed, ws, router_logits=l, shared=self.shared, out=out)   # fills every table
+            ids = ws.view("topk_ids", torch.int32, M * cfg.topk).view(M, cfg.topk).clone()
+            w = ws.view("topk_weights", torch.float32, M * cfg.topk).view(M, cfg.topk).clone()
+            torch.cuda._sleep(400_000)
+            vm.build_tables(ws, ids, w)                                            # same tables, work queue reset
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            ev[0].record()
+            ops.run_stage("gate_up", ws, self.routed, self.shared, M)
+            ev[1].record()
+            ops.run_stage("down", ws, self.routed, self.shared, M)
+            ev[2].record()
+            ev[2].synchronize()
+            gu.append(ev[0].elapsed_time(ev[1])); dn.append(ev[1].elapsed_time(ev[2]))
+            distinct.append(int(torch.unique(ids).numel()) + 1)
+        clocks = sampler.stop()
+        U = float(np.mean(distinct))
+        K, N = cfg.hidden, cfg.inter
+        gate_up_bytes = U * (2 * N * K // 2 + 2 * N * K // 16) + M * (K // 2 + K // 16)
+        down_bytes = U * (K * N // 2 + K * N // 16)
+        layer_bytes = U * self.routed.nbytes_per_expert() + M * (K * 2 * 2 + cfg.num_experts * 4)
+        gu_s, dn_s = statistics.median(gu) * 1e-3, statistics.median(dn) * 1e-3
+        return {"tokens": M, "ms_per_step": ms_step, "tokens_per_s": M / (ms_step * 1e-3), "repeats": len(reps),
+                "distinct_experts_per_step": U,
+                "layer_frac": layer_bytes / (ms_step * 1e-3) / 1e9 / self.peak, "layer_gbs": layer_bytes / (ms_step * 1e-3) / 1e9,
+                "layer_bytes": layer_bytes,
+                "gate_up_us": gu_s * 1e6, "gate_up_frac": gate_up_bytes / gu_s / 1e9 / self.peak, "gate_up_bytes": gate_up_bytes,
+                "down_us": dn_s * 1e6, "down_frac": down_bytes / dn_s / 1e9 / self.peak, "down_bytes": down_bytes,
+                "clocks": clocks, "device_status": status, "_ws": ws, "_sets": sets, "_out": out}
+
+    def parity_rows(self, case, rows):
+        """Three rows of the timed batch against the CPU oracle (router ids of the whole batch bit for bit)."""
+        import numpy as np
+        import torch
+        from oracle import moe as omoe
+        from tests import util
+        cfg, vm = self.cfg, self.vm
+        ws, (h, l), M = case["_ws"], case["_sets"][0], case["tokens"]
+        out = vm.fused_moe(h, self.routed, ws, router_logits=l, shared=self.shared)
+        torch.cuda.synchronize()
+        ids = ws.view("topk_ids", torch.int32, M * cfg.topk).view(M, cfg.topk).cpu().numpy()
+        wd = ws.view("topk_weights", torch.float32, M * cfg.topk).view(M, cfg.topk).cpu().numpy()
+        ids_ref, _ = omoe.route(l.cpu().numpy(), cfg.topk)
+        ow = util.to_oracle_weights(self.layer["routed"], np.unique(ids[rows]))
+        osh = util.to_oracle_weights(self.layer["shared"])
+        ref = omoe.moe_layer(h[rows].float().cpu().numpy(), ids[rows], wd[rows], ow, osh)
+        got = out[rows].float().cpu().numpy()
+        c, r = util.cosine(got, ref), util.rel_l2(got, ref)
+        ma = float(np.max(np.abs(got - ref))) / max(float(np.max(np.abs(ref))), 1e-30)
+        return {"against": "CPU oracle (oracle/moe.py), untimed", "rows": list(rows),
+                "router_ids_bit_exact": bool(np.array_equal(ids, ids_ref)),
+                "cosine": c, "rel_l2": r, "max_abs_over_max_ref": ma,
+                "tolerance": {"cosine_min": util.OUT_COSINE_MIN, "rel_l2_max": util.OUT_REL_L2_MAX,
+                              "max_abs_frac": util.OUT_MAX_ABS_FRAC},
+                "ok": bool(np.array_equal(ids, ids_ref) and c >= util.OUT_COSINE_MIN and r <= util.OUT_REL_L2_MAX
+                           and ma <= util.OUT_MAX_ABS_FRAC)}
+
+    def prefill_case(self, M, steps, warmup, zipf):
+        import torch
+        vm, ops, cfg = self.vm, self.ops, self.cfg
+        ws = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, M, has_shared=True, path=2), self.dev)
+        sets = [self.synth.make_inputs(cfg, M, seed=i, device=self.dev, zipf_s=zipf) for i in range(2)]
+        out = torch.empty(M, cfg.hidden, dtype=torch.bfloat16, device=self.dev)
+
+        def step(i):
+            vm.fused_moe(sets[i % 2][0], self.routed, ws, router_logits=sets[i % 2][1], shared=self.shared, out=out)
+
+        sampler = ClockSampler(self.dev.index or 0).start()
+        for i in range(max(warmup, 3)):
+            step(i)
+        torch.cuda.synchronize()
+        reps = timed_repeats(step, steps, torch.cuda.synchronize)
+        ms = statistics.median(reps) / steps
+        gu, dn = [], []
+        for i in range(6):
+            ids = ws.view("topk_ids", torch.int32, M * cfg.topk).view(M, cfg.topk).clone()
+            w = ws.view("topk_weights", torch.float32, M * cfg.topk).view(M, cfg.topk).clone()
+            torch.cuda._sleep(400_000)         # lets the host enqueue everything below ahead of the GPU
+            vm.build_tables(ws, ids, w)
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+            ev[0].record(); ops.run_stage("gate_up", ws, self.routed, self.shared, M)
+            ev[1].record(); ops.run_stage("down", ws, self.routed, self.shared, M)
+            ev[2].record(); ev[2].synchronize()
+            gu.append(ev[0].elapsed_time(ev[1])); dn.append(ev[1].elapsed_time(ev[2]))
+        clocks = sampler.stop()
+        K, N, T = cfg.hidden, cfg.inter, cfg.topk
+        flops = 2.0 * M * (T + 1) * 3 * K * N
+        bytes_alg = (cfg.num_experts + 1) * self.routed.nbytes_per_expert() + M * K * 4
+        gu_ms, dn_ms = statistics.median(gu), statistics.median(dn)
+        return {"tokens": M, "zipf_s": zipf, "ms_per_step": ms, "repeats": len(reps), "tokens_per_s": M / (ms * 1e-3),
+                "tflops": flops / (ms * 1e-3) / 1e12, "frac_of_nominal_fp4": flops / (ms * 1e-3) / 1e12 / NOMINAL_FP4_TFLOPS,
+                "hbm_gbs": bytes_alg / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": bytes_alg / (ms * 1e-3) / 1e9 / self.peak,
+                "algorithmic_bytes": bytes_alg, "flops": flops,
+                "gate_up_us": gu_ms * 1e3, "gate_up_tflops": flops * 2 / 3 / (gu_ms * 1e-3) / 1e12,
+                "down_us": dn_ms * 1e3, "down_tflops": flops / 3 / (dn_ms * 1e-3) / 1e12,
+                "clocks": clocks, "device_status": ws.status()}
+
+
 def run_ours(args):
-    import numpy as np
     import torch
     import torch.distributed as dist
 
@@ -213,11 +410,6 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-
-    import sm120_moe_bench_b200 as vm
-    from sm120_moe_bench_b200 import ops, synth
-    from sm120_moe_bench_b200.verdict_moe import VerdictMoEMonolithic
-
     if world > 1 and args.workload == "stack":
         return run_stack_expert_parallel(args, world, rank, local, dev)
     if world > 1:
@@ -227,87 +419,27 @@ def run_ours(args):
     if args.workload == "stack":
         return run_stack(args, dev)
 
-    cfg = synth.CONFIG_LARGE
+    from sm120_moe_bench_b200.verdict_moe import VerdictMoEMonolithic
+    b = DecodeBench(dev, args.path)
+    cfg, routed, shared = b.cfg, b.routed, b.shared
     M = args.tokens
-    layer = synth.make_layer(cfg, seed=0, device=dev)
-    routed = ops.MoEWeights(*layer["routed"]).prepare()
-    shared = ops.MoEWeights(*layer["shared"]).prepare()
-    path = 2 if args.path == "tc" else 1
-    shape = vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, max(M, 1), has_shared=True, path=path)
-    ws = vm.Workspace(shape, dev)
-    sets = [synth.make_inputs(cfg, M, seed=100 * rank + i, device=dev, zipf_s=args.zipf) for i in range(max(args.rotate, 1))]
-    out = torch.empty(M, cfg.hidden, dtype=torch.bfloat16, device=dev)
-
-    def step(i):
-        h, l = sets[i % len(sets)]
-        vm.fused_moe(h, routed, ws, router_logits=l, shared=shared, out=out)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    for i in range(args.warmup):
-        step(i)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for i in range(args.steps):
-        step(i)
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    status = ws.status()
-
-    # ---- per-kernel durations, same inputs, each stage bracketed by its own events ---------
-    stage_ms = {"gate_up": 0.0, "down": 0.0}
-    distinct = []
-    for i in range(args.steps):
-        h, l = sets[i % len(sets)]
-        vm.fused_moe(h, routed, ws, router_logits=l, shared=shared, out=out)   # fills every intermediate table
-        ids = ws.view("topk_ids", torch.int32, M * cfg.topk).view(M, cfg.topk).clone()
-        w = ws.view("topk_weights", torch.float32, M * cfg.topk).view(M, cfg.topk).clone()
-        # A device-side delay goes first so that the host has enqueued every launch and event below before
-        # the GPU reaches them: the event intervals then hold kernel time only, no host launch latency.
-        torch.cuda._sleep(400_000)
-        vm.build_tables(ws, ids, w)                                            # same tables, work queues reset
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-        ev[0].record()
-        ops.run_stage("gate_up", ws, routed, shared, M)
-        ev[1].record()
-        ops.run_stage("down", ws, routed, shared, M)
-        ev[2].record()
-        ev[2].synchronize()
-        stage_ms["gate_up"] += ev[0].elapsed_time(ev[1])
-        stage_ms["down"] += ev[1].elapsed_time(ev[2])
-        distinct.append(int(torch.unique(ids).numel()) + 1)
-    U = float(np.mean(distinct))
-    K, N = cfg.hidden, cfg.inter
-    gate_up_bytes = U * (2 * N * K // 2 + 2 * N * K // 16) + M * (K // 2 + K // 16)
-    down_bytes = U * (K * N // 2 + K * N // 16)
-    layer_bytes = U * routed.nbytes_per_expert() + M * (K * 2 * 2 + cfg.num_experts * 4)
-    peak, peak_kind = measured_peak_gbs()
-    gu_s = stage_ms["gate_up"] / args.steps * 1e-3
-    dn_s = stage_ms["down"] / args.steps * 1e-3
-    kname = "tc_gemm_kernel<2> (gate_up, tcgen05)" if path == 2 else "gate_up_kernel (CUDA-core GEMV)"
-    roof = {"bound": "hbm", "kernel": kname, "achieved": gate_up_bytes / gu_s / 1e9, "peak": peak,
-            "peak_source": peak_kind + " (MEASURED_PEAKS.json hbm_gbs)" if peak_kind == "measured" else "fallback 6650 GB/s",
-            "unit": "GB/s", "frac": gate_up_bytes / gu_s / 1e9 / peak,
-            # DRAM bytes per launch: one ncu capture of this kernel at batch 16 read + wrote 1.044x its
-            # algorithmic bytes (profiles/tc_gemm_gate_up_down_decode_bs16_ncu.md); traffic grows with the
-            # number of distinct experts like the algorithmic bytes do, so that ratio is applied here
-            "traffic": (1.044 if path == 2 else 1.048) * gate_up_bytes,
-            "algorithmic_bytes_per_launch": gate_up_bytes, "us_per_launch": gu_s * 1e6,
-            "distinct_experts_per_step": U,
-            "down_kernel": {"achieved": down_bytes / dn_s / 1e9, "frac": down_bytes / dn_s / 1e9 / peak,
-                            "us_per_launch": dn_s * 1e6, "algorithmic_bytes_per_launch": down_bytes},
-            "layer": {"achieved": layer_bytes / (ms / args.steps * 1e-3) / 1e9,
-                      "frac": layer_bytes / (ms / args.steps * 1e-3) / 1e9 / peak,
-                      "algorithmic_bytes_per_step": layer_bytes}}
+    main = b.case(M, args.steps, args.warmup, args.rotate, seed0=0, zipf=args.zipf)
+    parity = b.parity_rows(main, [0, M // 2, M - 1] if M >= 3 else list(range(M)))
+    kname = "tc_fused_kernel, gate_up items alone (tcgen05)" if b.path == 2 else "gate_up_kernel (CUDA-core GEMV)"
+    roof = {"bound": "hbm", "kernel": kname, "achieved": main["gate_up_bytes"] / (main["gate_up_us"] * 1e-6) / 1e9,
+            "peak": b.peak,
+            "peak_source": (b.peak_kind + " (MEASURED_PEAKS.json hbm_gbs: a copy kernel, read + write; a read-only stream "
+                            "may exceed it slightly)") if b.peak_kind == "measured" else "fallback 6650 GB/s",
+            "unit": "GB/s", "frac": main["gate_up_frac"],
+            "traffic": TRAFFIC_RATIO[args.path] * main["gate_up_bytes"],
+            "traffic_source": f"estimated: {TRAFFIC_RATIO[args.path]} x algorithmic bytes, the ratio one ncu capture of this "
+                              "kernel showed at batch 16 (dram__bytes_read.sum + dram__bytes_write.sum)",
+            "algorithmic_bytes_per_launch": main["gate_up_bytes"], "us_per_launch": main["gate_up_us"],
+            "distinct_experts_per_step": main["distinct_experts_per_step"],
+            "down_kernel": {"achieved": main["down_bytes"] / (main["down_us"] * 1e-6) / 1e9, "frac": main["down_frac"],
+                            "us_per_launch": main["down_us"], "algorithmic_bytes_per_launch": main["down_bytes"]},
+            "layer": {"achieved": main["layer_gbs"], "frac": main["layer_frac"],
+                      "algorithmic_bytes_per_step": main["layer_bytes"]}}
 
     # ---- end to end through the operator class with host buffers -----------------------------
     class _Q:  # quant-config attributes the class reads (fused-moe/verdict_moe.py:499-503,519-520)
@@ -317,9 +449,10 @@ def run_ours(args):
 
     class _C:
         experts_per_token = cfg.topk
-    VerdictMoEMonolithic.kernel_path = path
+    VerdictMoEMonolithic.kernel_path = b.path
     op = VerdictMoEMonolithic(_C(), _Q())
     op.set_shared_expert(shared)
+    sets = main["_sets"]
     host_sets = [(h.cpu().pin_memory(), l.cpu().pin_memory()) for h, l in sets]
     host_out = torch.empty(M, cfg.hidden, dtype=torch.bfloat16).pin_memory()
     h_dev = torch.empty(M, cfg.hidden, dtype=torch.bfloat16, device=dev)
@@ -335,23 +468,22 @@ def run_ours(args):
     # The user's call sequence (copy in, apply, copy out) is captured once per host input set and replayed as a
     # CUDA graph, as a serving engine does; every replay still performs both copies.  Eager calls if capture fails.
     e2e_mode, graphs = "eager calls", []
-    if world == 1:
-        try:
-            side = torch.cuda.Stream()
-            with torch.cuda.stream(side):
-                for k in range(len(host_sets)):
+    try:
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            for k in range(len(host_sets)):
+                e2e_enqueue(k)
+            side.synchronize()
+            for k in range(len(host_sets)):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
                     e2e_enqueue(k)
-                side.synchronize()
-                for k in range(len(host_sets)):
-                    g = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(g, stream=side):
-                        e2e_enqueue(k)
-                    graphs.append(g)
-            torch.cuda.synchronize()
-            e2e_mode = "one CUDA graph per host input set: H2D copies + operator call + D2H copy"
-        except Exception:  # noqa: BLE001
-            graphs = []
-            torch.cuda.synchronize()
+                graphs.append(g)
+        torch.cuda.synchronize()
+        e2e_mode = "one CUDA graph per host input set: H2D copies + operator call + D2H copy"
+    except Exception:  # noqa: BLE001
+        graphs = []
+        torch.cuda.synchronize()
 
     def e2e_step(i):
         k = i % len(host_sets)
@@ -361,117 +493,78 @@ def run_ours(args):
             e2e_enqueue(k)
         torch.cuda.current_stream().synchronize()     # the caller reads the result every step
 
-    for i in range(args.warmup):
+    sampler = ClockSampler(local).start()
+    for i in range(max(args.warmup, 3)):
         e2e_step(i)
-    barrier()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    f0.record()
-    for i in range(args.steps):
-        e2e_step(i)
-    f1.record()
-    barrier()
-    e2e_ms = f0.elapsed_time(f1)
+    e2e_reps = timed_repeats(e2e_step, args.steps, torch.cuda.synchronize)
+    e2e_ms = statistics.median(e2e_reps)
+    e2e_clocks = sampler.stop()
 
-    clocks = sampler.stop() if rank == 0 else None
-    if world > 1:
-        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = t.tolist()
-
-    line = None
-    if rank == 0:
-        tokens_total = M * world * args.steps
-        launches_per_step = 6 if M * cfg.topk <= 4096 else 10   # route, tables (1 or 5), quantise, gate_up, down, combine
-        line = {
-            "metric": METRIC, "value": tokens_total / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4(w4a4)->f32",
-            "data": "synthetic", "config": dict(workload_config(M, world), kernel_path=args.path),
-            "roofline": roof, "clocks": clocks,
-            "e2e": {"value": tokens_total / (e2e_ms * 1e-3), "unit": UNIT,
-                    "h2d_bytes_per_step": M * (cfg.hidden * 2 + cfg.num_experts * 4),
-                    "d2h_bytes_per_step": M * cfg.hidden * 2, "ms_per_step": e2e_ms / args.steps, "mode": e2e_mode},
-            "gpu_launches": launches_per_step * args.steps,
-            "device_status": status,
-        }
-        if not args.no_cpu_baseline and world == 1:
-            torch.set_num_threads(os.cpu_count() or 1)
-            time_once, kind, cores, what = cpu_reference()
-            problem = cpu_sample_problem(args.cpu_sample_tokens, seed=0)
-            dt = time_once(problem)
-            line["cpu_baseline"] = {
-                "value": args.cpu_sample_tokens / dt, "unit": UNIT, "cores": cores, "kind": kind,
-                "sample": f"{args.cpu_sample_tokens} tokens of the batch, {problem[5]} routed experts + 1 shared, "
-                          f"one pass through {what} ({dt:.1f} s)"}
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
-
-
-NOMINAL_FP4_TFLOPS = 9000.0     # dense FP4, B200 data sheet; no measured FP4 figure is provided
+    ms = main["ms_per_step"] * args.steps
+    front = "one-CTA front" if M <= 32 else "route, tables"
+    launches_per_step = {"tc": (2 if M <= 4 else 3 if M <= 32 else 4), "gemv": 6}[args.path]
+    line = {
+        "metric": METRIC, "value": M * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": main["ms_per_step"], "repeats": main["repeats"],
+        "timed_seconds": main["repeats"] * ms * 1e-3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4(w4a4)->f32",
+        "data": "synthetic", "config": dict(workload_config(M, 1), kernel_path=args.path),
+        "roofline": roof, "clocks": main["clocks"],
+        "e2e": {"value": M * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
+                "h2d_bytes_per_step": M * (cfg.hidden * 2 + cfg.num_experts * 4),
+                "d2h_bytes_per_step": M * cfg.hidden * 2, "ms_per_step": e2e_ms / args.steps, "mode": e2e_mode,
+                "repeats": len(e2e_reps), "clocks": e2e_clocks},
+        "gpu_launches": launches_per_step * args.steps,
+        "launches_per_step": f"{launches_per_step} ({front}" + (", permuting quantiser" if M > 4 else "") +
+                             ", fused gate_up + down + combine kernel)" if args.path == "tc" else "6",
+        "parity": parity,
+        "device_status": main["device_status"],
+    }
+    if not args.no_sweep and args.path == "tc":
+        sweep = []
+        for bs in (1, 4, 16):
+            c = b.case(bs, max(args.steps, 100), args.warmup, max(args.rotate, 8), seed0=1000 * bs)
+            sweep.append({k: v for k, v in c.items() if not k.startswith("_")})
+        sweep.append({k: v for k, v in main.items() if not k.startswith("_")})
+        line["sweep"] = sweep
+        del main
+        torch.cuda.empty_cache()
+        line["prefill"] = [b.prefill_case(8192, 10, 3, None), b.prefill_case(8192, 10, 3, 1.2)]
+    if not args.no_cpu_baseline:
+        torch.set_num_threads(os.cpu_count() or 1)
+        time_once, kind, cores, what = cpu_reference()
+        problem = cpu_sample_problem(args.cpu_sample_tokens, seed=0)
+        dt = time_once(problem)
+        line["cpu_baseline"] = {
+            "value": args.cpu_sample_tokens / dt, "unit": UNIT, "cores": cores, "kind": kind,
+            "sample": f"{args.cpu_sample_tokens} tokens of a decode batch, {problem[5]} routed experts + 1 shared, "
+                      f"one pass through {what} ({dt:.1f} s)"}
+    print(json.dumps(line), flush=True)
 
 
 def run_prefill(args, dev):
     """BASELINE config 3: 8192 tokens through the same layer on one GPU; FP4 TFLOP/s of the whole layer
     (2 * M * (T + 1) * 3 * K * N flops) and of the two grouped GEMMs, event-timed."""
-    import torch
-
-    import sm120_moe_bench_b200 as vm
-    from sm120_moe_bench_b200 import ops, synth
-    cfg = synth.CONFIG_LARGE
+    b = DecodeBench(dev, "tc")
     M = args.tokens if args.tokens != 64 else 8192
-    layer = synth.make_layer(cfg, seed=0, device=dev)
-    routed = ops.MoEWeights(*layer["routed"]).prepare()
-    shared = ops.MoEWeights(*layer["shared"]).prepare()
-    ws = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, M, has_shared=True, path=2), dev)
-    sets = [synth.make_inputs(cfg, M, seed=i, device=dev, zipf_s=args.zipf) for i in range(2)]
-    out = torch.empty(M, cfg.hidden, dtype=torch.bfloat16, device=dev)
-    sampler = ClockSampler(dev.index or 0)
-    sampler.start()
-    for i in range(args.warmup):
-        vm.fused_moe(sets[i % 2][0], routed, ws, router_logits=sets[i % 2][1], shared=shared, out=out)
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        vm.fused_moe(sets[i % 2][0], routed, ws, router_logits=sets[i % 2][1], shared=shared, out=out)
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / args.steps
-    stage_ms = {"gate_up": 0.0, "down": 0.0}
-    for i in range(min(args.steps, 10)):
-        ids = ws.view("topk_ids", torch.int32, M * cfg.topk).view(M, cfg.topk).clone()
-        w = ws.view("topk_weights", torch.float32, M * cfg.topk).view(M, cfg.topk).clone()
-        torch.cuda._sleep(400_000)         # lets the host enqueue everything below ahead of the GPU
-        vm.build_tables(ws, ids, w)
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-        ev[0].record(); ops.run_stage("gate_up", ws, routed, shared, M)
-        ev[1].record(); ops.run_stage("down", ws, routed, shared, M)
-        ev[2].record(); ev[2].synchronize()
-        stage_ms["gate_up"] += ev[0].elapsed_time(ev[1]) / min(args.steps, 10)
-        stage_ms["down"] += ev[1].elapsed_time(ev[2]) / min(args.steps, 10)
-    clocks = sampler.stop()
-    K, N, T = cfg.hidden, cfg.inter, cfg.topk
-    flops = 2.0 * M * (T + 1) * 3 * K * N
-    gu_flops, dn_flops = flops * 2 / 3, flops / 3
-    peak_hbm, kind = measured_peak_gbs()
-    bytes_alg = (cfg.num_experts + 1) * routed.nbytes_per_expert() + M * K * 4
-    line = {"metric": "moe_layer_prefill_fp4_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": 1,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+    c = b.prefill_case(M, args.steps, args.warmup, args.zipf)
+    cfg = b.cfg
+    line = {"metric": "moe_layer_prefill_fp4_tflops", "value": c["tflops"], "unit": "TFLOP/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": c["ms_per_step"], "repeats": c["repeats"],
+            "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "nvfp4(w4a4)->f32", "data": "synthetic",
             "config": {"workload": "single-GPU prefill MoE layer (BASELINE config 3)", "tokens": M, "zipf_s": args.zipf,
-                       "hidden": K, "inter": N, "experts": cfg.num_experts, "topk": T, "shared_experts": 1},
-            "tokens_per_s": M / (ms * 1e-3),
+                       "hidden": cfg.hidden, "inter": cfg.inter, "experts": cfg.num_experts, "topk": cfg.topk, "shared_experts": 1},
+            "tokens_per_s": c["tokens_per_s"],
             "roofline": {"bound": "tensor", "kernel": "pf_kernel<1> (gate_up, tcgen05, 128-token x 256-row items)",
-                         "achieved": gu_flops / (stage_ms["gate_up"] * 1e-3) / 1e12, "peak": NOMINAL_FP4_TFLOPS,
-                         "peak_source": "nominal dense FP4 (no measured FP4 peak available)", "unit": "TFLOP/s",
-                         "frac": gu_flops / (stage_ms["gate_up"] * 1e-3) / 1e12 / NOMINAL_FP4_TFLOPS, "traffic": None,
-                         "us_per_launch": stage_ms["gate_up"] * 1e3,
-                         "down_kernel": {"achieved": dn_flops / (stage_ms["down"] * 1e-3) / 1e12,
-                                         "us_per_launch": stage_ms["down"] * 1e3},
-                         "layer_hbm": {"algorithmic_bytes": bytes_alg, "achieved_gbs": bytes_alg / (ms * 1e-3) / 1e9,
-                                       "frac_of_hbm_peak": bytes_alg / (ms * 1e-3) / 1e9 / peak_hbm, "peak_source": kind}},
-            "clocks": clocks, "device_status": ws.status()}
+                         "achieved": c["gate_up_tflops"], "peak": NOMINAL_FP4_TFLOPS,
+                         "peak_source": "nominal dense FP4 (MEASURED_PEAKS.json holds no FP4 figure)", "unit": "TFLOP/s",
+                         "frac": c["gate_up_tflops"] / NOMINAL_FP4_TFLOPS, "traffic": None,
+                         "us_per_launch": c["gate_up_us"],
+                         "down_kernel": {"achieved": c["down_tflops"], "us_per_launch": c["down_us"]},
+                         "layer_hbm": {"algorithmic_bytes": c["algorithmic_bytes"], "achieved_gbs": c["hbm_gbs"],
+                                       "frac_of_hbm_peak": c["frac_of_hbm_peak"], "peak_source": b.peak_kind}},
+            "clocks": c["clocks"], "device_status": c["device_status"]}
     print(json.dumps(line), flush=True)
 
 
@@ -494,14 +587,16 @@ def run_stack(args, dev):
     x0, _ = synth.make_inputs(cfg, M, seed=0, device=dev)
     logits = [synth.make_inputs(cfg, M, seed=1000 + li, device=dev)[1] for li in range(L)]
     x = x0.clone()
+
     def one_pass():
         x.copy_(x0)
         for li in range(L):
-            # residual add fused into the combine kernel, in place: x <- x + moe(x)
+            # residual add fused into the combine, in place: x <- x + moe(x)
             vm.fused_moe(x, layers[li][0], ws, router_logits=logits[li], shared=layers[li][1], out=x, residual=x)
 
     one_pass()                                          # warm: tensor maps, attributes
     torch.cuda.synchronize()
+    eager_ref = x.clone()
     graph = torch.cuda.CUDAGraph()
     side = torch.cuda.Stream()
     with torch.cuda.stream(side):
@@ -510,29 +605,18 @@ def run_stack(args, dev):
         with torch.cuda.graph(graph, stream=side):
             one_pass()
     torch.cuda.synchronize()
-    eager_ref = x.clone()
-    sampler = ClockSampler(dev.index or 0)
-    sampler.start()
-    for _ in range(args.warmup):
+    sampler = ClockSampler(dev.index or 0).start()
+    for _ in range(max(args.warmup, 3)):
         graph.replay()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        graph.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    ms_graph = e0.elapsed_time(e1) / args.steps
+    reps = timed_repeats(lambda i: graph.replay(), args.steps, torch.cuda.synchronize)
+    ms_graph = statistics.median(reps) / args.steps
     same = bool(torch.equal(x, eager_ref))
-    e0.record()
-    for _ in range(args.steps):
-        one_pass()
-    e1.record()
-    torch.cuda.synchronize()
-    ms_eager = e0.elapsed_time(e1) / args.steps
+    ereps = timed_repeats(lambda i: one_pass(), args.steps, torch.cuda.synchronize, min_seconds=0.2)
+    ms_eager = statistics.median(ereps) / args.steps
     clocks = sampler.stop()
     line = {"metric": "moe_stack_latency_ms", "value": ms_graph, "unit": "ms per pass (per-token latency)", "n_gpus": 1,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_graph, "higher_is_better": False,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_graph, "repeats": len(reps), "higher_is_better": False,
             "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4(w4a4)->f32", "data": "synthetic",
             "config": {"workload": "stack of MoE layers, config-2 shape, residual add, one CUDA graph (BASELINE config 5 on one GPU)",
                        "layers": L, "tokens": M},
@@ -541,12 +625,15 @@ def run_stack(args, dev):
     print(json.dumps(line), flush=True)
 
 
+# ---------------------------------------------------------------------------------------------
+# expert parallel (N > 1)
+# ---------------------------------------------------------------------------------------------
 def run_stack_expert_parallel(args, world, rank, local, dev):
     """BASELINE config 5: ``--layers`` consecutive MoE layers (independent seeded weights, ``x <- x + moe(x)``)
     at a decode batch of 32 tokens over all ranks (``--tokens`` per rank, default 32 / N), experts split over the
-    ranks, dispatch and combine as peer-memory kernels.  Reports the latency of one pass = per-token latency,
-    device-timed, max over ranks.  Eager launches: the exchange epoch is a kernel argument, so the pass is not
-    replayed from a CUDA graph."""
+    ranks, dispatch and combine as peer-memory kernels, the residual fused into the combine.  One CUDA graph per
+    rank holds the whole pass; its replay is checked against the eager pass bit for bit.  Reports the latency of
+    one pass = per-token latency, device-timed, max over ranks."""
     import torch
     import torch.distributed as dist
 
@@ -566,47 +653,71 @@ def run_stack_expert_parallel(args, world, rank, local, dev):
     x0, _ = synth.make_inputs(cfg, M, seed=100 * rank, device=dev)
     logits = [synth.make_inputs(cfg, M, seed=1000 + 100 * rank + li, device=dev)[1] for li in range(L)]
     x = x0.clone()
-    y = torch.empty_like(x)
 
     def one_pass():
         x.copy_(x0)
         for li in range(L):
-            moes[li].forward(x, logits[li], out=y)
-            x.add_(y)                                   # residual
+            moes[li].forward(x, logits[li], out=x, residual=x)      # x <- x + moe(x), fused into the combine
 
     def barrier():
         dist.barrier()
         torch.cuda.synchronize()
 
+    def agree(total_ms):
+        t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return t.item()
+
+    for _ in range(3):
+        one_pass()
+    barrier()
+    eager_ref = x.clone()
+    mode, graph = "eager launches", None
+    try:
+        side = torch.cuda.Stream()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            one_pass()
+            side.synchronize()
+            with torch.cuda.graph(g, stream=side):
+                one_pass()
+        torch.cuda.synchronize()
+        graph, mode = g, "one CUDA graph per rank"
+    except Exception as exc:  # noqa: BLE001
+        mode = f"eager launches (graph capture failed: {type(exc).__name__})"
+        torch.cuda.synchronize()
+    ok = torch.tensor([1 if graph is not None else 0], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if int(ok.item()) == 0:
+        graph = None                                    # all ranks replay or none does: they must stay in step
+    run = (lambda i: graph.replay()) if graph is not None else (lambda i: one_pass())
+
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    for _ in range(max(args.warmup, 3)):
-        one_pass()
+    for i in range(max(args.warmup, 3)):
+        run(i)
     barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        one_pass()
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1) / args.steps
+    same = bool(torch.equal(x, eager_ref))
+    reps = timed_repeats(run, args.steps, barrier, agree=agree)
+    ms = statistics.median(reps) / args.steps
     status = max(m.status() for m in moes)
     clocks = sampler.stop() if rank == 0 else None
-    t = torch.tensor([ms, float(status)], device=dev, dtype=torch.float64)
+    t = torch.tensor([ms, float(status), 0.0 if same else 1.0], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     if rank == 0:
         ms = t[0].item()
         line = {"metric": "moe_stack_latency_ms", "value": ms, "unit": "ms per pass (per-token latency)", "n_gpus": world,
-                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": False,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "repeats": len(reps), "higher_is_better": False,
                 "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4(w4a4)->f32", "data": "synthetic",
-                "config": {"workload": f"stack of MoE layers, config-2 shape, residual add, expert parallel over {world} GPUs "
-                                       "(BASELINE config 5), eager launches",
+                "config": {"workload": f"stack of MoE layers, config-2 shape, residual add fused into the combine, expert parallel over "
+                                       f"{world} GPUs (BASELINE config 5), {mode}",
                            "layers": L, "tokens_per_gpu": M, "tokens": M * world, "experts_per_gpu": per},
                 "us_per_layer": ms * 1e3 / L, "tokens_per_s": M * world / (ms * 1e-3), "clocks": clocks,
+                "parity": {"graph_replay_equals_eager_on_all_ranks": t[2].item() == 0.0},
                 "device_status": int(t[1].item())}
         print(json.dumps(line), flush=True)
+    barrier()
     for m in moes:
         m.close()
     dist.destroy_process_group()
@@ -620,27 +731,53 @@ def run_expert_parallel(args, world, rank, local, dev):
     import torch
     import torch.distributed as dist
 
+    import sm120_moe_bench_b200 as vm
     from sm120_moe_bench_b200 import ep, ops, synth
+    from sm120_moe_bench_b200 import route as dev_route
 
     cfg = synth.CONFIG_LARGE
     M = args.tokens
+    group = 6 if args.mtp_corr > 0 else None
     layer = synth.make_layer(cfg, seed=0, device=dev)              # identical on every rank (same seed)
     first, per = ep.expert_partition(cfg.num_experts, world, rank)
     mine = ops.MoEWeights(*[t[first:first + per].contiguous() for t in layer["routed"]]).prepare()
     shared = ops.MoEWeights(*layer["shared"]).prepare()
-    del layer
+    full = ops.MoEWeights(*layer["routed"]).prepare()
+    sets = [synth.make_inputs(cfg, M, seed=100 * rank + i, device=dev, zipf_s=args.zipf, mtp_group=group, mtp_corr=args.mtp_corr)
+            for i in range(max(args.rotate, 1))]
+    # untimed, before the full layer is released: what ONE GPU holding all experts computes for this rank's tokens
+    # (the bit-identity reference) and, on rank 0, how long one GPU takes for the tokens of ALL ranks (strong scaling)
+    ws1 = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, max(M, 1), has_shared=True, path=2), dev)
+    single = [vm.fused_moe(h, full, ws1, router_logits=l, shared=shared).clone() for h, l in sets] if M else []
+    one_gpu_ms = None
+    if rank == 0 and M:
+        Mall = M * world
+        wsA = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, Mall, has_shared=True, path=2), dev)
+        allsets = [synth.make_inputs(cfg, Mall, seed=7000 + i, device=dev, zipf_s=args.zipf, mtp_group=group, mtp_corr=args.mtp_corr)
+                   for i in range(2)]
+        oA = torch.empty(Mall, cfg.hidden, dtype=torch.bfloat16, device=dev)
+        stepA = lambda i: vm.fused_moe(allsets[i % 2][0], full, wsA, router_logits=allsets[i % 2][1], shared=shared, out=oA)
+        for i in range(5):
+            stepA(i)
+        torch.cuda.synchronize()
+        one_gpu_ms = statistics.median(timed_repeats(stepA, 20, torch.cuda.synchronize, min_seconds=0.2)) / 20
+        del wsA, allsets, oA
+    del full, ws1, layer
     torch.cuda.empty_cache()
     moe = ep.ExpertParallelMoE(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, mine, shared, max_local_tokens=max(M, 1))
-    sets = [synth.make_inputs(cfg, M, seed=100 * rank + i, device=dev) for i in range(max(args.rotate, 1))]
     out = torch.empty(M, cfg.hidden, dtype=torch.bfloat16, device=dev)
 
     def barrier():
         dist.barrier()
         torch.cuda.synchronize()
 
+    def agree(total_ms):
+        t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return t.item()
+
     # untimed: how many distinct local experts each input set touches on this rank, and the NVLink rows
-    from sm120_moe_bench_b200 import route as dev_route
-    local_experts, remote_pairs = [], []
+    local_experts, remote_pairs, reuse = [], [], []
     for h, l in sets:
         ids, _ = dev_route(l, cfg.topk)
         gathered = [torch.empty_like(ids) for _ in range(world)]
@@ -649,21 +786,24 @@ def run_expert_parallel(args, world, rank, local, dev):
         mine_mask = (allids >= first) & (allids < first + per)
         local_experts.append(int(torch.unique(allids[mine_mask]).numel()) + 1)
         remote_pairs.append(int(((ids.flatten() < first) | (ids.flatten() >= first + per)).sum()))
+        if group:
+            reuse.append(synth.adjacent_reuse(ids, group))
+
+    def step(i):
+        moe.forward(*sets[i % len(sets)], out=out)
 
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    for i in range(args.warmup):
-        moe.forward(*sets[i % len(sets)], out=out)
+    equal, maxdiff = True, 0.0
+    for i in range(max(args.warmup, len(sets), 3)):
+        step(i)
+        if M:
+            equal = equal and bool(torch.equal(out, single[i % len(sets)]))     # synchronises; untimed
+            maxdiff = max(maxdiff, float((out.float() - single[i % len(sets)].float()).abs().max()))
     barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for i in range(args.steps):
-        moe.forward(*sets[i % len(sets)], out=out)
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
+    reps = timed_repeats(step, args.steps, barrier, agree=agree)
+    ms = statistics.median(reps)
     status = moe.status()
 
     host_sets = [(h.cpu().pin_memory(), l.cpu().pin_memory()) for h, l in sets]
@@ -679,16 +819,10 @@ def run_expert_parallel(args, world, rank, local, dev):
         host_out.copy_(out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
-    for i in range(args.warmup):
+    for i in range(max(args.warmup, 3)):
         e2e_step(i)
     barrier()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    f0.record()
-    for i in range(args.steps):
-        e2e_step(i)
-    f1.record()
-    barrier()
-    e2e_ms = f0.elapsed_time(f1)
+    e2e_ms = statistics.median(timed_repeats(e2e_step, args.steps, barrier, agree=agree))
     clocks = sampler.stop() if rank == 0 else None
 
     K, N = cfg.hidden, cfg.inter
@@ -701,6 +835,8 @@ def run_expert_parallel(args, world, rank, local, dev):
     ms, e2e_ms = tmax[0].item(), tmax[1].item()
     total_bytes, total_nv = -tsum[2].item(), -tsum[3].item()
     st = torch.tensor([status], device=dev); dist.all_reduce(st, op=dist.ReduceOp.MAX)
+    okr = torch.tensor([1 if equal else 0], device=dev); dist.all_reduce(okr, op=dist.ReduceOp.SUM)
+    mdf = torch.tensor([maxdiff], device=dev, dtype=torch.float64); dist.all_reduce(mdf, op=dist.ReduceOp.MAX)
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
         step_s = ms / args.steps * 1e-3
@@ -709,22 +845,31 @@ def run_expert_parallel(args, world, rank, local, dev):
         config["parallelism"] = f"expert parallel over {world} GPUs ({per} routed experts per GPU, shared expert replicated), dispatch/combine as NVLink peer-memory kernels"
         config["kernel_path"] = "tc"
         config["zipf_s"] = args.zipf
+        if group:
+            config["mtp"] = {"positions_per_sequence": group, "logit_correlation": args.mtp_corr,
+                             "adjacent_expert_reuse": float(np.mean(reuse))}
         line = {
             "metric": METRIC, "value": tokens_total / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "steps": args.steps, "warmup": max(args.warmup, len(sets), 3), "ms_per_step": ms / args.steps, "repeats": len(reps),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4(w4a4)->f32",
             "data": "synthetic", "config": config,
             "roofline": {"bound": "hbm", "kernel": "expert-parallel layer (all kernels of one step, per GPU)",
                          "achieved": total_bytes / world / step_s / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": total_bytes / world / step_s / 1e9 / peak, "traffic": None,
                          "peak_source": peak_kind, "algorithmic_bytes_per_step_all_gpus": total_bytes,
+                         "distinct_local_experts_rank0": float(np.mean(local_experts)),
                          "nvlink_bytes_per_step_all_gpus": total_nv,
                          "nvlink_gbs_per_gpu": total_nv / world / step_s / 1e9},
+            "strong_scaling": {"tokens": M * world, "one_gpu_ms_per_step": one_gpu_ms, "n_gpu_ms_per_step": ms / args.steps,
+                               "speedup_over_one_gpu": (one_gpu_ms / (ms / args.steps)) if one_gpu_ms else None,
+                               "note": "the same total batch through the single-GPU layer on rank 0 (all experts on one GPU), untimed region"},
+            "parity": {"ep_vs_single_gpu": "bit-identical" if int(okr.item()) == world else "DIFFERS",
+                       "ranks_ok": int(okr.item()), "max_abs_diff": mdf.item(), "checked": "every warm-up step's output against the single-GPU layer's (torch.equal)"},
             "clocks": clocks,
             "e2e": {"value": tokens_total / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": M * (cfg.hidden * 2 + cfg.num_experts * 4) * world,
                     "d2h_bytes_per_step": M * cfg.hidden * 2 * world, "ms_per_step": e2e_ms / args.steps},
-            "gpu_launches": 13 * args.steps * world,   # route, plan, dispatch, gather, tables, permute, gate_up, down, signal, combine (+3 when tables run as phases)
+            "gpu_launches": 6 * args.steps * world,   # front, dispatch, gather + tables, permute, experts, combine
             "device_status": int(st.item()),
         }
         print(json.dumps(line), flush=True)

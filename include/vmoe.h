@@ -31,7 +31,7 @@
 extern "C" {
 #endif
 
-#define VMOE_ABI_VERSION 3
+#define VMOE_ABI_VERSION 4
 
 enum vmoe_status {
     VMOE_OK = 0,
@@ -42,15 +42,16 @@ enum vmoe_status {
     VMOE_ERR_CUDA = 5,       /* a CUDA call failed; cudaGetLastError has details */
     VMOE_ERR_TIMEOUT = 6,    /* a bounded device-side wait ran out (read from the status word) */
     VMOE_ERR_SCALE = 7,      /* a block-scale byte has its sign bit set (NVFP4 scales are unsigned) */
-    VMOE_ERR_LIMIT = 8       /* size beyond a stated fixed maximum */
+    VMOE_ERR_LIMIT = 8,      /* size beyond a stated fixed maximum, or an expert id outside its range */
+    VMOE_ERR_PEER = 9        /* expert parallelism: another rank reported a failure for this call */
 };
 
 /* Problem shape.  Replaces the reference's compile-time HIDDEN = 4096 and the
  * (K, N_half, num_pairs) integer arguments of its forward functions
  * (fused-moe/csrc/verdict_fused_cooperative_tma_ext.cu:32, :594-596). */
 typedef struct vmoe_shape {
-    int32_t hidden;       /* K: multiple of 128, <= 4096 (tensor-core path: multiple of 256) */
-    int32_t inter;        /* N: multiple of 128, <= 1024 (tensor-core path: multiple of 256) */
+    int32_t hidden;       /* K: multiple of 128 (tensor-core path: multiple of 256; streaming GEMV path: <= 4096) */
+    int32_t inter;        /* N: multiple of 128 (tensor-core path: multiple of 256; streaming GEMV path: <= 1024) */
     int32_t num_experts;  /* E: routed experts whose weights this GPU holds */
     int32_t topk;         /* T: 1..16 */
     int32_t max_tokens;   /* largest M the workspace must serve */
@@ -102,11 +103,16 @@ typedef struct vmoe_ws_layout {
     size_t pair_out;        /* f32 [P + M, K] weighted down-projection rows per sorted slot */
     size_t bitmap;          /* u32 [E, ceil(M/32)] scratch of the permutation */
     size_t word_prefix;     /* int32 [E, ceil(M/32)] scratch of the permutation */
-    size_t tc_units;        /* int32 [max_tc_units, 4]: (expert, first slot, tokens, UMMA N) units of <= 64 tokens */
+    size_t tc_units;        /* int32 [max_tc_units, 4]: (expert, first slot, tokens, UMMA N) units of <= 16 tokens
+                               (weights-as-rows kernel) or <= 128 tokens (token-major kernel) */
     size_t tc_unit_base;    /* int32 [E + 1]: first tensor-core unit of each expert */
     size_t act_q_sorted;    /* u8 [P + M, K/2] quantised activations in sorted-slot order (B operand of GEMM1) */
     size_t act_sf_atoms;    /* u8 [max_tc_units, K/64, 512] activation scales, 128-row x 4-scale atoms per unit */
     size_t inter_sf_atoms;  /* u8 [max_tc_units, N/64, 512] intermediate scales, same layout */
+    size_t unit_done;       /* int32 [max_tc_units]: gate_up row tiles finished per unit (the down projection of a unit
+                               starts when all of them are) */
+    size_t token_done;      /* int32 [small-batch tokens, K/128]: down-projection rows finished per token and column tile */
+    size_t token_expect;    /* int32 [small-batch tokens]: rows a token receives (its local pairs + the shared expert) */
 } vmoe_ws_layout;
 
 int         vmoe_abi_version(void);
@@ -224,7 +230,8 @@ typedef struct vmoe_ep_ctx {
     int32_t experts_per_rank;
     int32_t capacity;             /* rows one source rank may send to one destination rank per call */
     int32_t max_local_tokens;     /* tokens a rank may bring to one call */
-    int32_t reserved[3];
+    int32_t wait_limit_us;        /* limit of every cross-GPU wait in microseconds; 0 = one second */
+    int32_t reserved[2];
     void*   slab[16];             /* slab of every rank as mapped into this process */
 } vmoe_ep_ctx;
 
@@ -237,25 +244,24 @@ int    vmoe_ep_ipc_open(const void* handle_64_bytes, void** out);
 int    vmoe_ep_ipc_close(void* mapped);
 
 /* One expert-parallel forward on this rank: route the M local tokens, dispatch them to the ranks
- * that own their experts, run the local experts on what arrived (tensor-core path; weights must
- * carry prepared scales), send each weighted row back to its owner, reduce.  shape->num_experts =
- * experts_per_rank, shape->num_global_experts = world * experts_per_rank.  `epoch` must be > 0 and
- * increase by one per call on every rank.  Every cross-GPU wait is bounded (about one second);
- * on expiry the call's status word reads VMOE_ERR_TIMEOUT and the output is not written.
- * VMOE_ERR_LIMIT in the status word: a (source, destination) pair exceeded `capacity`. */
+ * that own their experts, run the local experts on the rows that arrived (tensor-core path; weights
+ * must carry prepared scales), send each weighted row back to its owner, reduce (+ residual_bf16
+ * [M, hidden] when not NULL, as vmoe_extras.residual_bf16; may alias out_bf16).  shape->num_experts =
+ * experts_per_rank, shape->num_global_experts = world * experts_per_rank.  Every rank must make the
+ * same sequence of calls: the call number is kept in device memory inside the workspace (zeroed by the
+ * caller once, before the first call, together with the slab) and advanced by the call itself, so a
+ * call has no per-call host state and may be captured in a CUDA graph and replayed.
+ * Every cross-GPU wait is bounded (ctx->wait_limit_us).  Status word after the call: VMOE_ERR_TIMEOUT
+ * = a wait ran out on this rank; VMOE_ERR_LIMIT = this rank sent more than `capacity` rows to one
+ * destination; VMOE_ERR_PEER = another rank reported one of the two.  In all three cases the output
+ * of this call is not written on any rank that saw the mark; the status word stays set (and marks
+ * this rank's later calls) until vmoe_ep_read_status has read it. */
 int vmoe_ep_forward(const vmoe_ep_ctx* ctx, const vmoe_shape* shape, const vmoe_weights* routed,
                     const vmoe_weights* shared, const void* hidden_bf16, const float* router_logits,
-                    void* out_bf16, int32_t M, int32_t epoch, void* workspace, size_t workspace_bytes,
-                    void* stream);
-/* Status word of an expert-parallel workspace (synchronises the stream). */
+                    const void* residual_bf16, void* out_bf16, int32_t M, void* workspace,
+                    size_t workspace_bytes, void* stream);
+/* Status word of an expert-parallel workspace (synchronises the stream, clears the word). */
 int vmoe_ep_read_status(const vmoe_ep_ctx* ctx, const vmoe_shape* shape, void* workspace, void* stream);
-
-/* Development aid, no counterpart in the reference: cycle counters per warp role of the large-batch
- * tensor-core kernels, summed over CTAs since the previous call (MMA warp: waiting for data / for the
- * accumulator / issuing; epilogue: waiting / working; producer: waiting for a ring slot; items; stages).
- * Synchronises the device. */
-int vmoe_debug_read_profile(unsigned long long* out20);   /* [0..7] large-batch kernels, [8..15] decode kernels,
-                                                             [16..19] large-batch epilogue: TMEM loads, arithmetic, stores */
 
 /* Permutation by expert for callers that cannot allocate device memory.  It has no
  * counterpart in the reference.  Same tables as vmoe_build_tables, but written to arrays the
@@ -269,7 +275,10 @@ int vmoe_debug_read_profile(unsigned long long* out20);   /* [0..7] large-batch 
  * exits.  The first call on each device looks up the array's device address (that device must
  * be current); make that first call before any stream capture.  All calls share the one array,
  * which is cleared at the start of each call: calls that overlap on the GPU (two streams, two
- * threads) race and must be serialised by the caller. */
+ * threads) race and must be serialised by the caller.  The looked-up address is kept for the
+ * life of the process: do not use the entry point across a cudaDeviceReset.  With an expert_map
+ * every id must lie in [0, length of expert_map) -- the length is not an argument, so ids cannot
+ * be range-checked here (negative ids are dropped); without one, ids outside [0, E) are dropped. */
 int vmoe_permute_noalloc(const int32_t* topk_ids, const float* topk_weights,
                          const int32_t* expert_map, int32_t M, int32_t T, int32_t E,
                          int32_t has_shared, int32_t* expert_offsets, int32_t* sorted_pair,

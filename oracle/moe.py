@@ -32,19 +32,29 @@ def route(logits: np.ndarray, topk: int):
     by their own sum (:531-534).  Sums run sequentially in expert / rank order
     in float32, as the single device thread does.
 
+    Rows with a NaN or +inf logit: in the reference every probability of such a
+    row is NaN (``inf - inf``, or a NaN sum), no comparison succeeds and the ids
+    stay -1 (:516-528) -- an index nothing downstream can use.  Pinned here
+    instead: a NaN probability counts as 0 for the selection, so ids are always
+    distinct and in range (``0 .. T-1`` for such a row, lowest id wins the tie)
+    and the row's weights come out NaN (``0 / 0``), which marks the token's
+    output as invalid without any out-of-range access.
+
     Returns ``(topk_ids int32 [M, T], topk_weights float32 [M, T])``.
     """
     logits = np.asarray(logits, dtype=np.float32)
     M, E = logits.shape
-    mx = np.max(logits, axis=1, keepdims=True)
-    ex = np.exp((logits - mx).astype(np.float32)).astype(np.float32)
-    # sequential float32 sum (np.add.accumulate does not pair-wise reduce)
-    s = np.add.accumulate(ex, axis=1, dtype=np.float32)[:, -1:]
-    p = (ex * (np.float32(1.0) / s)).astype(np.float32)
-    order = np.argsort(-p, axis=1, kind="stable")[:, :topk]
-    sel = np.take_along_axis(p, order, axis=1)
-    ssum = np.add.accumulate(sel, axis=1, dtype=np.float32)[:, -1:]
-    w = (sel * (np.float32(1.0) / ssum)).astype(np.float32)
+    with np.errstate(invalid="ignore", over="ignore", divide="ignore"):
+        mx = np.fmax.reduce(logits, axis=1, keepdims=True, initial=-np.inf)     # fmaxf skips NaN
+        ex = np.exp((logits - mx).astype(np.float32)).astype(np.float32)
+        # sequential float32 sum (np.add.accumulate does not pair-wise reduce)
+        s = np.add.accumulate(ex, axis=1, dtype=np.float32)[:, -1:]
+        p = (ex * (np.float32(1.0) / s)).astype(np.float32)
+        p = np.where(np.isnan(p), np.float32(0), p)
+        order = np.argsort(-p, axis=1, kind="stable")[:, :topk]
+        sel = np.take_along_axis(p, order, axis=1)
+        ssum = np.add.accumulate(sel, axis=1, dtype=np.float32)[:, -1:]
+        w = (sel * (np.float32(1.0) / ssum)).astype(np.float32)
     return order.astype(np.int32), w
 
 

@@ -65,3 +65,60 @@ def load() -> RefHost | None:
     if not LIB.exists():
         return None
     return RefHost(C.CDLL(str(LIB)))
+
+
+# ---------------------------------------------------------------------------------------------
+# The reference's host permutation (build_group_tables, fused-moe/csrc/verdict_fused_grouped.cu:655-691)
+# and its router (moe_topk_select, fused-moe/csrc/megakernel_v1.cu:491-537), compiled by build_ref.py.
+# ---------------------------------------------------------------------------------------------
+LIB_TABLES = LIB.parent / "libref_tables.so"
+LIB_ROUTER = LIB.parent / "libref_router.so"
+
+
+class RefTables:
+    ROW = 10          # the reference's routing rows are ten experts wide
+
+    def __init__(self, lib: C.CDLL):
+        self.lib = lib
+        lib.ref_build_group_tables.restype = C.c_int
+        lib.ref_build_group_tables.argtypes = [_i32p, C.c_int, C.c_int, C.c_float, _i32p, _i32p, _i32p, _i32p, _f32p]
+
+    def build_group_tables(self, topk_ids: np.ndarray, weight: float = 1.0) -> dict:
+        """``topk_ids [M, T]`` (T <= 10) -> the reference's GroupTables as arrays.  The reference gives every
+        pair the same weight."""
+        ids = np.asarray(topk_ids, np.int32)
+        M, T = ids.shape
+        assert T <= self.ROW
+        rows = np.zeros((M, self.ROW), np.int32)
+        rows[:, :T] = ids
+        P = M * T
+        el, cnt, off = np.zeros(P, np.int32), np.zeros(P, np.int32), np.zeros(P + 1, np.int32)
+        gi, sw = np.zeros(P, np.int32), np.zeros(P, np.float32)
+        g = int(self.lib.ref_build_group_tables(rows, M, T, float(weight), el, cnt, off, gi, sw))
+        return dict(expert_list=el[:g], expert_token_count=cnt[:g], expert_token_offset=off[:g + 1],
+                    gather_idx=gi, scatter_weights=sw)
+
+
+class RefRouter:
+    def __init__(self, lib: C.CDLL):
+        self.lib = lib
+        lib.ref_topk_select.restype = None
+        lib.ref_topk_select.argtypes = [_f32p, C.c_int, C.c_int, _i32p, _f32p, _f32p]
+
+    def route(self, logits: np.ndarray, topk: int):
+        """Row by row through the reference's moe_topk_select -> ``(ids int32 [M, T], weights f32 [M, T])``."""
+        lg = np.ascontiguousarray(logits, np.float32)
+        M, E = lg.shape
+        ids, w = np.zeros((M, topk), np.int32), np.zeros((M, topk), np.float32)
+        scratch = np.zeros(E, np.float32)
+        for m in range(M):
+            self.lib.ref_topk_select(lg[m], E, topk, ids[m], w[m], scratch)
+        return ids, w
+
+
+def load_tables() -> RefTables | None:
+    return RefTables(C.CDLL(str(LIB_TABLES))) if LIB_TABLES.exists() else None
+
+
+def load_router() -> RefRouter | None:
+    return RefRouter(C.CDLL(str(LIB_ROUTER))) if LIB_ROUTER.exists() else None

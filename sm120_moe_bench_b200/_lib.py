@@ -27,12 +27,14 @@ class VmoeWeights(C.Structure):
 _LAYOUT_FIELDS = ["total_bytes", "topk_ids", "topk_weights", "expert_offsets", "sorted_pair",
                   "pair_slot", "gather_idx", "scatter_weights", "units", "counters", "act_q",
                   "act_sf", "inter_q", "inter_sf", "pair_out", "bitmap", "word_prefix", "tc_units",
-                  "tc_unit_base", "act_q_sorted", "act_sf_atoms", "inter_sf_atoms"]
+                  "tc_unit_base", "act_q_sorted", "act_sf_atoms", "inter_sf_atoms", "unit_done", "token_done",
+                  "token_expect"]
 
 
 class VmoeEpCtx(C.Structure):
     _fields_ = [("rank", C.c_int32), ("world", C.c_int32), ("experts_per_rank", C.c_int32),
-                ("capacity", C.c_int32), ("max_local_tokens", C.c_int32), ("reserved", C.c_int32 * 3),
+                ("capacity", C.c_int32), ("max_local_tokens", C.c_int32), ("wait_limit_us", C.c_int32),
+                ("reserved", C.c_int32 * 2),
                 ("slab", C.c_void_p * 16)]
 
 
@@ -75,9 +77,8 @@ SIGNATURES = {
     "vmoe_ep_ipc_open": (C.c_int, [_P, C.POINTER(C.c_void_p)]),
     "vmoe_ep_ipc_close": (C.c_int, [_P]),
     "vmoe_ep_forward": (C.c_int, [C.POINTER(VmoeEpCtx), C.POINTER(VmoeShape), C.POINTER(VmoeWeights),
-                                  C.POINTER(VmoeWeights), _P, _P, _P, C.c_int32, C.c_int32, _P, C.c_size_t, _P]),
+                                  C.POINTER(VmoeWeights), _P, _P, _P, _P, C.c_int32, _P, C.c_size_t, _P]),
     "vmoe_ep_read_status": (C.c_int, [C.POINTER(VmoeEpCtx), C.POINTER(VmoeShape), _P, _P]),
-    "vmoe_debug_read_profile": (C.c_int, [_P]),
     "vmoe_permute_noalloc": (C.c_int, [_P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                        _P, _P, _P, _P, _P, _P]),
 }

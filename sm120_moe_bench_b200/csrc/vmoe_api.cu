@@ -25,29 +25,40 @@ int tc_unit_cap(const vmoe_shape& s, int M) {
     return pairs <= TC_SMALL_PER_EXPERT * s.num_experts ? TC_UNIT_TOK_SMALL : TC_UNIT_TOK_PREFILL;
 }
 
+// Largest batch that can take the weights-as-rows kernel (and with it the in-kernel combine).
+int small_batch_tokens(const vmoe_shape* s) {
+    const long long m = TC_SMALL_PER_EXPERT * s->num_experts / s->topk;
+    return (int)(m < s->max_tokens ? m : s->max_tokens);
+}
+
+// Entries of the tensor-core unit list: every expert (+ shared) may end with one partial unit; full units are 16
+// tokens in the small regime (which ends at 7 E pairs + their shared rows) and 128 tokens above it.
 int max_tc_units(const vmoe_shape* s) {
     const long long S = (long long)s->max_tokens * s->topk + (s->has_shared ? s->max_tokens : 0);
-    // small-unit regime only exists up to M*T = 12E pairs (+ their shared rows)
-    long long small_slots = TC_SMALL_PER_EXPERT * s->num_experts + (s->has_shared ? TC_SMALL_PER_EXPERT * s->num_experts / s->topk + 1 : 0);
+    long long small_slots = (long long)small_batch_tokens(s) * (s->topk + (s->has_shared ? 1 : 0));
     if (small_slots > S) small_slots = S;
-    const long long a = (S + TC_UNIT_TOK - 1) / TC_UNIT_TOK, b = (small_slots + TC_UNIT_TOK_SMALL - 1) / TC_UNIT_TOK_SMALL;
+    const long long a = (S + TC_UNIT_TOK_PREFILL - 1) / TC_UNIT_TOK_PREFILL, b = (small_slots + TC_UNIT_TOK_SMALL - 1) / TC_UNIT_TOK_SMALL;
     return (int)(s->num_experts + 2 + (a > b ? a : b));
 }
 
+// The streaming GEMV kernels keep one activation row per 128 consumer threads x 32 elements.
+static bool gemv_shape_ok(const vmoe_shape* s) { return s->hidden <= 4096 && s->inter <= 1024; }
+
 static int check_shape(const vmoe_shape* s) {
     if (!s) return VMOE_ERR_NULL;
-    if (s->hidden <= 0 || s->hidden % 128 || s->hidden > 4096) return VMOE_ERR_SHAPE;
-    if (s->inter <= 0 || s->inter % 128 || s->inter > 1024) return VMOE_ERR_SHAPE;
+    if (s->hidden <= 0 || s->hidden % 128 || s->hidden > (1 << 20)) return VMOE_ERR_SHAPE;
+    if (s->inter <= 0 || s->inter % 128 || s->inter > (1 << 20)) return VMOE_ERR_SHAPE;
     if (s->num_experts <= 0 || s->topk <= 0 || s->topk > MAX_TOPK) return VMOE_ERR_SHAPE;
     if (s->max_tokens < 0) return VMOE_ERR_SHAPE;
     if (s->num_global_experts < s->num_experts) return VMOE_ERR_SHAPE;
     if (s->topk > s->num_global_experts) return VMOE_ERR_SHAPE;
     if (s->path < 0 || s->path > 2) return VMOE_ERR_SHAPE;
     if (s->path == VMOE_PATH_TC && (s->hidden % 256 || s->inter % 256)) return VMOE_ERR_SHAPE;
+    if (s->path == VMOE_PATH_GEMV && !gemv_shape_ok(s)) return VMOE_ERR_SHAPE;
     return VMOE_OK;
 }
 
-int compute_layout(const vmoe_shape* s, vmoe_ws_layout* L) {
+int compute_layout(const vmoe_shape* s, vmoe_ws_layout* L, int tc_units_override) {
     const int rc = check_shape(s);
     if (rc) return rc;
     const size_t M = (size_t)s->max_tokens, T = s->topk, E = s->num_experts, K = s->hidden, N = s->inter;
@@ -72,19 +83,23 @@ int compute_layout(const vmoe_shape* s, vmoe_ws_layout* L) {
     L->pair_out        = take(S * K * 4);
     L->bitmap          = take(E * words * 4);
     L->word_prefix     = take(E * words * 4);
-    const size_t TU = (size_t)max_tc_units(s);
+    const size_t TU = tc_units_override > 0 ? (size_t)tc_units_override : (size_t)max_tc_units(s);
     L->tc_units        = take(TU * 16);
     L->tc_unit_base    = take((E + 1) * 4);
     L->act_q_sorted    = take(S * K / 2);
     L->act_sf_atoms    = take(TU * (K / 64) * 512);
     L->inter_sf_atoms  = take(TU * ((N + 63) / 64) * 512);
+    const size_t small = (size_t)small_batch_tokens(s);
+    L->unit_done       = take(TU * 4);
+    L->token_done      = take(small * (K / TC_TILE_ROWS) * 4);
+    L->token_expect    = take(small * 4);
     L->total_bytes     = off;
     return VMOE_OK;
 }
 
-int resolve_workspace(const vmoe_shape* s, void* base, Workspace* ws) {
+int resolve_workspace(const vmoe_shape* s, void* base, Workspace* ws, int tc_units_override) {
     vmoe_ws_layout L;
-    const int rc = compute_layout(s, &L);
+    const int rc = compute_layout(s, &L, tc_units_override);
     if (rc) return rc;
     uint8_t* b = static_cast<uint8_t*>(base);
     ws->counters        = reinterpret_cast<int32_t*>(b + L.counters);
@@ -109,6 +124,11 @@ int resolve_workspace(const vmoe_shape* s, void* base, Workspace* ws) {
     ws->act_sf_atoms    = b + L.act_sf_atoms;
     ws->inter_sf_atoms  = b + L.inter_sf_atoms;
     ws->row_dst         = nullptr;
+    ws->unit_done       = reinterpret_cast<int32_t*>(b + L.unit_done);
+    ws->token_done      = reinterpret_cast<int32_t*>(b + L.token_done);
+    ws->token_expect    = reinterpret_cast<int32_t*>(b + L.token_expect);
+    ws->tc_unit_capacity = tc_units_override > 0 ? tc_units_override : max_tc_units(s);
+    ws->small_tokens    = small_batch_tokens(s);
     return VMOE_OK;
 }
 
@@ -147,6 +167,7 @@ static int pick_path(const vmoe_shape* s, const vmoe_weights* routed, const vmoe
     } else {
         *path = (prepared && shape_ok) ? VMOE_PATH_TC : VMOE_PATH_GEMV;
     }
+    if (*path == VMOE_PATH_GEMV && !gemv_shape_ok(s)) return VMOE_ERR_SHAPE;
     return VMOE_OK;
 }
 
@@ -180,7 +201,8 @@ const char* vmoe_status_string(int status) {
         case VMOE_ERR_CUDA: return "CUDA error";
         case VMOE_ERR_TIMEOUT: return "a bounded device-side wait ran out";
         case VMOE_ERR_SCALE: return "block-scale byte with the sign bit set";
-        case VMOE_ERR_LIMIT: return "size beyond a fixed maximum";
+        case VMOE_ERR_LIMIT: return "size beyond a fixed maximum, or expert id out of range";
+        case VMOE_ERR_PEER: return "another rank reported a failure for this call";
         default: return "unknown status";
     }
 }
@@ -249,8 +271,8 @@ int vmoe_stage_gate_up(const vmoe_shape* shape, const vmoe_weights* routed, cons
     if ((rc = pick_path(shape, routed, shared, &path))) return rc;
     const WeightSet r = to_set(routed), sh = to_set(shape->has_shared ? shared : nullptr);
     if (path == VMOE_PATH_TC)
-        return launch_tc_gate_up(*shape, r, sh, to_prep(routed, shape->has_shared ? shared : nullptr), M, ws,
-                                 static_cast<cudaStream_t>(stream));
+        return launch_tc(*shape, r, sh, to_prep(routed, shape->has_shared ? shared : nullptr), M, ws,
+                         static_cast<cudaStream_t>(stream), TC_PHASE_GATE_UP);
     return launch_gate_up(*shape, r, sh, M, ws, static_cast<cudaStream_t>(stream));
 }
 
@@ -264,8 +286,8 @@ int vmoe_stage_down(const vmoe_shape* shape, const vmoe_weights* routed, const v
     if ((rc = pick_path(shape, routed, shared, &path))) return rc;
     const WeightSet r = to_set(routed), sh = to_set(shape->has_shared ? shared : nullptr);
     if (path == VMOE_PATH_TC)
-        return launch_tc_down(*shape, r, sh, to_prep(routed, shape->has_shared ? shared : nullptr), M, ws,
-                              static_cast<cudaStream_t>(stream));
+        return launch_tc(*shape, r, sh, to_prep(routed, shape->has_shared ? shared : nullptr), M, ws,
+                         static_cast<cudaStream_t>(stream), TC_PHASE_DOWN);
     return launch_down(*shape, r, sh, M, ws, static_cast<cudaStream_t>(stream));
 }
 
@@ -325,26 +347,36 @@ int vmoe_forward_ex(const vmoe_shape* shape, const vmoe_weights* routed, const v
     }
     int path;
     if ((rc = pick_path(shape, routed, shared, &path))) return rc;
-    if (router_logits) {
-        if ((rc = launch_route(router_logits, M, shape->num_global_experts, shape->topk, ws.topk_ids,
-                               ws.topk_weights, st))) return rc;
-        topk_ids = ws.topk_ids; topk_weights = ws.topk_weights;
+    const int cap = tc_unit_cap(*shape, M);
+    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(out_bf16);
+    const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(hidden_bf16);
+    // small batches: router + tables (+ quantiser) in one CTA
+    bool front = false, quantized = false;
+    if (path == VMOE_PATH_TC && cap == TC_UNIT_TOK_SMALL) {
+        if ((rc = launch_front(*shape, router_logits, topk_ids, topk_weights, expert_map, x, M, ws, st, cap, &front, &quantized)))
+            return rc;
+        if (front && router_logits) { topk_ids = ws.topk_ids; topk_weights = ws.topk_weights; }
     }
-    if ((rc = launch_tables(*shape, topk_ids, topk_weights, expert_map, M, ws, st, tc_unit_cap(*shape, M),
-                            path != VMOE_PATH_TC))) return rc;
+    if (!front) {
+        if (router_logits) {
+            if ((rc = launch_route(router_logits, M, shape->num_global_experts, shape->topk, ws.topk_ids,
+                                   ws.topk_weights, st))) return rc;
+            topk_ids = ws.topk_ids; topk_weights = ws.topk_weights;
+        }
+        if ((rc = launch_tables(*shape, topk_ids, topk_weights, expert_map, M, ws, st, cap, path != VMOE_PATH_TC))) return rc;
+    }
     if (path == VMOE_PATH_TC) {
         const PreparedSet prep = to_prep(routed, shape->has_shared ? shared : nullptr);
-        if ((rc = launch_permute_quantize(*shape, static_cast<const __nv_bfloat16*>(hidden_bf16), topk_ids,
-                                          expert_map, M, ws, st))) return rc;
-        if ((rc = launch_tc_gate_up(*shape, r, sh, prep, M, ws, st))) return rc;
-        if ((rc = launch_tc_down(*shape, r, sh, prep, M, ws, st))) return rc;
+        if (!quantized && (rc = launch_permute_quantize(*shape, x, topk_ids, expert_map, M, ws, st))) return rc;
+        bool combined = false;
+        if ((rc = launch_tc(*shape, r, sh, prep, M, ws, st, TC_PHASE_GATE_UP | TC_PHASE_DOWN, out, residual, &combined))) return rc;
+        if (combined) return VMOE_OK;
     } else {
-        if ((rc = launch_quantize(static_cast<const __nv_bfloat16*>(hidden_bf16), M, shape->hidden, ws.act_q,
-                                  ws.act_sf, st))) return rc;
+        if ((rc = launch_quantize(x, M, shape->hidden, ws.act_q, ws.act_sf, st))) return rc;
         if ((rc = launch_gate_up(*shape, r, sh, M, ws, st))) return rc;
         if ((rc = launch_down(*shape, r, sh, M, ws, st))) return rc;
     }
-    return launch_combine(*shape, M, ws, static_cast<__nv_bfloat16*>(out_bf16), st, residual);
+    return launch_combine(*shape, M, ws, out, st, residual);
 }
 
 int vmoe_read_status(void* workspace, const vmoe_shape* shape, void* stream) {

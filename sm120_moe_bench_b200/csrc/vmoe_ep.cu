@@ -9,25 +9,39 @@
 // pair, already quantised (2304 bytes at K = 4096), and each weighted output row crosses once
 // (fp32, so the owner's fixed-order sum is bit-identical to the single-GPU result).
 //
-// Per forward call on rank r (one stream, no host synchronisation):
-//   route -> plan (slab positions) -> dispatch (quantise + 16-byte peer stores + release flag)
-//   -> gather (bounded acquire-wait on every source's flag, flat pair list) -> permutation tables
-//   -> permute (received rows into sorted-slot order) -> tcgen05 gate_up -> tcgen05 down whose
-//   epilogue stores each weighted row straight into the owner's combine slab over NVLink
-//   -> signal -> combine (bounded wait on every rank's flag, fixed-order sum -> bf16).
+// Per forward call on rank r (one stream, no host synchronisation, six launches):
+//   1 front     one CTA: route the local tokens, then the plan (destination rank and position inside the
+//               (source -> destination) slab of every pair, in pair order: deterministic)
+//   2 dispatch  quantise each 16-block once, store it into the slab of every destination of the token
+//               (16-byte peer stores); the last CTA publishes row counts and the call flag on every peer
+//   3 gather    one CTA: bounded acquire-wait on every source's flag, dense list of the rows that actually
+//               arrived (prefix over the sources' counts), permutation tables over exactly those rows
+//   4 permute   received rows into sorted-slot order + scale atoms, destination pointer of every output row
+//   5 experts   the tcgen05 kernels of the single-GPU layer; the down projection's epilogue stores each
+//               weighted row straight into the token owner's combine slab over NVLink; the last CTA
+//               publishes the "rows are in place" flag on every peer
+//   6 combine   bounded wait on every rank's flag, fixed-order sum (+ residual) -> bf16; the last CTA
+//               advances the call counter
+// The call number lives in device memory (a counter in the workspace, advanced by step 6), so the chain has
+// no per-call host argument and can be captured in a CUDA graph and replayed.  Every flag carries the call
+// number and an error bit: a rank that ran into a time-out or a capacity overflow still signals, marked,
+// and every rank that sees a marked flag reports VMOE_ERR_PEER and leaves its output unwritten.
 // Plain peer loads / stores only: no multimem, no TMA from peer memory.
 #include "vmoe_common.cuh"
+#include "vmoe_phases.cuh"
 
 #include <string.h>
 
 namespace vmoe {
 
 constexpr int EP_MAX_RANKS = 16;
+constexpr int EP_FRONT_THREADS = 1024;
+constexpr int EP_FRONT_ROUTE_TOKENS = 64;      // above this the router runs as its own grid-wide launch
 
 struct EpFlags {            // lives at the start of every rank's slab; written by peers
-    int32_t dispatch_flag[EP_MAX_RANKS];    // [src] epoch of the last completed dispatch from src
-    int32_t dispatch_count[EP_MAX_RANKS];   // [src] rows src wrote for that epoch
-    int32_t combine_flag[EP_MAX_RANKS];     // [src] epoch of the last completed down projection on src
+    int32_t dispatch_flag[EP_MAX_RANKS];    // [src] 2 * call + error bit of the last completed dispatch from src
+    int32_t dispatch_count[EP_MAX_RANKS];   // [src] rows src wrote for that call
+    int32_t combine_flag[EP_MAX_RANKS];     // [src] 2 * call + error bit of the last completed down projection on src
     int32_t pad[16];
 };
 
@@ -50,12 +64,22 @@ static EpLayout ep_layout(int world, int capacity, int max_local_tokens, int K, 
     return L;
 }
 
+// device-side state of the exchange (local workspace, behind the regular workspace)
+struct EpState {
+    int32_t epoch;              // calls completed on this rank
+    int32_t ticket_dispatch, ticket_experts, ticket_combine;
+    int32_t recv_rows;          // rows that arrived for this call
+    int32_t src_base[EP_MAX_RANKS + 1];   // exclusive prefix of the rows per source
+    int32_t send_count[EP_MAX_RANKS];
+};
+
 struct EpDev {              // by value into kernels
-    int rank, world, e_local, capacity, epoch;
+    int rank, world, e_local, capacity;
+    unsigned long long wait_ns;             // limit of every cross-GPU wait
     uint8_t* slab[EP_MAX_RANKS];            // every rank's slab as mapped into this process
     EpLayout L;
-    // plan scratch (local workspace)
-    int32_t* plan_dest; int32_t* plan_pos; int32_t* send_count; int32_t* ticket;
+    EpState* state;
+    int32_t* plan_dest; int32_t* plan_pos;
     int32_t* flat_ids; float* flat_w; float** row_dst;
 };
 
@@ -67,34 +91,43 @@ __device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-// bounded wait for *p >= want; false when the limit passes
-__device__ __forceinline__ bool wait_flag(const int32_t* p, int32_t want) {
-    if (ld_acquire_sys(p) >= want) return true;
+// Bounded wait until the flag carries call number `call` (or a later one).  Returns the flag value, or -1
+// when the limit passes.
+__device__ __forceinline__ int32_t wait_flag(const int32_t* p, int32_t call, unsigned long long limit_ns) {
+    int32_t v = ld_acquire_sys(p);
+    if ((v >> 1) >= call) return v;
     const unsigned long long t0 = global_timer_ns();
     for (uint32_t i = 1;; ++i) {
-        if (ld_acquire_sys(p) >= want) return true;
-        if ((i & 15u) == 0 && global_timer_ns() - t0 > MBAR_WAIT_LIMIT_NS) return false;
+        v = ld_acquire_sys(p);
+        if ((v >> 1) >= call) return v;
+        if ((i & 15u) == 0 && global_timer_ns() - t0 > limit_ns) return -1;
     }
 }
 
 // ---------------------------------------------------------------------------------
-// plan: destination rank and position inside the (src -> dst) slab of every pair, in pair order
-// (deterministic).  Pair index p = m*T + j for routed pairs, M*T + m for the shared expert, which
-// stays on the owner.  One CTA.
+// 1 front: router (one warp per token, several rounds) + plan.  Pair index p = m*T + j for routed pairs,
+// M*T + m for the shared expert, which stays on the owner.  One CTA.
 // ---------------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024)
-ep_plan_kernel(const int32_t* __restrict__ topk_ids, int M, int T, int has_shared, EpDev ep) {
+__global__ void __launch_bounds__(EP_FRONT_THREADS)
+ep_front_kernel(const float* __restrict__ logits, int num_global, int32_t* __restrict__ topk_ids, float* __restrict__ topk_w,
+                int M, int T, int has_shared, EpDev ep) {
     __shared__ int32_t s_cnt[32][EP_MAX_RANKS];     // pairs per (warp, destination) in the current chunk
     __shared__ int32_t s_base[EP_MAX_RANKS];        // pairs per destination in earlier chunks
+    extern __shared__ float s_prob[];               // [warps][num_global]
     pdl_begin();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    if (logits) {
+        for (int m = warp; m < M; m += nwarps)
+            route_token(logits + (size_t)m * num_global, s_prob + (size_t)warp * num_global, num_global, T, lane,
+                        topk_ids + (size_t)m * T, topk_w + (size_t)m * T);
+    }
     const int P = M * T + (has_shared ? M : 0);
     if (tid < ep.world) s_base[tid] = 0;
     __syncthreads();
     for (int p0 = 0; p0 < P; p0 += blockDim.x) {
         const int p = p0 + tid;
         int dest = -1;
-        if (p < P) dest = (p < M * T) ? topk_ids[p] / ep.e_local : ep.rank;
+        if (p < P) dest = (p < M * T) ? min(max(topk_ids[p] / ep.e_local, 0), ep.world - 1) : ep.rank;
         int wrank = 0;
         for (int d = 0; d < ep.world; ++d) {
             const unsigned bal = __ballot_sync(0xffffffffu, dest == d);
@@ -116,12 +149,11 @@ ep_plan_kernel(const int32_t* __restrict__ topk_ids, int M, int T, int has_share
         }
         __syncthreads();
     }
-    if (tid < ep.world) ep.send_count[tid] = s_base[tid];
-    if (tid == 0) *ep.ticket = 0;
+    if (tid < ep.world) ep.state->send_count[tid] = s_base[tid];
 }
 
 // ---------------------------------------------------------------------------------
-// dispatch: quantise each 16-block once (same arithmetic as quantize_kernel), store it into the
+// 2 dispatch: quantise each 16-block once (same arithmetic as quantize_kernel), store it into the
 // slab of every destination of the token, then release the per-source flag on every peer.
 // ---------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
@@ -170,124 +202,198 @@ ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restric
             reinterpret_cast<uint2*>(slab + ep.L.recv_q + row * (K / 2))[kb] = make_uint2(lo, hi);
             (slab + ep.L.recv_sf + row * (K / 16))[kb] = sb;
             if (kb == 0) {
-                const int le = (j < T) ? topk_ids[p] % ep.e_local : ep.e_local;     // shared expert = local id E_local
+                const int id = (j < T) ? topk_ids[p] : 0;
+                const int le = (j < T) ? id - (id / ep.e_local) * ep.e_local : ep.e_local;     // shared expert = local id E_local
                 const float w = (j < T) ? topk_w[p] : 1.0f;
                 reinterpret_cast<int4*>(slab + ep.L.recv_meta)[row] = make_int4(le, p, __float_as_int(w), 0);
             }
         }
     }
-    // last CTA to finish publishes the counts and the epoch flag on every peer
+    // last CTA to finish publishes the counts and the call flag on every peer
     __threadfence_system();
     __syncthreads();
     __shared__ int s_last;
-    if (threadIdx.x == 0) s_last = (atomicAdd(ep.ticket, 1) == (int)gridDim.x - 1);
+    if (threadIdx.x == 0) s_last = (atomicAdd(&ep.state->ticket_dispatch, 1) == (int)gridDim.x - 1);
     __syncthreads();
     if (s_last && threadIdx.x < ep.world) {
         __threadfence_system();
         const int d = threadIdx.x;
         EpFlags* f = reinterpret_cast<EpFlags*>(ep.slab[d] + ep.L.flags);
-        const int c = min(ep.send_count[d], ep.capacity);
+        const int c = min(ep.state->send_count[d], ep.capacity);
+        const int32_t call = ep.state->epoch + 1;
+        const int32_t bad = (*(volatile int32_t*)status) != 0;
         f->dispatch_count[ep.rank] = c;
         __threadfence_system();
-        st_release_sys(&f->dispatch_flag[ep.rank], ep.epoch);
+        st_release_sys(&f->dispatch_flag[ep.rank], call * 2 + bad);
     }
+    if (s_last && threadIdx.x == 0) ep.state->ticket_dispatch = 0;
 }
 
 // ---------------------------------------------------------------------------------
-// gather: wait (bounded) for every source's flag, then lay the received pairs out as a flat list of
-// "tokens" with one expert each: index f = src * capacity + i; unused positions get expert -1.
+// 3 gather + tables: wait (bounded) for every source's flag, make the dense list of the rows that arrived
+// -- row i of the list is (source s, position i - src_base[s]), one single-expert "token" each -- and build
+// the permutation tables over exactly those rows.  One CTA.
 // ---------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256)
-ep_gather_kernel(EpDev ep, int32_t* status) {
+__device__ __forceinline__ int ep_source_of(const int32_t* base, int world, int i) {
+    int s = 0;
+    while (s + 1 < world && i >= base[s + 1]) ++s;
+    return s;
+}
+
+__global__ void __launch_bounds__(TC_TILE_ROWS * 8)
+ep_gather_tables_kernel(EpDev ep, TableArgs a, int smem_table_words) {
+    extern __shared__ int32_t s_mem[];          // [E] counts, [3 * nthr] scan, then bitmap + running popcounts when they fit
+    __shared__ int32_t s_base[EP_MAX_RANKS + 1];
     __shared__ int s_ok;
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    int32_t* s_count = s_mem; int32_t* s_scan = s_mem + a.E;
     pdl_begin();
+    int32_t* status = a.ws.counters + CNT_STATUS;
     const EpFlags* f = reinterpret_cast<const EpFlags*>(ep.slab[ep.rank] + ep.L.flags);
-    if (threadIdx.x == 0) s_ok = 1;
+    const int32_t call = ep.state->epoch + 1;
+    if (tid == 0) s_ok = 1;
     __syncthreads();
-    if (threadIdx.x < ep.world) {
-        if (!wait_flag(&f->dispatch_flag[threadIdx.x], ep.epoch)) { atomicExch(status, VMOE_ERR_TIMEOUT); s_ok = 0; }
+    if (tid < ep.world) {
+        const int32_t v = wait_flag(&f->dispatch_flag[tid], call, ep.wait_ns);
+        if (v < 0) { atomicExch(status, VMOE_ERR_TIMEOUT); s_ok = 0; }
+        else if (v & 1) atomicCAS(status, 0, VMOE_ERR_PEER);          // the sender dropped rows: results are incomplete
     }
     __syncthreads();
-    const int total = ep.world * ep.capacity;
+    if (tid == 0) {
+        int run = 0;
+        for (int s = 0; s < ep.world; ++s) {
+            s_base[s] = run;
+            run += s_ok ? min(max(f->dispatch_count[s], 0), ep.capacity) : 0;
+        }
+        s_base[ep.world] = run;
+        for (int s = 0; s <= ep.world; ++s) ep.state->src_base[s] = s_base[s];
+        ep.state->recv_rows = run;
+    }
+    __syncthreads();
+    const int R = s_base[ep.world];
     const int4* meta = reinterpret_cast<const int4*>(ep.slab[ep.rank] + ep.L.recv_meta);
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-        const int s = i / ep.capacity, pos = i % ep.capacity;
-        const bool live = s_ok && pos < f->dispatch_count[s];
-        const int4 mt = live ? meta[i] : make_int4(-1, 0, 0, 0);
+    for (int i = tid; i < R; i += nthr) {
+        const int s = ep_source_of(s_base, ep.world, i);
+        const int4 mt = meta[(size_t)s * ep.capacity + (i - s_base[s])];
         ep.flat_ids[i] = mt.x;
         ep.flat_w[i] = __int_as_float(mt.z);
     }
+    __syncthreads();
+    a.M = R; a.words = (R + 31) / 32;
+    if ((long long)a.E * a.words * 2 <= smem_table_words) {
+        a.ws.bitmap = reinterpret_cast<uint32_t*>(s_scan + 3 * nthr);
+        a.ws.word_prefix = reinterpret_cast<int32_t*>(a.ws.bitmap + (size_t)a.E * a.words);
+    }
+    phase_clear(a, tid, nthr);       __syncthreads();
+    phase_mark(a, tid, nthr);        __syncthreads();
+    phase_count(a, tid >> 5, nthr >> 5, tid & 31, s_count); __syncthreads();
+    phase_scan(a, tid, nthr, s_count, s_scan); __syncthreads();
+    phase_place(a, tid, nthr);
 }
 
 // ---------------------------------------------------------------------------------
-// permute: received FP4 rows -> sorted-slot order + scale atoms (B operand of the tensor-core
-// GEMM), and the destination of each slot's output row in its owner's combine slab.
+// 4 permute: received FP4 rows -> sorted-slot order + scale atoms (B operand of the tensor-core GEMM), and
+// the destination of each slot's output row in its owner's combine slab.  Grid-stride over the rows that
+// arrived (their number is only known on the device).
 // ---------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 ep_permute_kernel(EpDev ep, int K, int tc_cap, Workspace ws) {
+    __shared__ int32_t s_base[EP_MAX_RANKS + 1];
     pdl_begin();
+    if (threadIdx.x <= ep.world) s_base[threadIdx.x] = ep.state->src_base[threadIdx.x];
+    __syncthreads();
     const int bpr = K / SF_BLOCK;
-    const long long total = (long long)ep.world * ep.capacity * bpr;
-    const long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (b >= total) return;
-    const int i = (int)(b / bpr), kb = (int)(b % bpr);
-    const int slot = ws.pair_slot[i];
-    if (slot < 0) return;
+    const long long total = (long long)s_base[ep.world] * bpr;
     const uint8_t* slab = ep.slab[ep.rank];
-    const uint2 q = reinterpret_cast<const uint2*>(slab + ep.L.recv_q + (size_t)i * (K / 2))[kb];
-    const uint8_t sb = (slab + ep.L.recv_sf + (size_t)i * (K / 16))[kb];
-    const int e = ep.flat_ids[i];
-    const int rank_in_e = slot - ws.expert_offsets[e];
-    const int unit = ws.tc_unit_base[e] + (rank_in_e >> (31 - __clz(tc_cap)));     // tc_cap is 16, 64 or 128
-    const int r = rank_in_e & (tc_cap - 1);
-    reinterpret_cast<uint2*>(ws.act_q_sorted + (size_t)slot * (K / 2))[kb] = q;
-    ws.act_sf_atoms[((size_t)unit * (K / 64) + (kb >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = sb;
-    if (kb == 0) {
-        const int4 mt = reinterpret_cast<const int4*>(slab + ep.L.recv_meta)[i];
-        const int src = i / ep.capacity;
-        ep.row_dst[slot] = reinterpret_cast<float*>(ep.slab[src] + ep.L.comb) + (size_t)mt.y * K;   // row of pair id mt.y
+    const int cap_shift = 31 - __clz(tc_cap);                     // tc_cap is 16 or 128
+    for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < total; b += (long long)gridDim.x * blockDim.x) {
+        const int i = (int)(b / bpr), kb = (int)(b % bpr);
+        const int slot = ws.pair_slot[i];
+        if (slot < 0) continue;
+        const int src = ep_source_of(s_base, ep.world, i);
+        const size_t row = (size_t)src * ep.capacity + (i - s_base[src]);
+        const uint2 q = reinterpret_cast<const uint2*>(slab + ep.L.recv_q + row * (K / 2))[kb];
+        const uint8_t sb = (slab + ep.L.recv_sf + row * (K / 16))[kb];
+        const int e = ep.flat_ids[i];
+        const int rank_in_e = slot - ws.expert_offsets[e];
+        const int unit = ws.tc_unit_base[e] + (rank_in_e >> cap_shift);
+        const int r = rank_in_e & (tc_cap - 1);
+        reinterpret_cast<uint2*>(ws.act_q_sorted + (size_t)slot * (K / 2))[kb] = q;
+        if (unit < ws.tc_unit_capacity)
+            ws.act_sf_atoms[((size_t)unit * (K / 64) + (kb >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = sb;
+        if (kb == 0) {
+            const int4 mt = reinterpret_cast<const int4*>(slab + ep.L.recv_meta)[row];
+            ep.row_dst[slot] = reinterpret_cast<float*>(ep.slab[src] + ep.L.comb) + (size_t)mt.y * K;   // row of pair id mt.y
+        }
     }
 }
 
-__global__ void ep_signal_kernel(EpDev ep) {
+// 5b: the "rows are in place" flag when the token-major kernels ran (the weights-as-rows kernel publishes it itself)
+__global__ void ep_signal_kernel(EpDev ep, const int32_t* status) {
     pdl_begin();
     __threadfence_system();
     if (threadIdx.x < ep.world) {
         EpFlags* f = reinterpret_cast<EpFlags*>(ep.slab[threadIdx.x] + ep.L.flags);
-        st_release_sys(&f->combine_flag[ep.rank], ep.epoch);
+        const int32_t bad = (*(volatile const int32_t*)status) != 0;
+        st_release_sys(&f->combine_flag[ep.rank], (ep.state->epoch + 1) * 2 + bad);
     }
 }
 
-// out[m, :] = bf16( sum_{j < T} comb[m*T + j, :] + comb[M*T + m, :] ), fp32, ascending j: the same
-// order as combine_kernel, over rows that arrived from the ranks owning the experts.
+// ---------------------------------------------------------------------------------
+// 6 combine: out[m, :] = bf16( sum_{j < T} comb[m*T + j, :] + comb[M*T + m, :] ) (+ residual), fp32, ascending
+// j: the same order as combine_kernel, over rows that arrived from the ranks owning the experts.  Nothing is
+// written when a wait ran out or a rank marked its flag.  The last CTA advances the call counter.
+// ---------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
-ep_combine_kernel(EpDev ep, int M, int K, int T, int has_shared, __nv_bfloat16* __restrict__ out, int32_t* status) {
+ep_combine_kernel(EpDev ep, int M, int K, int T, int has_shared, const __nv_bfloat16* residual, __nv_bfloat16* out,
+                  int32_t* status) {
     __shared__ int s_ok;
     pdl_begin();
     const EpFlags* f = reinterpret_cast<const EpFlags*>(ep.slab[ep.rank] + ep.L.flags);
+    const int32_t call = ep.state->epoch + 1;
     if (threadIdx.x == 0) s_ok = 1;
     __syncthreads();
     if (threadIdx.x < ep.world) {
-        if (!wait_flag(&f->combine_flag[threadIdx.x], ep.epoch)) { atomicExch(status, VMOE_ERR_TIMEOUT); s_ok = 0; }
+        const int32_t v = wait_flag(&f->combine_flag[threadIdx.x], call, ep.wait_ns);
+        if (v < 0) { atomicExch(status, VMOE_ERR_TIMEOUT); s_ok = 0; }
+        else if (v & 1) { atomicCAS(status, 0, VMOE_ERR_PEER); s_ok = 0; }
     }
     __syncthreads();
-    if (!s_ok) return;
-    const float* comb = reinterpret_cast<const float*>(ep.slab[ep.rank] + ep.L.comb);
-    const int k4 = K / 4;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)M * k4; i += (long long)gridDim.x * blockDim.x) {
-        const int m = (int)(i / k4), c = (int)(i % k4);
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int j = 0; j < T; ++j) {
-            const float4 v = reinterpret_cast<const float4*>(comb + (size_t)(m * T + j) * K)[c];
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    if (s_ok && *(volatile int32_t*)status != 0) s_ok = 0;      // benign race: every thread stores the same value
+    __syncthreads();
+    if (s_ok) {
+        const float* comb = reinterpret_cast<const float*>(ep.slab[ep.rank] + ep.L.comb);
+        const int k4 = K / 4;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)M * k4; i += (long long)gridDim.x * blockDim.x) {
+            const int m = (int)(i / k4), c = (int)(i % k4);
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j = 0; j < T; ++j) {
+                const float4 v = reinterpret_cast<const float4*>(comb + (size_t)(m * T + j) * K)[c];
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+            if (has_shared) {
+                const float4 v = reinterpret_cast<const float4*>(comb + (size_t)(M * T + m) * K)[c];
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+            __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+            if (residual) {
+                // x + moe(x) with the layer output rounded to bf16 first: the same bits as a separate bf16 add
+                const uint2 r = reinterpret_cast<const uint2*>(residual + (size_t)m * K)[c];
+                const __nv_bfloat162 r0 = *reinterpret_cast<const __nv_bfloat162*>(&r.x), r1 = *reinterpret_cast<const __nv_bfloat162*>(&r.y);
+                lo = __floats2bfloat162_rn(__bfloat162float(r0.x) + __bfloat162float(lo.x), __bfloat162float(r0.y) + __bfloat162float(lo.y));
+                hi = __floats2bfloat162_rn(__bfloat162float(r1.x) + __bfloat162float(hi.x), __bfloat162float(r1.y) + __bfloat162float(hi.y));
+            }
+            uint2 o; o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
+            reinterpret_cast<uint2*>(out + (size_t)m * K)[c] = o;
         }
-        if (has_shared) {
-            const float4 v = reinterpret_cast<const float4*>(comb + (size_t)(M * T + m) * K)[c];
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        if (atomicAdd(&ep.state->ticket_combine, 1) == (int)gridDim.x - 1) {
+            ep.state->ticket_combine = 0;
+            ep.state->epoch = call;           // every kernel of this call has read the old value
         }
-        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
-        uint2 o; o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
-        reinterpret_cast<uint2*>(out + (size_t)m * K)[c] = o;
     }
 }
 
@@ -301,7 +407,7 @@ using namespace vmoe;
 static int ep_check(const vmoe_ep_ctx* c) {
     if (!c) return VMOE_ERR_NULL;
     if (c->world < 1 || c->world > EP_MAX_RANKS || c->rank < 0 || c->rank >= c->world) return VMOE_ERR_SHAPE;
-    if (c->experts_per_rank <= 0 || c->capacity <= 0 || c->max_local_tokens <= 0) return VMOE_ERR_SHAPE;
+    if (c->experts_per_rank <= 0 || c->capacity <= 0 || c->max_local_tokens <= 0 || c->wait_limit_us < 0) return VMOE_ERR_SHAPE;
     for (int i = 0; i < c->world; ++i) if (!c->slab[i]) return VMOE_ERR_NULL;
     return VMOE_OK;
 }
@@ -319,6 +425,20 @@ static vmoe_shape ep_local_shape(const vmoe_ep_ctx* c, const vmoe_shape* s, bool
     return l;
 }
 
+// Entries of the tensor-core unit list of an expert-parallel workspace: the rows a rank receives depend on the
+// other ranks' routing, so the list is sized for the worst case in 16-token units whatever this rank's own batch.
+static int ep_tc_units(const vmoe_ep_ctx* c) {
+    const long long rows = (long long)c->world * c->capacity;
+    return (int)(c->experts_per_rank + 3 + rows / TC_UNIT_TOK_SMALL);
+}
+
+static size_t ep_extra_bytes(const vmoe_ep_ctx* c, const vmoe_shape* s) {
+    const size_t rows = (size_t)c->world * c->capacity;
+    const size_t P = (size_t)c->max_local_tokens * (s->topk + 1);
+    // state, plan_dest, plan_pos [P], flat_ids, flat_w [rows], row_dst [rows], local topk ids / weights [P]
+    return ep_align(sizeof(EpState)) + ep_align(P * 4) * 2 + ep_align(rows * 4) * 2 + ep_align(rows * 8) + ep_align(P * 4) * 2;
+}
+
 extern "C" {
 
 size_t vmoe_ep_slab_bytes(const vmoe_ep_ctx* ctx, const vmoe_shape* shape) {
@@ -329,12 +449,9 @@ size_t vmoe_ep_slab_bytes(const vmoe_ep_ctx* ctx, const vmoe_shape* shape) {
 size_t vmoe_ep_workspace_bytes(const vmoe_ep_ctx* ctx, const vmoe_shape* shape) {
     if (ep_check(ctx) || !shape) return 0;
     const vmoe_shape l = ep_local_shape(ctx, shape, true);
-    const size_t base = vmoe_workspace_bytes(&l);
-    if (!base) return 0;
-    const size_t rows = (size_t)ctx->world * ctx->capacity;
-    const size_t P = (size_t)ctx->max_local_tokens * (shape->topk + 1);
-    // + plan_dest, plan_pos [P], send_count[16], ticket, flat_ids, flat_w [rows], row_dst [rows], local topk ids / weights
-    return base + ep_align(P * 4) * 2 + 512 + ep_align(rows * 4) * 2 + ep_align(rows * 8) + ep_align(P * 4) * 2;
+    vmoe_ws_layout L;
+    if (compute_layout(&l, &L, ep_tc_units(ctx))) return 0;
+    return L.total_bytes + ep_extra_bytes(ctx, shape);
 }
 
 int vmoe_ep_alloc(size_t bytes, void** out) {
@@ -359,38 +476,41 @@ int vmoe_ep_ipc_close(void* p) { return cuda_status(cudaIpcCloseMemHandle(p)); }
 
 int vmoe_ep_forward(const vmoe_ep_ctx* ctx, const vmoe_shape* shape, const vmoe_weights* routed,
                     const vmoe_weights* shared, const void* hidden_bf16, const float* router_logits,
-                    void* out_bf16, int32_t M, int32_t epoch, void* workspace, size_t workspace_bytes,
+                    const void* residual_bf16, void* out_bf16, int32_t M, void* workspace, size_t workspace_bytes,
                     void* stream) {
     int rc = ep_check(ctx);
     if (rc) return rc;
     if (!shape || !routed || !workspace) return VMOE_ERR_NULL;
     if (M > 0 && (!hidden_bf16 || !router_logits || !out_bf16)) return VMOE_ERR_NULL;   // a rank may bring no tokens
     if (shape->has_shared && !shared) return VMOE_ERR_NULL;
-    if (M < 0 || M > ctx->max_local_tokens || epoch <= 0) return VMOE_ERR_SHAPE;
+    if (M < 0 || M > ctx->max_local_tokens) return VMOE_ERR_SHAPE;
     if (shape->num_global_experts != ctx->world * ctx->experts_per_rank || shape->num_experts != ctx->experts_per_rank) return VMOE_ERR_SHAPE;
-    if (shape->hidden % 256 || shape->inter % 256) return VMOE_ERR_SHAPE;
+    if (shape->hidden % 256 || shape->inter % 256 || shape->topk < 1 || shape->topk > MAX_TOPK) return VMOE_ERR_SHAPE;
     if (!routed->w13_sf_atoms || !routed->w2_sf_atoms || (shape->has_shared && (!shared->w13_sf_atoms || !shared->w2_sf_atoms)))
         return VMOE_ERR_NULL;                              // the expert-parallel path runs on the tensor cores only
     if (workspace_bytes < vmoe_ep_workspace_bytes(ctx, shape)) return VMOE_ERR_WORKSPACE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int K = shape->hidden, T = shape->topk;
     const vmoe_shape lt = ep_local_shape(ctx, shape, true), lk = ep_local_shape(ctx, shape, false);
+    const int tc_units = ep_tc_units(ctx);
     Workspace ws;
-    if ((rc = resolve_workspace(&lt, workspace, &ws))) return rc;
+    if ((rc = resolve_workspace(&lt, workspace, &ws, tc_units))) return rc;
     // EP scratch behind the regular workspace
-    uint8_t* extra = static_cast<uint8_t*>(workspace) + vmoe_workspace_bytes(&lt);
+    vmoe_ws_layout L;
+    compute_layout(&lt, &L, tc_units);
+    uint8_t* extra = static_cast<uint8_t*>(workspace) + L.total_bytes;
     const size_t rows = (size_t)ctx->world * ctx->capacity;
     const size_t P = (size_t)ctx->max_local_tokens * (T + 1);
     EpDev ep;
     memset(&ep, 0, sizeof(ep));
-    ep.rank = ctx->rank; ep.world = ctx->world; ep.e_local = ctx->experts_per_rank; ep.capacity = ctx->capacity; ep.epoch = epoch;
+    ep.rank = ctx->rank; ep.world = ctx->world; ep.e_local = ctx->experts_per_rank; ep.capacity = ctx->capacity;
+    ep.wait_ns = ctx->wait_limit_us > 0 ? (unsigned long long)ctx->wait_limit_us * 1000ull : MBAR_WAIT_LIMIT_NS;
     for (int i = 0; i < ctx->world; ++i) ep.slab[i] = static_cast<uint8_t*>(ctx->slab[i]);
     ep.L = ep_layout(ctx->world, ctx->capacity, ctx->max_local_tokens, K, T);
     auto take = [&](size_t b) { uint8_t* p = extra; extra += ep_align(b); return p; };
+    ep.state = reinterpret_cast<EpState*>(take(sizeof(EpState)));
     ep.plan_dest = reinterpret_cast<int32_t*>(take(P * 4));
     ep.plan_pos = reinterpret_cast<int32_t*>(take(P * 4));
-    ep.send_count = reinterpret_cast<int32_t*>(take(256));
-    ep.ticket = reinterpret_cast<int32_t*>(take(256));
     ep.flat_ids = reinterpret_cast<int32_t*>(take(rows * 4));
     ep.flat_w = reinterpret_cast<float*>(take(rows * 4));
     ep.row_dst = reinterpret_cast<float**>(take(rows * 8));
@@ -398,27 +518,52 @@ int vmoe_ep_forward(const vmoe_ep_ctx* ctx, const vmoe_shape* shape, const vmoe_
     float* loc_w = reinterpret_cast<float*>(take(P * 4));
     int32_t* status = ws.counters + CNT_STATUS;
     const int has_shared = shape->has_shared ? 1 : 0;
+    const int Eg = shape->num_global_experts;
 
-    if ((rc = launch_route(router_logits, M, shape->num_global_experts, T, loc_ids, loc_w, st))) return rc;
-    launch_pdl(ep_plan_kernel, 1u, 1024u, 0, st, loc_ids, M, T, has_shared, ep);
+    // 1 front
+    {
+        const float* lg = router_logits;
+        size_t smem = (size_t)(EP_FRONT_THREADS / 32) * Eg * sizeof(float);
+        if (M > EP_FRONT_ROUTE_TOKENS || smem > 160 * 1024) {
+            if ((rc = launch_route(router_logits, M, Eg, T, loc_ids, loc_w, st))) return rc;
+            lg = nullptr; smem = 0;
+        }
+        static bool attr_done = false;
+        if (!attr_done) {
+            cudaFuncSetAttribute(ep_front_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+            cudaFuncSetAttribute(ep_gather_tables_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            attr_done = true;
+        }
+        launch_pdl(ep_front_kernel, 1u, (unsigned)EP_FRONT_THREADS, smem, st, lg, Eg, loc_ids, loc_w, M, T, has_shared, ep);
+    }
+    // 2 dispatch
     {
         const long long nb = (long long)M * (K / SF_BLOCK);
         const unsigned grid = (unsigned)((nb + 255) / 256 > 0 ? (nb + 255) / 256 : 1);
         launch_pdl(ep_dispatch_kernel, grid, 256u, 0, st, static_cast<const __nv_bfloat16*>(hidden_bf16), loc_ids, loc_w,
                    M, K, T, has_shared, ep, status);
     }
-    launch_pdl(ep_gather_kernel, 64u, 256u, 0, st, ep, status);
-    const int Mr = (int)rows;
-    // Tokens per work unit: the slab is sized for the worst case, so the choice is made from the rows a
-    // rank receives under balanced routing (about its own M * (T + 1)), not from the slab capacity.
+    // Tokens per work unit and with them the kernel: chosen from the rows a rank receives under balanced routing
+    // (about its own M * (T + 1)); any other row count is still computed correctly, only not by the faster kernel.
     vmoe_shape est = lt;
     est.topk = 1;
     const int cap = tc_unit_cap(est, M * (T + 1));
-    if ((rc = launch_tables(lt, ep.flat_ids, ep.flat_w, nullptr, Mr, ws, st, cap, false))) return rc;
+    // 3 gather + tables
     {
-        const long long nb = (long long)rows * (K / SF_BLOCK);
-        launch_pdl(ep_permute_kernel, (unsigned)((nb + 255) / 256), 256u, 0, st, ep, K, cap, ws);
+        TableArgs a;
+        memset(&a, 0, sizeof(a));
+        a.ids = ep.flat_ids; a.w = ep.flat_w; a.expert_map = nullptr;
+        a.M = 0; a.T = 1; a.E = lt.num_experts; a.has_shared = 0; a.words = 0;
+        a.num_global = lt.num_experts; a.tiles_d = 0; a.tc_cap = cap; a.gemv_units = 0;
+        a.ws = ws;
+        const unsigned nthr = TC_TILE_ROWS * 8;
+        const size_t fixed = ((size_t)a.E + 3 * nthr) * sizeof(int32_t);
+        const size_t smem = 200 * 1024;
+        launch_pdl(ep_gather_tables_kernel, 1u, nthr, smem, st, ep, a, (int)((smem - fixed) / 4));
     }
+    // 4 permute
+    launch_pdl(ep_permute_kernel, (unsigned)(2 * 148), 256u, 0, st, ep, K, cap, ws);
+    // 5 experts
     const WeightSet r{routed->w13, routed->w13_sf, routed->w13_gs, routed->w2, routed->w2_sf, routed->w2_gs};
     const WeightSet sh = shape->has_shared ? WeightSet{shared->w13, shared->w13_sf, shared->w13_gs, shared->w2, shared->w2_sf, shared->w2_gs}
                                            : r;
@@ -426,10 +571,21 @@ int vmoe_ep_forward(const vmoe_ep_ctx* ctx, const vmoe_shape* shape, const vmoe_
                      shape->has_shared ? shared->w13_sf_atoms : routed->w13_sf_atoms,
                      shape->has_shared ? shared->w2_sf_atoms : routed->w2_sf_atoms};
     ws.row_dst = ep.row_dst;
-    if ((rc = launch_tc_gate_up(lk, r, sh, prep, Mr, ws, st, cap, Mr))) return rc;
-    if ((rc = launch_tc_down(lk, r, sh, prep, Mr, ws, st, cap, Mr))) return rc;
-    launch_pdl(ep_signal_kernel, 1u, 32u, 0, st, ep);
-    launch_pdl(ep_combine_kernel, 296u, 256u, 0, st, ep, M, K, T, has_shared, static_cast<__nv_bfloat16*>(out_bf16), status);
+    const int Mr = (int)rows;
+    if (cap == TC_UNIT_TOK_SMALL) {
+        TcEpSignal sig;
+        memset(&sig, 0, sizeof(sig));
+        for (int i = 0; i < ctx->world; ++i)
+            sig.flag[i] = &reinterpret_cast<EpFlags*>(ep.slab[i] + ep.L.flags)->combine_flag[ctx->rank];
+        sig.world = ctx->world; sig.epoch = &ep.state->epoch; sig.ticket = &ep.state->ticket_experts;
+        if ((rc = launch_tc(lk, r, sh, prep, Mr, ws, st, TC_PHASE_GATE_UP | TC_PHASE_DOWN, nullptr, nullptr, nullptr, cap, Mr, &sig))) return rc;
+    } else {
+        if ((rc = launch_tc(lk, r, sh, prep, Mr, ws, st, TC_PHASE_GATE_UP | TC_PHASE_DOWN, nullptr, nullptr, nullptr, cap, Mr, nullptr))) return rc;
+        launch_pdl(ep_signal_kernel, 1u, 32u, 0, st, ep, static_cast<const int32_t*>(status));
+    }
+    // 6 combine
+    launch_pdl(ep_combine_kernel, 148u, 256u, 0, st, ep, M, K, T, has_shared, static_cast<const __nv_bfloat16*>(residual_bf16),
+               static_cast<__nv_bfloat16*>(out_bf16), status);
     return cuda_status(cudaGetLastError());
 }
 
@@ -438,7 +594,14 @@ int vmoe_ep_read_status(const vmoe_ep_ctx* ctx, const vmoe_shape* shape, void* w
     if (rc) return rc;
     if (!shape || !workspace) return VMOE_ERR_NULL;
     const vmoe_shape lt = ep_local_shape(ctx, shape, true);
-    return vmoe_read_status(workspace, &lt, stream);
+    Workspace ws;
+    if ((rc = resolve_workspace(&lt, workspace, &ws, ep_tc_units(ctx)))) return rc;
+    int32_t v = 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (cudaMemcpyAsync(&v, ws.counters + CNT_STATUS, 4, cudaMemcpyDeviceToHost, st) != cudaSuccess) return VMOE_ERR_CUDA;
+    if (cudaStreamSynchronize(st) != cudaSuccess) return VMOE_ERR_CUDA;
+    if (v != 0) cudaMemsetAsync(ws.counters + CNT_STATUS, 0, 4, st);
+    return v;
 }
 
 }  // extern "C"

@@ -11,6 +11,9 @@ namespace vmoe {
 
 // One warp routes one token: p = the warp's E floats of shared memory, l = the token's logits.
 // fp32 softmax, T rounds of arg-max under (probability desc, expert id asc), renormalise.
+// A row with a NaN or +inf logit has only NaN probabilities (the reference then leaves its ids at -1,
+// fused-moe/csrc/megakernel_v1.cu:516-528); here a NaN probability counts as 0 in the selection, so the ids
+// are always distinct and inside [0, E) and the row's weights come out NaN (0 / 0).
 __device__ __forceinline__ void route_token(const float* l, float* p, int E, int T, int lane,
                                             int32_t* ids_out, float* w_out) {
     float mx = -INFINITY;
@@ -22,27 +25,34 @@ __device__ __forceinline__ void route_token(const float* l, float* p, int E, int
 #pragma unroll
     for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
     const float inv = 1.0f / sum;
-    for (int e = lane; e < E; e += 32) p[e] *= inv;
+    for (int e = lane; e < E; e += 32) { const float v = p[e] * inv; p[e] = (v == v) ? v : 0.0f; }
     __syncwarp();
 
+    // Every lane keeps the best of its own (strided) entries; a round is two warp reductions -- the largest value
+    // (probabilities are >= 0, so their bit patterns order like unsigned integers), then the lowest expert id
+    // among the lanes that hold it -- and only the winning lane rescans its entries.
+    auto local_best = [&](float& bv, int& bi) {
+        bv = -1.0f; bi = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) { const float v = p[e]; if (v > bv) { bv = v; bi = e; } }
+    };
+    float bv; int bi;
+    local_best(bv, bi);
     float sel_w = 0.f; int sel_id = 0; float wsum = 0.f;   // lane j keeps the j-th selection
     for (int j = 0; j < T; ++j) {
-        float bv = -1.0f; int bi = 0x7fffffff;
-        for (int e = lane; e < E; e += 32) { float v = p[e]; if (v > bv) { bv = v; bi = e; } }
-#pragma unroll
-        for (int o = 16; o; o >>= 1) {
-            float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            int   oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        const unsigned key = bv >= 0.0f ? __float_as_uint(bv) + 1u : 0u;
+        const unsigned top = __reduce_max_sync(0xffffffffu, key);
+        const unsigned win = __reduce_min_sync(0xffffffffu, key == top ? (unsigned)bi : 0x7fffffffu);
+        const float wv = top ? __uint_as_float(top - 1u) : 0.0f;
+        if (lane == j) { sel_w = wv; sel_id = (int)win; }
+        wsum += wv;                              // same value in every lane, rank order
+        if (win < (unsigned)E && (int)(win & 31u) == lane) {       // taken (T <= E: an untaken entry >= 0 always exists)
+            p[win] = -2.0f;
+            local_best(bv, bi);
         }
-        if (lane == j) { sel_w = bv; sel_id = bi; }
-        if (lane == 0) p[bi] = -2.0f;            // taken
-        wsum += bv;                              // same value in every lane, rank order
-        __syncwarp();
     }
     const float winv = 1.0f / wsum;
     if (lane < T) {
-        ids_out[lane] = sel_id;
+        ids_out[lane] = min(max(sel_id, 0), E - 1);
         w_out[lane] = sel_w * winv;
     }
 }
@@ -53,13 +63,22 @@ __device__ __forceinline__ void route_token(const float* l, float* p, int E, int
 struct TableArgs {
     const int32_t* ids; const float* w; const int32_t* expert_map;
     int M, T, E, has_shared, words;   // words = ceil(M / 32)
+    int num_global;                   // range of the ids (length of expert_map when there is one)
+    int tiles_d;                      // column tiles of the down projection (hidden / 128); 0 = no dependency counters
     int tc_cap;                       // tokens per tensor-core unit
     int gemv_units;                   // also emit the 4-token work units of the CUDA-core path
     Workspace ws;
 };
 
+// Local expert of pair p, -1 when the pair is dropped: its expert lives on another GPU, or its id is outside
+// [0, num_global) -- caller-supplied ids are never used as an index unchecked; an id past the range also
+// sets VMOE_ERR_LIMIT in the status word (negative ids are the framework's "no expert" marker and drop silently).
 __device__ __forceinline__ int local_expert(const TableArgs& a, int p) {
     int e = a.ids[p];
+    if ((unsigned)e >= (unsigned)a.num_global) {
+        if (e >= 0 && a.ws.counters) atomicExch(&a.ws.counters[CNT_STATUS], VMOE_ERR_LIMIT);
+        return -1;
+    }
     if (a.expert_map) e = a.expert_map[e];
     return (e >= 0 && e < a.E) ? e : -1;
 }
@@ -68,6 +87,13 @@ __device__ inline void phase_clear(const TableArgs& a, int tid, int nthr) {
     const int n = a.E * a.words;
     for (int i = tid; i < n; i += nthr) a.ws.bitmap[i] = 0u;
     if (tid < CNT_N && tid != CNT_STATUS) a.ws.counters[tid] = 0;
+    // dependency counters of the fused weights-as-rows kernel
+    if (a.ws.unit_done)
+        for (int i = tid; i < a.ws.tc_unit_capacity; i += nthr) a.ws.unit_done[i] = 0;
+    if (a.ws.token_done && a.tiles_d > 0 && a.M <= a.ws.small_tokens) {
+        for (int i = tid; i < a.M * a.tiles_d; i += nthr) a.ws.token_done[i] = 0;
+        for (int i = tid; i < a.M; i += nthr) a.ws.token_expect[i] = 0;
+    }
 }
 __device__ inline void phase_mark(const TableArgs& a, int tid, int nthr) {
     const int P = a.M * a.T;
@@ -162,7 +188,9 @@ __device__ inline void phase_scan(const TableArgs& a, int tid, int nthr, const i
                 a.ws.tc_unit_base[e] = t;
                 for (int s = 0; s < cnt; s += a.tc_cap) {
                     const int nt = min(a.tc_cap, cnt - s);
-                    a.ws.tc_units[t++] = make_int4(e, c + s, nt, tc_box(nt));
+                    if (t < a.ws.tc_unit_capacity) a.ws.tc_units[t] = make_int4(e, c + s, nt, tc_box(nt));
+                    else a.ws.counters[CNT_STATUS] = VMOE_ERR_LIMIT;     // more units than the workspace was sized for
+                    ++t;
                 }
             }
             c += cnt;
@@ -171,6 +199,7 @@ __device__ inline void phase_scan(const TableArgs& a, int tid, int nthr, const i
 }
 __device__ inline void phase_place(const TableArgs& a, int tid, int nthr) {
     const int P = a.M * a.T;
+    const bool count_rows = a.ws.token_done && a.tiles_d > 0 && a.M <= a.ws.small_tokens;
     for (int p = tid; p < P; p += nthr) {
         const int e = local_expert(a, p);
         int slot = -1;
@@ -181,6 +210,7 @@ __device__ inline void phase_place(const TableArgs& a, int tid, int nthr) {
             a.ws.sorted_pair[slot] = p;
             a.ws.gather_idx[slot] = m;
             a.ws.scatter_weights[slot] = a.w[p];
+            if (count_rows) atomicAdd(&a.ws.token_expect[m], 1);      // rows the token's combine waits for
         }
         a.ws.pair_slot[p] = slot;
     }
@@ -190,6 +220,7 @@ __device__ inline void phase_place(const TableArgs& a, int tid, int nthr) {
             a.ws.sorted_pair[base + m] = P + m;
             a.ws.gather_idx[base + m] = m;
             a.ws.scatter_weights[base + m] = 1.0f;
+            if (count_rows) atomicAdd(&a.ws.token_expect[m], 1);
         }
     }
 }

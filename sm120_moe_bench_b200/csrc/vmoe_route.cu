@@ -7,6 +7,8 @@
 #include "vmoe_common.cuh"
 #include "vmoe_phases.cuh"
 
+#include <stdlib.h>
+
 namespace vmoe {
 
 // ---------------------------------------------------------------------------------
@@ -50,23 +52,6 @@ int launch_route(const float* logits, int M, int E, int T, int32_t* ids, float* 
 // ---------------------------------------------------------------------------------
 constexpr int TABLE_THREADS = 1024;
 
-// small problems: everything in one CTA
-__global__ void __launch_bounds__(TABLE_THREADS) tables_fused_kernel(TableArgs a, int tables_in_smem) {
-    extern __shared__ int32_t s_mem[];          // [E] counts + [3 * nthr] scan (+ bitmap and running popcounts)
-    int32_t* s_count = s_mem; int32_t* s_scan = s_mem + a.E;
-    const int tid = threadIdx.x, nthr = blockDim.x;
-    pdl_begin();
-    if (tables_in_smem) {
-        // the bitmap and its popcounts are touched by every phase: keep them on chip when they fit
-        a.ws.bitmap = reinterpret_cast<uint32_t*>(s_scan + 3 * nthr);
-        a.ws.word_prefix = reinterpret_cast<int32_t*>(a.ws.bitmap + (size_t)a.E * a.words);
-    }
-    phase_clear(a, tid, nthr);       __syncthreads();
-    phase_mark(a, tid, nthr);        __syncthreads();
-    phase_count(a, tid >> 5, nthr >> 5, tid & 31, s_count); __syncthreads();
-    phase_scan(a, tid, nthr, s_count, s_scan); __syncthreads();
-    phase_place(a, tid, nthr);
-}
 // large problems: grid-wide phases as separate launches
 __global__ void tables_clear_kernel(TableArgs a) { pdl_begin(); phase_clear(a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x); }
 __global__ void tables_mark_kernel(TableArgs a)  { pdl_begin(); phase_mark(a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x); }
@@ -82,34 +67,141 @@ __global__ void __launch_bounds__(TABLE_THREADS) tables_scan_kernel(TableArgs a)
 }
 __global__ void tables_place_kernel(TableArgs a) { pdl_begin(); phase_place(a, blockIdx.x * blockDim.x + threadIdx.x, gridDim.x * blockDim.x); }
 
+// ---------------------------------------------------------------------------------
+// Up to 4096 pairs: the front of the layer in ONE CTA.  Optionally the router (one warp per token), then the
+// permutation phases, optionally -- for the very smallest batches, one or two 16-element blocks per thread --
+// the permuting activation quantiser.  Everything a later phase of this CTA reads back (ids, weights, expert
+// offsets, first unit per expert, slot of each pair; bitmap and running popcounts when they fit) lives in
+// shared memory and is copied to the workspace at the end, so no phase waits for a round trip through L2.
+// ---------------------------------------------------------------------------------
+template <bool WITH_PQ>
+__global__ void __launch_bounds__(WITH_PQ ? TABLE_THREADS / 2 : TABLE_THREADS)
+front_kernel(const float* __restrict__ logits, int num_global, TableArgs a, int tables_in_smem,
+             const __nv_bfloat16* __restrict__ x, int K) {
+    extern __shared__ int32_t s_mem[];
+    const int tid = threadIdx.x, nthr = blockDim.x, warp = tid >> 5, lane = tid & 31, nwarps = nthr >> 5;
+    const int P = a.M * a.T;
+    int32_t* s_count = s_mem;                      // [E]
+    int32_t* s_scan = s_count + a.E;               // [3 * nthr]
+    int32_t* s_off = s_scan + 3 * nthr;            // [E + 2] expert offsets
+    int32_t* s_ub = s_off + a.E + 2;               // [E + 2] first tensor-core unit per expert
+    int32_t* s_slot = s_ub + a.E + 2;              // [P] slot of each pair
+    int32_t* s_ids = s_slot + P;                   // [P]
+    float* s_w = reinterpret_cast<float*>(s_ids + P);      // [P]
+    int32_t* s_next = s_ids + 2 * P;
+    pdl_begin();
+    if (tables_in_smem) {
+        a.ws.bitmap = reinterpret_cast<uint32_t*>(s_next);
+        a.ws.word_prefix = s_next + (size_t)a.E * a.words;
+        s_next += 2 * (size_t)a.E * a.words;
+    }
+    if (logits) {
+        float* s_prob = reinterpret_cast<float*>(s_next) + (size_t)warp * num_global;
+        for (int m = warp; m < a.M; m += nwarps) {
+            route_token(logits + (size_t)m * num_global, s_prob, num_global, a.T, lane, s_ids + m * a.T, s_w + m * a.T);
+            __syncwarp();
+            if (lane < a.T) {        // the workspace copy (read by later kernels and by the caller)
+                a.ws.topk_ids[(size_t)m * a.T + lane] = s_ids[m * a.T + lane];
+                a.ws.topk_weights[(size_t)m * a.T + lane] = s_w[m * a.T + lane];
+            }
+        }
+    } else {
+        for (int p = tid; p < P; p += nthr) { s_ids[p] = a.ids[p]; s_w[p] = a.w[p]; }
+    }
+    for (int i = tid; i < a.E + 2; i += nthr) s_ub[i] = 0;
+    int32_t* g_off = a.ws.expert_offsets; int32_t* g_ub = a.ws.tc_unit_base; int32_t* g_slot = a.ws.pair_slot;
+    a.ids = s_ids; a.w = s_w;
+    a.ws.expert_offsets = s_off; a.ws.tc_unit_base = s_ub; a.ws.pair_slot = s_slot;
+    __syncthreads();
+    phase_clear(a, tid, nthr);       __syncthreads();
+    phase_mark(a, tid, nthr);        __syncthreads();
+    phase_count(a, warp, nwarps, lane, s_count); __syncthreads();
+    phase_scan(a, tid, nthr, s_count, s_scan); __syncthreads();
+    phase_place(a, tid, nthr);
+    __syncthreads();
+    if (WITH_PQ) {
+        const int nb = a.M * (K / SF_BLOCK);
+        for (int b = tid; b < nb; b += nthr)
+            permute_quantize_block<true>(b, x, a.M, K, a.T, a.E, a.has_shared, a.tc_cap, s_ids, a.expert_map, a.ws);
+    }
+    for (int i = tid; i < a.E + 2; i += nthr) g_off[i] = s_off[i];
+    if (g_ub) for (int i = tid; i < a.E + 1; i += nthr) g_ub[i] = s_ub[i];
+    for (int p = tid; p < P; p += nthr) g_slot[p] = s_slot[p];
+}
+
+int tuning(const char* name, int dflt) {
+    const char* v = getenv(name);
+    return v ? atoi(v) : dflt;
+}
+
+// Launches front_kernel when the problem fits one CTA; *done = false (and nothing launched) otherwise.
+static int launch_one_cta(const vmoe_shape& s, const float* logits, const int32_t* ids, const float* w,
+                          const int32_t* expert_map, const __nv_bfloat16* x, bool pq, int M, const Workspace& ws,
+                          cudaStream_t st, int tc_cap, bool gemv_units, bool* done) {
+    *done = false;
+    const long long P = (long long)M * s.topk;
+    if (M <= 0 || P > 4096) return VMOE_OK;
+    const int nthr = pq ? TABLE_THREADS / 2 : TABLE_THREADS;
+    TableArgs a;
+    a.tc_cap = tc_cap; a.gemv_units = gemv_units ? 1 : 0;
+    a.ids = ids; a.w = w; a.expert_map = expert_map;
+    a.M = M; a.T = s.topk; a.E = s.num_experts; a.has_shared = s.has_shared; a.words = (M + 31) / 32;
+    a.num_global = s.num_global_experts;
+    a.tiles_d = s.hidden / TC_TILE_ROWS;
+    a.ws = ws;
+    size_t smem = ((size_t)a.E + 3 * nthr + 2 * ((size_t)a.E + 2) + 3 * (size_t)P) * sizeof(int32_t);
+    const size_t tab = 2 * (size_t)a.E * a.words * sizeof(int32_t);
+    const size_t prob = logits ? (size_t)(nthr / 32) * s.num_global_experts * sizeof(float) : 0;
+    const bool in_smem = smem + tab + prob <= 200 * 1024;
+    if (in_smem) smem += tab;
+    smem += prob;
+    if (smem > 200 * 1024) return VMOE_OK;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaFuncSetAttribute(front_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(front_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        attr_done = true;
+    }
+    if (pq) launch_pdl(front_kernel<true>, 1u, (unsigned)nthr, smem, st, logits, s.num_global_experts, a, in_smem ? 1 : 0, x, s.hidden);
+    else    launch_pdl(front_kernel<false>, 1u, (unsigned)nthr, smem, st, logits, s.num_global_experts, a, in_smem ? 1 : 0, x, s.hidden);
+    *done = true;
+    return cuda_status(cudaGetLastError());
+}
+
 int launch_tables(const vmoe_shape& s, const int32_t* ids, const float* w, const int32_t* expert_map,
                   int M, const Workspace& ws, cudaStream_t st, int tc_cap, bool gemv_units) {
+    bool done = false;
+    int rc = launch_one_cta(s, nullptr, ids, w, expert_map, nullptr, false, M, ws, st, tc_cap, gemv_units, &done);
+    if (rc || done) return rc;
+    // large problems: grid-wide phases as separate launches
     TableArgs a;
     a.tc_cap = tc_cap;
     a.gemv_units = gemv_units ? 1 : 0;
     a.ids = ids; a.w = w; a.expert_map = expert_map;
     a.M = M; a.T = s.topk; a.E = s.num_experts; a.has_shared = s.has_shared; a.words = (M + 31) / 32;
+    a.num_global = s.num_global_experts;
+    a.tiles_d = s.hidden / TC_TILE_ROWS;
     a.ws = ws;
-    const size_t smem = ((size_t)a.E + 3 * TABLE_THREADS) * sizeof(int32_t);
-    if (smem > 200 * 1024) return VMOE_ERR_SHAPE;
-    const size_t smem_tab = smem + 2 * (size_t)a.E * a.words * sizeof(int32_t);
-    const bool in_smem = smem_tab <= 200 * 1024;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaFuncSetAttribute(tables_fused_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        attr_done = true;
-    }
-    if ((long long)M * s.topk <= 4096) {      // one CTA up to ~4 k pairs, grid-wide phases above
-        launch_pdl(tables_fused_kernel, 1u, (unsigned)TABLE_THREADS, in_smem ? smem_tab : smem, st, a, in_smem ? 1 : 0);
-    } else {
-        const int blocks = 296;
-        launch_pdl(tables_clear_kernel, (unsigned)blocks, 256u, 0, st, a);
-        launch_pdl(tables_mark_kernel, (unsigned)blocks, 256u, 0, st, a);
-        launch_pdl(tables_count_kernel, (unsigned)((a.E + 7) / 8), 256u, 0, st, a);
-        launch_pdl(tables_scan_kernel, 1u, (unsigned)TABLE_THREADS, 0, st, a);
-        launch_pdl(tables_place_kernel, (unsigned)blocks, 256u, 0, st, a);
-    }
+    const int blocks = 296;
+    launch_pdl(tables_clear_kernel, (unsigned)blocks, 256u, 0, st, a);
+    launch_pdl(tables_mark_kernel, (unsigned)blocks, 256u, 0, st, a);
+    launch_pdl(tables_count_kernel, (unsigned)((a.E + 7) / 8), 256u, 0, st, a);
+    launch_pdl(tables_scan_kernel, 1u, (unsigned)TABLE_THREADS, 0, st, a);
+    launch_pdl(tables_place_kernel, (unsigned)blocks, 256u, 0, st, a);
     return cuda_status(cudaGetLastError());
+}
+
+int launch_front(const vmoe_shape& s, const float* logits, const int32_t* ids, const float* w,
+                 const int32_t* expert_map, const __nv_bfloat16* x, int M, const Workspace& ws, cudaStream_t st,
+                 int tc_cap, bool* done, bool* quantized) {
+    const int max_tokens = tuning("VMOE_FRONT_TOKENS", 32);            // router inside the one-CTA front up to this batch
+    const int max_pq_tokens = tuning("VMOE_FRONT_PQ_TOKENS", 2);       // ... and the permuting quantiser up to this one
+    *done = false; *quantized = false;
+    if (M <= 0 || M > max_tokens) return VMOE_OK;
+    const bool pq = x != nullptr && M <= max_pq_tokens && (long long)M * (s.hidden / SF_BLOCK) <= 2 * (TABLE_THREADS / 2);
+    const int rc = launch_one_cta(s, logits, ids, w, expert_map, x, pq, M, ws, st, tc_cap, false, done);
+    *quantized = *done && pq;
+    return rc;
 }
 
 }  // namespace vmoe
@@ -157,7 +249,7 @@ static int noalloc_scratch_address(unsigned char** out) {
     return VMOE_OK;
 }
 
-// Same phases as tables_fused_kernel, over caller outputs + the static scratch.  The first
+// Same phases as the one-CTA front, over caller outputs + the static scratch.  The first
 // phase clears the bitmap and the counters, so nothing of an earlier call survives.
 __global__ void __launch_bounds__(TABLE_THREADS) tables_noalloc_kernel(TableArgs a) {
     extern __shared__ int32_t s_mem[];
@@ -188,7 +280,9 @@ extern "C" int vmoe_permute_noalloc(const int32_t* topk_ids, const float* topk_w
     TableArgs a;
     a.ids = topk_ids; a.w = topk_weights; a.expert_map = expert_map;
     a.M = M; a.T = T; a.E = E; a.has_shared = has_shared ? 1 : 0; a.words = (M + 31) / 32;
-    a.tc_cap = TC_UNIT_TOK;
+    a.num_global = expert_map ? 0x7fffffff : E;      // the length of expert_map is not known here: see vmoe.h
+    a.tiles_d = 0;
+    a.tc_cap = TC_UNIT_TOK_SMALL;
     a.gemv_units = 1;
     a.ws = Workspace{};
     a.ws.expert_offsets = expert_offsets; a.ws.sorted_pair = sorted_pair; a.ws.pair_slot = pair_slot;

@@ -62,12 +62,15 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "r"(taddr) : "memory");
 }
 
-// Cycle counters per role, summed over CTAs (development aid; read and cleared by vmoe_debug_read_profile):
+// Cycle counters per role, summed over CTAs (development builds with -DVMOE_PROFILE only; read and cleared by
+// vmoe_debug_read_profile of csrc/vmoe_debug.h):
 // [0] MMA warp: waiting for a full stage, [1] MMA warp: waiting for the accumulator, [2] MMA warp: issuing,
 // [3] epilogue warp 2: waiting for the accumulator, [4] epilogue warp 2: working, [5] producer: waiting for a slot,
 // [6] items, [7] stages.
+#ifdef VMOE_PROFILE
 static __device__ unsigned long long g_pf_prof[8];
 static __device__ unsigned long long g_pf_prof2[4];   // epilogue warp 2: [0] TMEM loads, [1] arithmetic, [2] stores
+#endif
 
 template <int GU>
 __global__ void __launch_bounds__(PF_THREADS, 1)
@@ -399,6 +402,7 @@ int launch_pf_down(const vmoe_shape& s, const WeightSet& routed, const WeightSet
     return launch_pf<0>(s, routed, shared, prep, M, ws, st, b_rows);
 }
 
+#ifdef VMOE_PROFILE
 int debug_read_pf_profile(unsigned long long* out8) {
     if (cudaMemcpyFromSymbol(out8, g_pf_prof, sizeof(g_pf_prof)) != cudaSuccess) return VMOE_ERR_CUDA;
     unsigned long long zero[8] = {0};
@@ -409,15 +413,17 @@ int debug_read_pf_profile2(unsigned long long* out4) {
     unsigned long long zero[4] = {0};
     return cuda_status(cudaMemcpyToSymbol(g_pf_prof2, zero, sizeof(zero)));
 }
+#endif
 
 }  // namespace vmoe
 
-// Development aid: role cycle counters of the tensor-core kernels (see g_pf_prof / g_tc_prof), summed over
-// CTAs since the last call.  Synchronises the device.  Not part of the operator surface.
-namespace vmoe { int debug_read_tc_profile(unsigned long long* out8); }
-extern "C" int vmoe_debug_read_profile(unsigned long long* out16) {   // 20 values
-    if (!out16) return VMOE_ERR_NULL;
-    int rc = vmoe::debug_read_pf_profile(out16);                // [0..7]  large-batch kernels
-    if (!rc) rc = vmoe::debug_read_tc_profile(out16 + 8);       // [8..15] decode kernels
-    return rc ? rc : vmoe::debug_read_pf_profile2(out16 + 16);  // [16..19] large-batch epilogue split
+#ifdef VMOE_PROFILE
+#include "vmoe_debug.h"
+// Development builds only (-DVMOE_PROFILE): role cycle counters of the token-major kernels, summed over CTAs
+// since the last call.  Synchronises the device.  Not part of the operator surface.
+extern "C" int vmoe_debug_read_profile(unsigned long long* out12) {
+    if (!out12) return VMOE_ERR_NULL;
+    const int rc = vmoe::debug_read_pf_profile(out12);               // [0..7]  roles
+    return rc ? rc : vmoe::debug_read_pf_profile2(out12 + 8);         // [8..11] epilogue split
 }
+#endif

@@ -52,10 +52,16 @@ class ExpertParallelMoE:
 
     def __init__(self, hidden: int, inter: int, num_global_experts: int, topk: int,
                  routed: ops.MoEWeights, shared: ops.MoEWeights | None, max_local_tokens: int,
-                 group=None, capacity: int | None = None, device=None):
+                 group=None, capacity: int | None = None, device=None, wait_limit_us: int = 0,
+                 fake_world: int | None = None):
+        """``wait_limit_us``: limit of every cross-GPU wait (0 = one second).  ``fake_world`` (tests of the
+        time-out path only): this process plays rank 0 of that many ranks, the other ranks' slabs are local
+        buffers that nobody ever signals."""
         import torch.distributed as dist
         self.group = group
-        if dist.is_available() and dist.is_initialized():
+        if fake_world:
+            self.rank, self.world = 0, int(fake_world)
+        elif dist.is_available() and dist.is_initialized():
             self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         else:
             self.rank, self.world = 0, 1
@@ -72,6 +78,7 @@ class ExpertParallelMoE:
         self.ctx = VmoeEpCtx()
         self.ctx.rank, self.ctx.world = self.rank, self.world
         self.ctx.experts_per_rank, self.ctx.capacity, self.ctx.max_local_tokens = per, self.capacity, max_local_tokens
+        self.ctx.wait_limit_us = wait_limit_us          # 0 = one second
         for i in range(self.world):
             self.ctx.slab[i] = 1          # placeholder so that the size queries validate
         slab_bytes = lib.vmoe_ep_slab_bytes(C.byref(self.ctx), C.byref(self._cshape))
@@ -87,11 +94,19 @@ class ExpertParallelMoE:
             handle = (C.c_ubyte * 64)()
             check(lib.vmoe_ep_ipc_export(self._own, handle), "vmoe_ep_ipc_export")
             handles = [bytes(handle)]
-            if self.world > 1:
+            self._fake = []
+            if fake_world:
+                for i in range(1, self.world):
+                    other = C.c_void_p()
+                    check(lib.vmoe_ep_alloc(slab_bytes, C.byref(other)), "vmoe_ep_alloc")
+                    self._fake.append(other.value)
+                    self.ctx.slab[i] = other.value
+                self.ctx.slab[0] = self._own
+            elif self.world > 1:
                 gathered = [None] * self.world
                 dist.all_gather_object(gathered, bytes(handle), group=group)
                 handles = gathered
-            for i in range(self.world):
+            for i in range(self.world if not fake_world else 0):
                 if i == self.rank:
                     self.ctx.slab[i] = self._own
                 else:
@@ -101,18 +116,21 @@ class ExpertParallelMoE:
                     self._opened.append(mapped.value)
                     self.ctx.slab[i] = mapped.value
             self.ws = torch.zeros(ws_bytes, dtype=torch.uint8, device=self.device)
-        self.epoch = 0
-        if self.world > 1:
+        if self.world > 1 and not fake_world:
             dist.barrier(group=group)     # every slab is mapped everywhere before the first forward
 
-    def forward(self, hidden: torch.Tensor, router_logits: torch.Tensor, out: torch.Tensor | None = None):
+    def forward(self, hidden: torch.Tensor, router_logits: torch.Tensor, out: torch.Tensor | None = None,
+                residual: torch.Tensor | None = None):
+        """One expert-parallel pass over this rank's tokens; every rank must call it the same number of times.
+        The call keeps its sequence number on the device, so it can be captured in a CUDA graph.  With
+        ``residual`` the result is ``residual + layer(hidden)`` (may be the same tensor as ``out``)."""
         M = hidden.shape[0]
         if out is None:
             out = torch.empty_like(hidden)
-        self.epoch += 1
         check(lib.vmoe_ep_forward(C.byref(self.ctx), C.byref(self._cshape), C.byref(self.routed.cstruct()),
                                   C.byref(self.shared.cstruct()) if self.shared is not None else None,
-                                  hidden.data_ptr(), router_logits.data_ptr(), out.data_ptr(), M, self.epoch,
+                                  hidden.data_ptr(), router_logits.data_ptr(),
+                                  residual.data_ptr() if residual is not None else None, out.data_ptr(), M,
                                   self.ws.data_ptr(), self.ws_bytes, torch.cuda.current_stream().cuda_stream),
               "vmoe_ep_forward")
         return out
@@ -126,6 +144,9 @@ class ExpertParallelMoE:
         for p in self._opened:
             lib.vmoe_ep_ipc_close(p)
         self._opened = []
+        for p in self._fake:
+            lib.vmoe_ep_free(p)
+        self._fake = []
         if self._own:
             lib.vmoe_ep_free(self._own)
             self._own = None

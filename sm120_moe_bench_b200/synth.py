@@ -87,16 +87,38 @@ def make_layer(cfg: LayerConfig, seed: int = 0, device="cpu"):
     return dict(routed=routed, shared=shared)
 
 
-def make_inputs(cfg: LayerConfig, tokens: int, seed: int = 0, device="cpu", zipf_s: float | None = None):
+def make_inputs(cfg: LayerConfig, tokens: int, seed: int = 0, device="cpu", zipf_s: float | None = None,
+                mtp_group: int | None = None, mtp_corr: float = 0.0):
     """bf16 activations N(0,1) ``[M, K]`` and fp32 router logits N(0,1) ``[M, E]``; with
-    ``zipf_s`` the bias ``log(rank ** -s)`` over a seeded permutation of expert ids is added."""
+    ``zipf_s`` the bias ``log(rank ** -s)`` over a seeded permutation of expert ids is added.
+
+    ``mtp_group`` / ``mtp_corr``: consecutive groups of ``mtp_group`` tokens stand for the positions of one
+    sequence under multi-token prediction (1 verified + 5 speculative draft positions at 6).  Their logits share a
+    seeded component, ``l_i = c * base + sqrt(1 - c^2) * own_i`` (still N(0,1) each), so adjacent positions reuse
+    part of their experts, as the reference observed on real traffic (71 % adjacent-token expert reuse,
+    RELEASE_MANIFEST.md:108-110); ``c = 0.98`` gives about that figure for 512 experts, top-10."""
     gen = torch.Generator(device=device)
     gen.manual_seed(seed + 1000003)
     hidden = torch.randn(tokens, cfg.hidden, generator=gen, device=device).to(torch.bfloat16)
     logits = torch.randn(tokens, cfg.num_experts, generator=gen, device=device)
+    if mtp_group and mtp_corr > 0.0:
+        if tokens % mtp_group:
+            raise ValueError("tokens must be a multiple of mtp_group")
+        base = torch.randn(tokens // mtp_group, 1, cfg.num_experts, generator=gen, device=device)
+        own = logits.view(tokens // mtp_group, mtp_group, cfg.num_experts)
+        logits = (mtp_corr * base + (1.0 - mtp_corr * mtp_corr) ** 0.5 * own).reshape(tokens, cfg.num_experts)
     if zipf_s is not None:
         perm = torch.randperm(cfg.num_experts, generator=gen, device=device)
         rank = torch.empty(cfg.num_experts, device=device)
         rank[perm] = torch.arange(1, cfg.num_experts + 1, device=device, dtype=torch.float32)
         logits = logits + (-zipf_s) * torch.log(rank)
     return hidden, logits.float().contiguous()
+
+
+def adjacent_reuse(topk_ids: torch.Tensor, group: int) -> float:
+    """Fraction of a position's experts that the next position of the same sequence also selected."""
+    M, T = topk_ids.shape
+    sel = torch.zeros(M, int(topk_ids.max()) + 1, dtype=torch.bool, device=topk_ids.device)
+    sel.scatter_(1, topk_ids.long(), True)
+    sel = sel.view(M // group, group, -1)
+    return float((sel[:, 1:] & sel[:, :-1]).sum(-1).float().mean() / T)

@@ -41,6 +41,29 @@ def main():
         if st != 0 or not same:
             ok = False
             print(f"rank {rank} iter {it} M {M}: status {st} equal {same}", flush=True)
+    # one captured call, replayed: equal to the eager result, with the residual fused into the combine
+    M = 24
+    hidden, logits = synth.make_inputs(cfg, M, seed=900 + rank)
+    hidden, logits = hidden.cuda(), logits.cuda()
+    eager = moe.forward(hidden, logits, residual=hidden).clone()
+    ref = hidden + vm.fused_moe(hidden, full, ws, router_logits=logits, shared=shared)
+    out = torch.empty_like(hidden)
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        moe.forward(hidden, logits, out=out, residual=hidden)
+        side.synchronize()
+        dist.barrier()
+        with torch.cuda.graph(graph, stream=side):
+            moe.forward(hidden, logits, out=out, residual=hidden)
+    torch.cuda.synchronize()
+    dist.barrier()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    if moe.status() != 0 or not torch.equal(out, eager) or not torch.equal(eager, ref):
+        ok = False
+        print(f"rank {rank}: graph replay differs from eager / single GPU", flush=True)
     dist.barrier()
     moe.close()
     dist.destroy_process_group()

@@ -24,7 +24,7 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, n), n
     from sm120_moe_bench_b200 import _lib
     assert sorted(_lib.SIGNATURES) == names
-    assert _lib.lib.vmoe_abi_version() == 3
+    assert _lib.lib.vmoe_abi_version() == 4
     assert _lib.lib.vmoe_status_string(6) == b"a bounded device-side wait ran out"
 
 

@@ -214,6 +214,175 @@ def test_config_large_prefill_properties(vm, large_layer):
             util.assert_output_close(out1[m].float().cpu().numpy(), o[0].float().cpu().numpy())
 
 
+def _oracle_rows(cfg, layer, hidden, ids_dev, w_dev, rows):
+    """The oracle on a few token rows of a large batch.  A token's output only depends on its own top-k experts
+    (and the shared one), so only those are copied back and dequantised: the cost of a batch-1 oracle run per row."""
+    ids = ids_dev[rows].cpu().numpy()
+    w = w_dev[rows].cpu().numpy()
+    ow = util.to_oracle_weights(layer["routed"], np.unique(ids))
+    osh = util.to_oracle_weights(layer["shared"]) if cfg.shared else None
+    return omoe.moe_layer(hidden[rows].float().cpu().numpy(), ids, w, ow, osh)
+
+
+@pytest.mark.parametrize("path", PATHS)
+@pytest.mark.parametrize("M", [16, 64])
+def test_config_large_decode_oracle_rows(vm, large_layer, M, path):
+    """BASELINE config 2 at batch 16 and 64: three token rows of the batch against the oracle (router ids bit for
+    bit for the whole batch, output within the layer tolerance)."""
+    from sm120_moe_bench_b200 import synth
+    cfg = synth.CONFIG_LARGE
+    routed, shared = _device_layer(vm, large_layer)
+    hidden, logits = synth.make_inputs(cfg, M, seed=M)
+    hid_d, log_d = hidden.cuda(), logits.cuda()
+    ws = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, M, has_shared=True, path=path))
+    out = vm.fused_moe(hid_d, routed, ws, router_logits=log_d, shared=shared)
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    ids_dev = ws.view("topk_ids", torch.int32, M * cfg.topk).view(M, cfg.topk).clone()
+    w_dev = ws.view("topk_weights", torch.float32, M * cfg.topk).view(M, cfg.topk).clone()
+    ids_ref, _ = omoe.route(logits.numpy(), cfg.topk)
+    assert np.array_equal(ids_dev.cpu().numpy(), ids_ref)
+    rows = [0, M // 2 + 1, M - 1]
+    ref = _oracle_rows(cfg, large_layer, hid_d, ids_dev, w_dev, rows)
+    util.assert_output_close(out[rows].float().cpu().numpy(), ref)
+
+
+@pytest.mark.parametrize("zipf", [None, 1.2])
+def test_config_large_prefill_oracle_rows(vm, large_layer, zipf):
+    """BASELINE config 3 (8192 tokens, token-major tcgen05 kernels), uniform and Zipf(1.2) routing: three token
+    rows against the oracle, router ids of 256 sampled rows bit for bit."""
+    from sm120_moe_bench_b200 import synth
+    cfg = synth.CONFIG_LARGE
+    routed, shared = _device_layer(vm, large_layer)
+    M = 8192
+    ws = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, M, has_shared=True, path=TC))
+    hidden, logits = synth.make_inputs(cfg, M, seed=3, device="cuda", zipf_s=zipf)
+    out = vm.fused_moe(hidden, routed, ws, router_logits=logits, shared=shared)
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    ids_dev = ws.view("topk_ids", torch.int32, M * cfg.topk).view(M, cfg.topk).clone()
+    w_dev = ws.view("topk_weights", torch.float32, M * cfg.topk).view(M, cfg.topk).clone()
+    sample = torch.arange(0, M, 32)
+    lg = logits[sample.cuda()].cpu().numpy()
+    ids_ref, _ = omoe.route(lg, cfg.topk)
+    ok = np.array([omoe.route_ids_are_unambiguous(lg[i:i + 1], cfg.topk) for i in range(len(lg))])
+    assert ok.mean() > 0.99
+    assert np.array_equal(ids_dev[sample.cuda()].cpu().numpy()[ok], ids_ref[ok])
+    rows = [0, 4097, 8191]
+    ref = _oracle_rows(cfg, large_layer, hidden, ids_dev, w_dev, rows)
+    util.assert_output_close(out[rows].float().cpu().numpy(), ref)
+
+
+def test_wide_shape_on_the_tensor_core_path(vm):
+    """Hidden 7168, intermediate 2048 (beyond what the streaming GEMV kernels take): the tensor-core path has no
+    such cap.  Four experts, top-2 + shared; decode (weights-as-rows kernel) and a 160-token batch (token-major)."""
+    from sm120_moe_bench_b200 import synth
+    cfg = synth.LayerConfig("wide", 7168, 2048, 4, 2, True)
+    layer = synth.make_layer(cfg, seed=21, device="cuda")
+    routed, shared = _device_layer(vm, layer)
+    for M in (5, 160):
+        hidden, logits = synth.make_inputs(cfg, M, seed=M, device="cuda")
+        ws = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, M, has_shared=True, path=TC))
+        out = vm.fused_moe(hidden, routed, ws, router_logits=logits, shared=shared)
+        torch.cuda.synchronize()
+        assert ws.status() == 0
+        ids_dev = ws.view("topk_ids", torch.int32, M * cfg.topk).view(M, cfg.topk).clone()
+        w_dev = ws.view("topk_weights", torch.float32, M * cfg.topk).view(M, cfg.topk).clone()
+        rows = [0, M // 2, M - 1]
+        ref = _oracle_rows(cfg, layer, hidden, ids_dev, w_dev, rows)
+        util.assert_output_close(out[rows].float().cpu().numpy(), ref)
+    # the streaming GEMV path refuses the shape instead of running past its limits
+    import sm120_moe_bench_b200._lib as L
+    with pytest.raises(L.VmoeError):
+        vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, 4, has_shared=True, path=GEMV))
+
+
+@pytest.mark.parametrize("path", PATHS)
+def test_non_finite_router_logits_are_safe(vm, path):
+    """Rows with a NaN, +inf or all -inf logit: the reference's router leaves their ids at -1
+    (fused-moe/csrc/megakernel_v1.cu:516-528); here they get valid, distinct ids (what oracle.moe.route pins), so
+    nothing indexes out of range, their output rows are NaN, and every other row is untouched by them."""
+    from sm120_moe_bench_b200 import ops, synth
+    cfg = synth.LayerConfig("mid", 512, 256, 12, 3, True)
+    layer = synth.make_layer(cfg, seed=3)
+    routed, shared = _device_layer(vm, layer)
+    M = 9
+    hidden, logits = synth.make_inputs(cfg, M, seed=77)
+    clean = logits.clone()
+    logits[1, 4] = float("nan")
+    logits[4, 0] = float("inf")
+    logits[6, :] = float("-inf")
+    ids_ref, w_ref = omoe.route(logits.numpy(), cfg.topk)
+    ids, w = ops.route(logits.cuda(), cfg.topk)
+    assert np.array_equal(ids.cpu().numpy(), ids_ref)
+    assert np.array_equal(np.isnan(w.cpu().numpy()), np.isnan(w_ref))
+    for m in (1, 4, 6):
+        assert ids_ref[m].tolist() == [0, 1, 2] and np.isnan(w_ref[m]).all()
+    ws = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, M, has_shared=True, path=path))
+    out = vm.fused_moe(hidden.cuda(), routed, ws, router_logits=logits.cuda(), shared=shared).clone()
+    ref = vm.fused_moe(hidden.cuda(), routed, ws, router_logits=clean.cuda(), shared=shared)
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    good = [0, 2, 3, 5, 7, 8]
+    assert torch.equal(out[good], ref[good])
+    assert torch.isnan(out[[1, 4, 6]].float()).all()
+
+
+@pytest.mark.parametrize("path", PATHS)
+def test_out_of_range_expert_ids_are_dropped_and_reported(vm, path):
+    """Pre-routed ids outside [0, E) never index anything: the pair is dropped; an id past the range also sets
+    VMOE_ERR_LIMIT in the status word.  Negative ids (a framework's "no expert" marker) drop silently."""
+    from sm120_moe_bench_b200 import synth
+    cfg = synth.LayerConfig("mid", 512, 256, 12, 3, False)
+    layer = synth.make_layer(cfg, seed=3)
+    routed, _ = _device_layer(vm, layer)
+    M = 6
+    hidden, logits = synth.make_inputs(cfg, M, seed=5)
+    ids, w = omoe.route(logits.numpy(), cfg.topk)
+    ws = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, M, path=path))
+    bad = ids.copy()
+    bad[2, 1] = -1
+    keep = np.ones_like(w); keep[2, 1] = 0
+    out = vm.fused_moe(hidden.cuda(), routed, ws, topk_ids=torch.from_numpy(bad).cuda(), topk_weights=torch.from_numpy(w).cuda())
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    ok_ids = ids.copy()
+    ref = omoe.moe_layer(hidden.float().numpy(), ok_ids, (w * keep).astype(np.float32), util.to_oracle_weights(layer["routed"]))
+    util.assert_output_close(out.float().cpu().numpy(), ref)
+    bad[4, 0] = 1 << 20
+    keep[4, 0] = 0
+    out = vm.fused_moe(hidden.cuda(), routed, ws, topk_ids=torch.from_numpy(bad).cuda(), topk_weights=torch.from_numpy(w).cuda())
+    torch.cuda.synchronize()
+    assert ws.status() == 8                  # VMOE_ERR_LIMIT; the read clears the word
+    assert ws.status() == 0
+    ref = omoe.moe_layer(hidden.float().numpy(), ok_ids, (w * keep).astype(np.float32), util.to_oracle_weights(layer["routed"]))
+    util.assert_output_close(out.float().cpu().numpy(), ref)
+
+
+def test_checkpoint_layer_runs_on_the_device(vm, tmp_path):
+    """A layer written in checkpoint naming (per-expert gate_proj / up_proj / down_proj .weight, .weight_scale,
+    .weight_scale_2, as fused-moe/ep_moe_poc.py:26-57 reads them), loaded by checkpoint.load_moe_layer and run
+    through fused_moe on the tensor-core path, against the oracle on the original tensors."""
+    from sm120_moe_bench_b200 import checkpoint, ops, synth
+    cfg = synth.LayerConfig("ckpt", 512, 256, 6, 2, True)
+    layer = synth.make_layer(cfg, seed=13)
+    checkpoint.save_moe_layer(str(tmp_path), 3, layer["routed"], layer["shared"], shards=2)
+    loaded = checkpoint.load_moe_layer(str(tmp_path), 3, cfg.num_experts, shared_prefix=checkpoint.DEFAULT_SHARED_PREFIX)
+    routed = ops.MoEWeights(*[t.cuda() for t in loaded["routed"]]).prepare()
+    shared = ops.MoEWeights(*[t.cuda() for t in loaded["shared"]]).prepare()
+    M = 7
+    hidden, logits = synth.make_inputs(cfg, M, seed=2)
+    ws = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, M, has_shared=True, path=TC))
+    out = vm.fused_moe(hidden.cuda(), routed, ws, router_logits=logits.cuda(), shared=shared)
+    torch.cuda.synchronize()
+    assert ws.status() == 0
+    ids, _ = omoe.route(logits.numpy(), cfg.topk)
+    w_dev = ws.view("topk_weights", torch.float32, M * cfg.topk).cpu().numpy().reshape(M, cfg.topk)
+    ref = omoe.moe_layer(hidden.float().numpy(), ids, w_dev, util.to_oracle_weights(layer["routed"]),
+                         util.to_oracle_weights(layer["shared"]))
+    util.assert_output_close(out.float().cpu().numpy(), ref)
+
+
 def test_expert_parallel_halves_sum_to_whole(vm):
     """a4: two ranks each holding half of the experts (expert_map with -1 for the other half); the
     fp32 sum of their outputs equals the single-GPU output up to one bf16 rounding per rank."""
@@ -238,8 +407,8 @@ def test_expert_parallel_halves_sum_to_whole(vm):
 
 
 def test_back_to_back_calls_of_different_sizes_do_not_interfere(vm):
-    """Calls are queued without synchronisation, alternating batch sizes (and with them the small-unit,
-    64-token-unit and 128-token-unit kernels) over ONE workspace.  The kernels of consecutive calls overlap
+    """Calls are queued without synchronisation, alternating batch sizes (and with them the one-CTA front, the
+    weights-as-rows kernel with its in-kernel combine and the token-major kernels) over ONE workspace.  The kernels of consecutive calls overlap
     their prologues (programmatic dependent launch), so each result is compared with the same call made
     alone: bit-identical."""
     from sm120_moe_bench_b200 import ops, synth

@@ -77,3 +77,72 @@ def test_layer_single_token():
     assert rel < 2e-4, rel
     cos = float(np.dot(got, want) / (np.linalg.norm(got) * np.linalg.norm(want)))
     assert cos > 0.99999
+
+
+# ---------------------------------------------------------------------------------------------
+# Router and permutation against the reference's own functions (compiled by oracle/build_ref.py)
+# ---------------------------------------------------------------------------------------------
+ref_router = ref_host.load_router()
+ref_tables = ref_host.load_tables()
+
+
+def _config_logits():
+    from sm120_moe_bench_b200 import synth
+    out = []
+    for cfg, M, zipf in ((synth.CONFIG_TINY, 4, None), (synth.CONFIG_LARGE, 64, None), (synth.CONFIG_LARGE, 64, 1.2)):
+        _, logits = synth.make_inputs(cfg, M, seed=0, zipf_s=zipf)
+        out.append((cfg, logits.numpy()))
+    return out
+
+
+@pytest.mark.skipif(ref_router is None, reason="oracle/_ref/libref_router.so has not been built")
+def test_route_matches_reference_topk_select():
+    """oracle.moe.route against moe_topk_select (fused-moe/csrc/megakernel_v1.cu:491-537) on the logits of
+    BASELINE configs 1 and 2 (uniform and Zipf): ids and their order bit for bit, weights to the last bits of
+    two different expf implementations; plus exact ties (lowest id first)."""
+    for cfg, logits in _config_logits():
+        ids, w = omoe.route(logits, cfg.topk)
+        rid, rw = ref_router.route(logits, cfg.topk)
+        assert omoe.route_ids_are_unambiguous(logits, cfg.topk)
+        assert np.array_equal(ids, rid)
+        assert np.allclose(w, rw, rtol=2e-6, atol=0)
+    tie = np.zeros((2, 16), np.float32)
+    tie[1, [3, 9, 12]] = 1.0
+    ids, w = omoe.route(tie, 4)
+    rid, rw = ref_router.route(tie, 4)
+    assert np.array_equal(ids, rid) and ids[0].tolist() == [0, 1, 2, 3] and ids[1].tolist() == [3, 9, 12, 0]
+    assert np.allclose(w, rw, rtol=2e-6, atol=0)
+
+
+@pytest.mark.skipif(ref_router is None, reason="oracle/_ref/libref_router.so has not been built")
+def test_route_non_finite_rows_are_pinned_differently_from_the_reference():
+    """The reference leaves ids at -1 for a row whose softmax is NaN; the oracle (and the device) pin valid
+    ids and NaN weights instead.  This test records both behaviours."""
+    lg = np.random.default_rng(0).standard_normal((3, 32)).astype(np.float32)
+    lg[0, 5] = np.nan
+    lg[1, 7] = np.inf
+    rid, _ = ref_router.route(lg, 4)
+    assert (rid[0] == -1).all() and (rid[1] == -1).all()
+    ids, w = omoe.route(lg, 4)
+    assert ids[0].tolist() == [0, 1, 2, 3] and ids[1].tolist() == [0, 1, 2, 3]
+    assert np.isnan(w[0]).all() and np.isnan(w[1]).all()
+    assert np.array_equal(ids[2], rid[2]) and np.isfinite(w[2]).all()
+
+
+@pytest.mark.skipif(ref_tables is None, reason="oracle/_ref/libref_tables.so has not been built")
+def test_group_tables_match_reference_build_group_tables():
+    """oracle.moe.build_group_tables against build_group_tables (fused-moe/csrc/verdict_fused_grouped.cu:655-691)
+    on the routing of BASELINE configs 1 and 2 and on a ragged random case: every table bit for bit."""
+    cases = [(omoe.route(lg, cfg.topk)[0], cfg.num_experts) for cfg, lg in _config_logits()]
+    rng = np.random.default_rng(3)
+    cases.append((np.stack([rng.permutation(40)[:7] for _ in range(37)]).astype(np.int32), 40))
+    cases.append((np.zeros((1, 1), np.int32), 4))
+    for ids, E in cases:
+        w = np.full(ids.shape, 0.25, np.float32)
+        t = omoe.build_group_tables(ids, w, E)
+        r = ref_tables.build_group_tables(ids, 0.25)
+        assert np.array_equal(t.expert_list, r["expert_list"])
+        assert np.array_equal(t.expert_token_count, r["expert_token_count"])
+        assert np.array_equal(t.expert_token_offset, r["expert_token_offset"])
+        assert np.array_equal(t.gather_idx, r["gather_idx"])
+        assert np.array_equal(t.scatter_weights, r["scatter_weights"])

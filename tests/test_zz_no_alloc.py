@@ -72,4 +72,4 @@ def test_no_alloc_rejects_sizes_beyond_the_fixed_maximum():
                          d.data_ptr(), f.data_ptr(), None)
     assert lib.vmoe_permute_noalloc(*args(1025, 8)) == 8      # VMOE_ERR_LIMIT
     assert lib.vmoe_permute_noalloc(*args(4, 1025)) == 8
-    assert lib.vmoe_status_string(8) == b"size beyond a fixed maximum"
+    assert lib.vmoe_status_string(8).startswith(b"size beyond a fixed maximum")
