@@ -182,6 +182,20 @@ typedef struct vmoe_extras {
     const void* residual_bf16;   /* [M, hidden]: out = bf16(residual + bf16(layer output)), the residual add the
                                     reference's whole-model kernel performs after the MoE block
                                     (fused-moe/csrc/megakernel_v1.cu:1431-1505); may alias out_bf16 */
+    /* RMSNorm + NVFP4 activation quantisation of the NEXT layer's input, fused behind the combine (+ residual):
+     * y = bf16(out * rsqrt(mean(out^2) + eps) * gamma), then y quantised per 16 elements exactly as vmoe_quantize
+     * does.  Replaces rmsnorm_parallel + rmsnorm_apply_and_quantize (fused-moe/csrc/megakernel_v1.cu:257-352).
+     * next_norm_weight == NULL: not used. */
+    const float* next_norm_weight;  /* [hidden] f32 gamma */
+    float        next_norm_eps;
+    void*        next_normed_bf16;  /* out [M, hidden] bf16 normalised rows (the next router's input); may be NULL */
+    uint8_t*     next_act_q;        /* out [M, hidden/2] E2M1 codes */
+    uint8_t*     next_act_sf;       /* out [M, hidden/16] E4M3 block scales */
+    /* This layer's input already quantised (the next_act_q / next_act_sf a previous layer wrote): the activation
+     * quantiser is skipped and these codes are used as they are.  hidden_bf16 is then only read by the router
+     * projection (gate_weight) and may be NULL without one. */
+    const uint8_t* hidden_q;
+    const uint8_t* hidden_sf;
 } vmoe_extras;
 
 /* vmoe_forward with the optional neighbours above.  extras == NULL behaves exactly like vmoe_forward. */
@@ -191,6 +205,12 @@ int vmoe_forward_ex(const vmoe_shape* shape, const vmoe_weights* routed,
                     const float* topk_weights, const int32_t* expert_map,
                     void* out_bf16, int32_t M, void* workspace, size_t workspace_bytes,
                     const vmoe_extras* extras, void* stream);
+
+/* RMSNorm + activation quantisation alone, over rows x [rows, K] bf16 (the arithmetic of vmoe_extras.next_norm_*;
+ * the first layer of a stack needs it once).  y_bf16 may be NULL.  K a multiple of 16.  Replaces
+ * rmsnorm_parallel + rmsnorm_apply_and_quantize (fused-moe/csrc/megakernel_v1.cu:257-352). */
+int vmoe_rmsnorm_quantize(const void* x_bf16, const float* gamma, float eps, int32_t rows, int32_t K,
+                          void* y_bf16, uint8_t* packed, uint8_t* sf, void* stream);
 
 /* Router projection alone: logits[M, E] (f32) = hidden[M, K] (bf16) @ gate_weight[E, K]^T, f32 accumulation in a
  * fixed order (deterministic).  K a multiple of 256.  Replaces moe_gate_distributed

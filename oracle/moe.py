@@ -271,3 +271,44 @@ def moe_layer_from_logits(hidden_bf16, logits, topk, ew, shared=None, expert_map
                           accum="f64"):
     ids, w = route(logits, topk)
     return moe_layer(hidden_bf16, ids, w, ew, shared, expert_map, accum)
+
+
+# --------------------------------------------------------------------------
+# behind the layer: RMSNorm + activation quantisation of the next layer's input
+# --------------------------------------------------------------------------
+def rmsnorm_quantize(x_bf16: np.ndarray, gamma: np.ndarray, eps: float = 1e-6, threads: int = 256):
+    """RMSNorm of bf16 rows and NVFP4 quantisation of the result, as the next layer's GEMM wants it.
+
+    fused-moe/csrc/megakernel_v1.cu:257-352 (``rmsnorm_parallel`` + ``rmsnorm_apply_and_quantize``): sum of
+    squares over the row, ``rms = 1 / sqrt(sum / K + eps)``, ``norm = x * rms * weight``, then the per-16 block
+    quantiser.  The reference holds the row in float32 and sums with atomics (order undefined); pinned here: the
+    row is bf16, the sum of squares runs in the device's fixed order -- ``threads`` partial sums, thread ``t`` over
+    the 16-element blocks ``t, t + threads, ...`` in element order; a 32-wide xor tree (16, 8, 4, 2, 1) inside
+    each warp; then the warp sums in warp order -- the reciprocal square root is exact IEEE arithmetic, and the
+    normalised row is rounded to bf16 before it is quantised.
+
+    Returns ``(y float32 holding bf16 values [M, K], packed u8 [M, K/2], sf u8 [M, K/16])``.
+    """
+    x = np.asarray(x_bf16, dtype=np.float32)
+    g = np.asarray(gamma, dtype=np.float32)
+    M, K = x.shape
+    nblk = K // 16
+    sq = (x * x).astype(np.float32)                       # exact: bf16 x bf16 fits float32
+    part = np.zeros((M, threads), np.float32)
+    blocks = sq.reshape(M, nblk, 16)
+    for b0 in range(0, nblk, threads):                    # every thread walks its blocks in order
+        chunk = blocks[:, b0:b0 + threads]                # [M, <=threads, 16]
+        for i in range(16):
+            part[:, :chunk.shape[1]] = (part[:, :chunk.shape[1]] + chunk[:, :, i]).astype(np.float32)
+    lanes = np.arange(32)
+    w = part.reshape(M, threads // 32, 32)
+    for o in (16, 8, 4, 2, 1):
+        w = (w + w[:, :, lanes ^ o]).astype(np.float32)
+    total = np.zeros(M, np.float32)
+    for k in range(threads // 32):
+        total = (total + w[:, k, 0]).astype(np.float32)
+    mean = (total / np.float32(K)).astype(np.float32)
+    rms = (np.float32(1.0) / np.sqrt((mean + np.float32(eps)).astype(np.float32)).astype(np.float32)).astype(np.float32)
+    y = nvfp4.bf16_round(((x * rms[:, None]).astype(np.float32) * g[None, :]).astype(np.float32))
+    packed, sf = nvfp4.quantize_act(y)
+    return y, packed, sf

@@ -43,7 +43,9 @@ class VmoeWsLayout(C.Structure):
 
 
 class VmoeExtras(C.Structure):
-    _fields_ = [("gate_weight", C.c_void_p), ("gate_dtype", C.c_int32), ("residual_bf16", C.c_void_p)]
+    _fields_ = [("gate_weight", C.c_void_p), ("gate_dtype", C.c_int32), ("residual_bf16", C.c_void_p),
+                ("next_norm_weight", C.c_void_p), ("next_norm_eps", C.c_float), ("next_normed_bf16", C.c_void_p),
+                ("next_act_q", C.c_void_p), ("next_act_sf", C.c_void_p), ("hidden_q", C.c_void_p), ("hidden_sf", C.c_void_p)]
 
 
 # name -> (restype, argtypes); exactly the entry points of include/vmoe.h
@@ -62,6 +64,7 @@ SIGNATURES = {
                                _P, _P, _P, _P, _P, _P, C.c_int32, _P, C.c_size_t, _P]),
     "vmoe_forward_ex": (C.c_int, [C.POINTER(VmoeShape), C.POINTER(VmoeWeights), C.POINTER(VmoeWeights),
                                   _P, _P, _P, _P, _P, _P, C.c_int32, _P, C.c_size_t, C.POINTER(VmoeExtras), _P]),
+    "vmoe_rmsnorm_quantize": (C.c_int, [_P, _P, C.c_float, C.c_int32, C.c_int32, _P, _P, _P, _P]),
     "vmoe_router_gemv": (C.c_int, [_P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P]),
     "vmoe_stage_gate_up": (C.c_int, [C.POINTER(VmoeShape), C.POINTER(VmoeWeights), C.POINTER(VmoeWeights),
                                      C.c_int32, _P, _P]),

@@ -13,21 +13,23 @@ int max_units(const vmoe_shape* s) {
     return (int)(s->num_experts + 1 + (P + TOK_PER_UNIT - 1) / TOK_PER_UNIT);
 }
 
-// Units carry at most 16 tokens while the batch averages <= 7 tokens per expert (weights-as-rows kernel: a
-// small token tile leaves shared memory for a deeper weight ring; the few experts above 16 tokens are split
-// and re-read through L2) and 128 tokens above (token-major kernel).  The crossover was measured: the
-// token-major kernel is ahead from about 350 tokens of the 512-expert top-10 layer on, and far ahead of
-// 64-token units of the weights-as-rows kernel everywhere in between (0.79 against 0.58 of the HBM roofline
-// at 1536 tokens).
-constexpr long long TC_SMALL_PER_EXPERT = 7;
+// Units carry at most 16 tokens while the batch averages <= 10 pairs per expert (weights-as-rows kernel: gate_up
+// and down in one launch, a small token tile leaves shared memory for a deep weight ring; experts above 16 tokens
+// are split and re-read through L2) and 128 tokens above (token-major kernels).  The crossover was measured on the
+// 512-expert top-10 layer: 384 tokens (7.5 pairs per expert) 625 against 658 us, 512 tokens equal, 640 tokens
+// (12.5 per expert) 700 against 667 us.  VMOE_SMALL_PER_EXPERT overrides it (up to the 16 the workspace is sized for).
+constexpr long long TC_SMALL_PER_EXPERT = 10;         // default crossover (pairs per expert), measured
+constexpr long long TC_SMALL_PER_EXPERT_MAX = 16;     // what the workspace is sized for
 int tc_unit_cap(const vmoe_shape& s, int M) {
     const long long pairs = (long long)M * s.topk;
-    return pairs <= TC_SMALL_PER_EXPERT * s.num_experts ? TC_UNIT_TOK_SMALL : TC_UNIT_TOK_PREFILL;
+    long long per = tuning("VMOE_SMALL_PER_EXPERT", (int)TC_SMALL_PER_EXPERT);
+    if (per > TC_SMALL_PER_EXPERT_MAX) per = TC_SMALL_PER_EXPERT_MAX;
+    return pairs <= per * s.num_experts ? TC_UNIT_TOK_SMALL : TC_UNIT_TOK_PREFILL;
 }
 
 // Largest batch that can take the weights-as-rows kernel (and with it the in-kernel combine).
 int small_batch_tokens(const vmoe_shape* s) {
-    const long long m = TC_SMALL_PER_EXPERT * s->num_experts / s->topk;
+    const long long m = TC_SMALL_PER_EXPERT_MAX * s->num_experts / s->topk;
     return (int)(m < s->max_tokens ? m : s->max_tokens);
 }
 
@@ -325,12 +327,20 @@ int vmoe_forward_ex(const vmoe_shape* shape, const vmoe_weights* routed, const v
     int rc = check_call(shape, routed, shared, M, workspace);
     if (rc) return rc;
     if (M == 0) return VMOE_OK;                          // an empty batch may come with NULL data pointers
-    if (!hidden_bf16 || !out_bf16) return VMOE_ERR_NULL;
     const void* gate_weight = extras ? extras->gate_weight : nullptr;
     const __nv_bfloat16* residual = extras ? static_cast<const __nv_bfloat16*>(extras->residual_bf16) : nullptr;
+    const uint8_t* pre_q = extras ? extras->hidden_q : nullptr;
+    const uint8_t* pre_sf = extras ? extras->hidden_sf : nullptr;
+    const float* norm_w = extras ? extras->next_norm_weight : nullptr;
+    if ((pre_q == nullptr) != (pre_sf == nullptr)) return VMOE_ERR_NULL;
+    if (norm_w && (!extras->next_act_q || !extras->next_act_sf)) return VMOE_ERR_NULL;
     const bool own_logits = !router_logits && !(topk_ids && topk_weights) && gate_weight;
+    if (!out_bf16 || (!hidden_bf16 && (!pre_q || own_logits))) return VMOE_ERR_NULL;
     if (!router_logits && !(topk_ids && topk_weights) && !gate_weight) return VMOE_ERR_NULL;
-    if (!aligned16(hidden_bf16) || !aligned16(out_bf16) || (residual && !aligned16(residual))) return VMOE_ERR_ALIGN;
+    if ((hidden_bf16 && !aligned16(hidden_bf16)) || !aligned16(out_bf16) || (residual && !aligned16(residual))) return VMOE_ERR_ALIGN;
+    if (pre_q && ((reinterpret_cast<uintptr_t>(pre_q) & 7) != 0)) return VMOE_ERR_ALIGN;
+    if (norm_w && ((reinterpret_cast<uintptr_t>(extras->next_act_q) & 7) != 0 ||
+                   (extras->next_normed_bf16 && !aligned16(extras->next_normed_bf16)))) return VMOE_ERR_ALIGN;
     if (own_logits && !aligned16(gate_weight)) return VMOE_ERR_ALIGN;
     if (own_logits && shape->num_global_experts > (shape->topk + 1) * shape->hidden) return VMOE_ERR_SHAPE;   // logits scratch
     if (workspace_bytes < vmoe_workspace_bytes(shape)) return VMOE_ERR_WORKSPACE;
@@ -353,7 +363,7 @@ int vmoe_forward_ex(const vmoe_shape* shape, const vmoe_weights* routed, const v
     // small batches: router + tables (+ quantiser) in one CTA
     bool front = false, quantized = false;
     if (path == VMOE_PATH_TC && cap == TC_UNIT_TOK_SMALL) {
-        if ((rc = launch_front(*shape, router_logits, topk_ids, topk_weights, expert_map, x, M, ws, st, cap, &front, &quantized)))
+        if ((rc = launch_front(*shape, router_logits, topk_ids, topk_weights, expert_map, pre_q ? nullptr : x, M, ws, st, cap, &front, &quantized)))
             return rc;
         if (front && router_logits) { topk_ids = ws.topk_ids; topk_weights = ws.topk_weights; }
     }
@@ -367,16 +377,33 @@ int vmoe_forward_ex(const vmoe_shape* shape, const vmoe_weights* routed, const v
     }
     if (path == VMOE_PATH_TC) {
         const PreparedSet prep = to_prep(routed, shape->has_shared ? shared : nullptr);
-        if (!quantized && (rc = launch_permute_quantize(*shape, x, topk_ids, expert_map, M, ws, st))) return rc;
+        if (!quantized && (rc = launch_permute_quantize(*shape, x, topk_ids, expert_map, M, ws, st, pre_q, pre_sf))) return rc;
         bool combined = false;
-        if ((rc = launch_tc(*shape, r, sh, prep, M, ws, st, TC_PHASE_GATE_UP | TC_PHASE_DOWN, out, residual, &combined))) return rc;
+        // with the next layer's RMSNorm behind it the combine runs as its own row-wide kernel
+        if ((rc = launch_tc(*shape, r, sh, prep, M, ws, st, TC_PHASE_GATE_UP | TC_PHASE_DOWN, norm_w ? nullptr : out, residual, &combined))) return rc;
         if (combined) return VMOE_OK;
     } else {
-        if ((rc = launch_quantize(x, M, shape->hidden, ws.act_q, ws.act_sf, st))) return rc;
+        if (pre_q) {
+            if (cudaMemcpyAsync(ws.act_q, pre_q, (size_t)M * shape->hidden / 2, cudaMemcpyDeviceToDevice, st) != cudaSuccess ||
+                cudaMemcpyAsync(ws.act_sf, pre_sf, (size_t)M * shape->hidden / 16, cudaMemcpyDeviceToDevice, st) != cudaSuccess) return VMOE_ERR_CUDA;
+        } else if ((rc = launch_quantize(x, M, shape->hidden, ws.act_q, ws.act_sf, st))) return rc;
         if ((rc = launch_gate_up(*shape, r, sh, M, ws, st))) return rc;
         if ((rc = launch_down(*shape, r, sh, M, ws, st))) return rc;
     }
+    if (norm_w)
+        return launch_combine_norm(*shape, M, ws, out, st, residual, norm_w, extras->next_norm_eps,
+                                   static_cast<__nv_bfloat16*>(extras->next_normed_bf16), extras->next_act_q, extras->next_act_sf);
     return launch_combine(*shape, M, ws, out, st, residual);
+}
+
+int vmoe_rmsnorm_quantize(const void* x_bf16, const float* gamma, float eps, int32_t rows, int32_t K,
+                          void* y_bf16, uint8_t* packed, uint8_t* sf, void* stream) {
+    if (rows == 0) return VMOE_OK;
+    if (!x_bf16 || !gamma || !packed || !sf) return VMOE_ERR_NULL;
+    if (rows < 0 || K <= 0 || K % SF_BLOCK) return VMOE_ERR_SHAPE;
+    if (!aligned16(x_bf16) || (y_bf16 && !aligned16(y_bf16)) || (reinterpret_cast<uintptr_t>(packed) & 7)) return VMOE_ERR_ALIGN;
+    return launch_rmsnorm_quantize(static_cast<const __nv_bfloat16*>(x_bf16), gamma, eps, rows, K,
+                                   static_cast<__nv_bfloat16*>(y_bf16), packed, sf, static_cast<cudaStream_t>(stream));
 }
 
 int vmoe_read_status(void* workspace, const vmoe_shape* shape, void* stream) {

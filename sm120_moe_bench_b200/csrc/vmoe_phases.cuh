@@ -226,13 +226,31 @@ __device__ inline void phase_place(const TableArgs& a, int tid, int nthr) {
 }
 
 
+// The activation quantiser on one block of 16 bf16 values (…tma_ext.cu:249-279: amax / 6 floored at 1e-30 -> E4M3,
+// round to nearest even, saturating -> decoded scale floored at 1e-30 -> e2m1(x / scale), even element in the low nibble).
+__device__ __forceinline__ void quantize_block16(const __nv_bfloat16* h, float (&v)[SF_BLOCK], uint32_t& lo, uint32_t& hi, uint8_t& sb) {
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < SF_BLOCK; ++i) { v[i] = __bfloat162float(h[i]); amax = fmaxf(amax, fabsf(v[i])); }
+    sb = e4m3_encode(fmaxf(amax / 6.0f, 1e-30f));
+    float scale = e4m3_decode(sb);
+    if (scale < 1e-30f) scale = 1e-30f;
+    const ScaleDivider div_scale(scale);
+    lo = 0; hi = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) lo |= e2m1_encode(div_scale(v[i])) << (4 * i);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) hi |= e2m1_encode(div_scale(v[8 + i])) << (4 * i);
+}
+
 // Permuting activation quantiser for one 16-element block b of the token-major activations: quantise
 // (same arithmetic as quantize_kernel) and write the codes to the token-order copy and to every sorted slot
 // of the token, the block scale into the per-unit atom layout of the tensor-core B operand.
 template <bool BATCHED>
 __device__ __forceinline__ void permute_quantize_block(long long b, const __nv_bfloat16* __restrict__ x, int M, int K, int T, int E,
                                                        int has_shared, int tc_cap, const int32_t* topk_ids,
-                                                       const int32_t* expert_map, const Workspace& ws) {
+                                                       const int32_t* expert_map, const Workspace& ws,
+                                                       const uint8_t* pre_q = nullptr, const uint8_t* pre_sf = nullptr) {
     const int bpr = K / SF_BLOCK;
     const int cap_shift = 31 - __clz(tc_cap);
     const int m = (int)(b / bpr), kb = (int)(b % bpr);
@@ -259,22 +277,19 @@ __device__ __forceinline__ void permute_quantize_block(long long b, const __nv_b
             if (slot[j] >= 0) { off[j] = ws.expert_offsets[ex[j]]; ub[j] = ws.tc_unit_base[ex[j]]; }
         }
     }
-    const uint4* src = reinterpret_cast<const uint4*>(x + b * SF_BLOCK);
-    uint4 raw[2] = {src[0], src[1]};
-    const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(raw);
-    float v[SF_BLOCK];
-    float amax = 0.f;
-#pragma unroll
-    for (int i = 0; i < SF_BLOCK; ++i) { v[i] = __bfloat162float(h[i]); amax = fmaxf(amax, fabsf(v[i])); }
-    const uint8_t sb = e4m3_encode(fmaxf(amax / 6.0f, 1e-30f));
-    float scale = e4m3_decode(sb);
-    if (scale < 1e-30f) scale = 1e-30f;
     uint32_t lo = 0, hi = 0;
-    const ScaleDivider div_scale(scale);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) lo |= e2m1_encode(div_scale(v[i])) << (4 * i);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) hi |= e2m1_encode(div_scale(v[8 + i])) << (4 * i);
+    uint8_t sb;
+    if (pre_q) {
+        // the row arrives quantised (a previous layer's fused RMSNorm + quantise epilogue)
+        const uint2 c = reinterpret_cast<const uint2*>(pre_q)[b];
+        lo = c.x; hi = c.y; sb = pre_sf[b];
+    } else {
+        const uint4* src = reinterpret_cast<const uint4*>(x + b * SF_BLOCK);
+        uint4 raw[2] = {src[0], src[1]};
+        const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(raw);
+        float v[SF_BLOCK];
+        quantize_block16(h, v, lo, hi, sb);
+    }
     // token-order copy (stage-wise checks and the GEMV path read it)
     reinterpret_cast<uint2*>(ws.act_q)[b] = make_uint2(lo, hi);
     ws.act_sf[b] = sb;
@@ -310,9 +325,9 @@ __device__ __forceinline__ void permute_quantize_block(long long b, const __nv_b
 // out[m, 4c .. 4c+3] = bf16( sum_j pair_out[slot(m, j), :]  (ascending j, fp32)  + shared row ) [+ residual],
 // element i = m * (K / 4) + c.  BATCHED: slot numbers and then all rows requested at once (small launches).
 template <bool BATCHED>
-__device__ __forceinline__ void combine_element(long long i, const float* pair_out, const int32_t* pair_slot,
-                                                const int32_t* expert_offsets, int M, int K, int T, int E, int has_shared,
-                                                const __nv_bfloat16* residual, __nv_bfloat16* out) {
+__device__ __forceinline__ uint2 combine_value(long long i, const float* pair_out, const int32_t* pair_slot,
+                                               const int32_t* expert_offsets, int K, int T, int E, int has_shared,
+                                               const __nv_bfloat16* residual) {
     const int k4 = K / 4;
     const int m = (int)(i / k4), c = (int)(i % k4);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -351,7 +366,14 @@ __device__ __forceinline__ void combine_element(long long i, const float* pair_o
         hi = __floats2bfloat162_rn(__bfloat162float(r1.x) + __bfloat162float(hi.x), __bfloat162float(r1.y) + __bfloat162float(hi.y));
     }
     uint2 o; o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
-    reinterpret_cast<uint2*>(out + (size_t)m * K)[c] = o;
+    return o;                       // four bf16 values
+}
+template <bool BATCHED>
+__device__ __forceinline__ void combine_element(long long i, const float* pair_out, const int32_t* pair_slot,
+                                                const int32_t* expert_offsets, int M, int K, int T, int E, int has_shared,
+                                                const __nv_bfloat16* residual, __nv_bfloat16* out) {
+    (void)M;
+    reinterpret_cast<uint2*>(out)[i] = combine_value<BATCHED>(i, pair_out, pair_slot, expert_offsets, K, T, E, has_shared, residual);
 }
 
 }  // namespace vmoe

@@ -98,6 +98,108 @@ int launch_combine(const vmoe_shape& s, int M, const Workspace& ws, __nv_bfloat1
 }
 
 // ---------------------------------------------------------------------------------
+// RMSNorm + NVFP4 quantisation of a row, either of a given matrix or of the combine's result (fused behind the
+// combine: the row is summed, the residual added, written, normalised and quantised in one pass over it).
+// Follows rmsnorm_parallel + rmsnorm_apply_and_quantize (fused-moe/csrc/megakernel_v1.cu:257-352): sum of squares
+// over the row, scale by 1 / sqrt(mean + eps) and by gamma, quantise per 16 elements.  The reference keeps the
+// residual stream in f32 and uses rsqrtf; here the stream is bf16 (what the operator's caller holds), the
+// normalised row is rounded to bf16 before it is quantised (the activation quantiser's input type) and the
+// reciprocal square root is IEEE (1 / sqrtf), so the result is reproducible bit for bit.
+// One CTA of 256 threads per row; a thread owns the 16-element blocks b = tid, tid + 256, ...  Order of the sum
+// of squares (part of the definition, restated by the oracle): per thread in element order across its blocks, then
+// the warp's xor tree (16, 8, 4, 2, 1), then the eight warp sums in warp order.
+// ---------------------------------------------------------------------------------
+constexpr int NORM_THREADS = 256;
+
+template <bool FROM_COMBINE>
+__global__ void __launch_bounds__(NORM_THREADS)
+norm_quant_kernel(const __nv_bfloat16* x, const float* __restrict__ pair_out, const int32_t* __restrict__ pair_slot,
+                  const int32_t* __restrict__ expert_offsets, int K, int T, int E, int has_shared,
+                  const __nv_bfloat16* residual, __nv_bfloat16* out,          // FROM_COMBINE: the combined row goes here
+                  const float* __restrict__ gamma, float eps, __nv_bfloat16* normed, uint8_t* packed, uint8_t* sf) {
+    extern __shared__ float s_row[];                 // [K] the row as f32
+    __shared__ float s_warp[NORM_THREADS / 32];
+    pdl_begin();
+    const int m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nblk = K / SF_BLOCK;
+    float ss = 0.f;
+    for (int b = tid; b < nblk; b += NORM_THREADS) {
+        uint2 q[4];
+        if (FROM_COMBINE) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                q[i] = combine_value<false>((long long)m * (K / 4) + b * 4 + i, pair_out, pair_slot, expert_offsets, K, T, E, has_shared, residual);
+                reinterpret_cast<uint2*>(out + (size_t)m * K)[b * 4 + i] = q[i];
+            }
+        } else {
+            const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)m * K + (size_t)b * SF_BLOCK);
+            const uint4 r0 = src[0], r1 = src[1];
+            q[0] = make_uint2(r0.x, r0.y); q[1] = make_uint2(r0.z, r0.w); q[2] = make_uint2(r1.x, r1.y); q[3] = make_uint2(r1.z, r1.w);
+        }
+        const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(q);
+#pragma unroll
+        for (int i = 0; i < SF_BLOCK; ++i) {
+            const float v = __bfloat162float(h[i]);
+            s_row[b * SF_BLOCK + i] = v;
+            ss = fmaf(v, v, ss);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (lane == 0) s_warp[warp] = ss;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < NORM_THREADS / 32; ++w) total += s_warp[w];
+    const float rms = 1.0f / sqrtf(total / (float)K + eps);
+    for (int b = tid; b < nblk; b += NORM_THREADS) {
+        __align__(16) __nv_bfloat16 y[SF_BLOCK];
+#pragma unroll
+        for (int i = 0; i < SF_BLOCK; ++i) y[i] = __float2bfloat16_rn((s_row[b * SF_BLOCK + i] * rms) * gamma[b * SF_BLOCK + i]);
+        if (normed) {
+            uint4* dst = reinterpret_cast<uint4*>(normed + (size_t)m * K + (size_t)b * SF_BLOCK);
+            dst[0] = reinterpret_cast<const uint4*>(y)[0]; dst[1] = reinterpret_cast<const uint4*>(y)[1];
+        }
+        float v[SF_BLOCK]; uint32_t lo, hi; uint8_t sb;
+        quantize_block16(y, v, lo, hi, sb);
+        reinterpret_cast<uint2*>(packed + (size_t)m * (K / 2))[b] = make_uint2(lo, hi);
+        sf[(size_t)m * nblk + b] = sb;
+    }
+}
+
+static int launch_norm(bool from_combine, const __nv_bfloat16* x, const vmoe_shape* s, const Workspace* ws, int rows, int K,
+                       const __nv_bfloat16* residual, __nv_bfloat16* out, const float* gamma, float eps, __nv_bfloat16* normed,
+                       uint8_t* packed, uint8_t* sf, cudaStream_t st) {
+    if (rows == 0) return VMOE_OK;
+    const size_t smem = (size_t)K * sizeof(float);
+    if (smem > 200 * 1024) return VMOE_ERR_SHAPE;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaFuncSetAttribute(norm_quant_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(norm_quant_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        attr_done = true;
+    }
+    if (from_combine)
+        launch_pdl(norm_quant_kernel<true>, (unsigned)rows, (unsigned)NORM_THREADS, smem, st, x, ws->pair_out, ws->pair_slot,
+                   ws->expert_offsets, K, s->topk, s->num_experts, s->has_shared, residual, out, gamma, eps, normed, packed, sf);
+    else
+        launch_pdl(norm_quant_kernel<false>, (unsigned)rows, (unsigned)NORM_THREADS, smem, st, x, (const float*)nullptr,
+                   (const int32_t*)nullptr, (const int32_t*)nullptr, K, 0, 0, 0, (const __nv_bfloat16*)nullptr,
+                   (__nv_bfloat16*)nullptr, gamma, eps, normed, packed, sf);
+    return cuda_status(cudaGetLastError());
+}
+
+int launch_combine_norm(const vmoe_shape& s, int M, const Workspace& ws, __nv_bfloat16* out, cudaStream_t st,
+                        const __nv_bfloat16* residual, const float* gamma, float eps, __nv_bfloat16* normed,
+                        uint8_t* packed, uint8_t* sf) {
+    return launch_norm(true, nullptr, &s, &ws, M, s.hidden, residual, out, gamma, eps, normed, packed, sf, st);
+}
+int launch_rmsnorm_quantize(const __nv_bfloat16* x, const float* gamma, float eps, int rows, int K, __nv_bfloat16* normed,
+                            uint8_t* packed, uint8_t* sf, cudaStream_t st) {
+    return launch_norm(false, x, nullptr, nullptr, rows, K, nullptr, nullptr, gamma, eps, normed, packed, sf, st);
+}
+
+// ---------------------------------------------------------------------------------
 // Router projection: logits[m, e] = sum_k hidden[m, k] * gate_weight[e, k]  (f32 accumulation).
 // Follows moe_gate_distributed (fused-moe/csrc/megakernel_v1.cu:455-489): one dot product per (token,
 // expert).  One warp per expert and chunk of 8 tokens; a lane owns 8 consecutive k out of every 256 and

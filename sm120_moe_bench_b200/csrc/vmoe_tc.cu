@@ -536,11 +536,12 @@ tc_fused_kernel(const __grid_constant__ FuParams p) {
 template <bool BATCHED>
 __global__ void __launch_bounds__(256)
 permute_quantize_kernel(const __nv_bfloat16* __restrict__ x, int M, int K, int T, int E, int has_shared, int tc_cap,
-                        const int32_t* __restrict__ topk_ids, const int32_t* __restrict__ expert_map, Workspace ws) {
+                        const int32_t* __restrict__ topk_ids, const int32_t* __restrict__ expert_map, Workspace ws,
+                        const uint8_t* __restrict__ pre_q, const uint8_t* __restrict__ pre_sf) {
     pdl_begin();
     const long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= (long long)M * (K / SF_BLOCK)) return;
-    permute_quantize_block<BATCHED>(b, x, M, K, T, E, has_shared, tc_cap, topk_ids, expert_map, ws);
+    permute_quantize_block<BATCHED>(b, x, M, K, T, E, has_shared, tc_cap, topk_ids, expert_map, ws, pre_q, pre_sf);
 }
 
 // linear block scales [rows, K/16] -> atoms [rows/128][K/64][32][4][4]; NaN patterns become 0x00
@@ -620,16 +621,16 @@ int tc_sm_count() {
 }
 
 int launch_permute_quantize(const vmoe_shape& s, const __nv_bfloat16* x, const int32_t* ids, const int32_t* expert_map,
-                            int M, const Workspace& ws, cudaStream_t st) {
+                            int M, const Workspace& ws, cudaStream_t st, const uint8_t* pre_q, const uint8_t* pre_sf) {
     const long long nblocks = (long long)M * (s.hidden / SF_BLOCK);
     if (nblocks == 0) return VMOE_OK;
     const unsigned blocks = (unsigned)((nblocks + 255) / 256);
     if (blocks <= 1024)
         launch_pdl(permute_quantize_kernel<true>, blocks, 256u, 0, st, x, M, s.hidden, s.topk, s.num_experts,
-                                                              s.has_shared, tc_unit_cap(s, M), ids, expert_map, ws);
+                                                              s.has_shared, tc_unit_cap(s, M), ids, expert_map, ws, pre_q, pre_sf);
     else
         launch_pdl(permute_quantize_kernel<false>, blocks, 256u, 0, st, x, M, s.hidden, s.topk, s.num_experts,
-                                                               s.has_shared, tc_unit_cap(s, M), ids, expert_map, ws);
+                                                               s.has_shared, tc_unit_cap(s, M), ids, expert_map, ws, pre_q, pre_sf);
     return cuda_status(cudaGetLastError());
 }
 

@@ -192,15 +192,26 @@ def fused_moe(hidden: torch.Tensor, weights: MoEWeights, ws: Workspace, *,
               topk_ids: torch.Tensor | None = None, topk_weights: torch.Tensor | None = None,
               shared: MoEWeights | None = None, expert_map: torch.Tensor | None = None,
               out: torch.Tensor | None = None, gate_weight: torch.Tensor | None = None,
-              residual: torch.Tensor | None = None) -> torch.Tensor:
+              residual: torch.Tensor | None = None, hidden_quantized: "QuantizedRows | None" = None,
+              next_norm: "tuple[torch.Tensor, float] | None" = None,
+              next_rows: "QuantizedRows | None" = None) -> torch.Tensor:
     """The fused NVFP4 MoE expert layer: bf16 hidden states + router logits (or pre-routed
     ids / weights, or the router matrix ``gate_weight [E, K]`` f32 / bf16 for the projection to run
     on the device too) + packed expert weights in, combined bf16 out.  With ``residual`` the result
-    is ``residual + layer(hidden)`` (may be the same tensor as ``out``)."""
-    _need(hidden, torch.bfloat16, "hidden")
-    M, K = hidden.shape
+    is ``residual + layer(hidden)`` (may be the same tensor as ``out``).
+
+    ``next_norm = (gamma f32 [K], eps)`` fuses the next layer's RMSNorm and activation quantisation behind the
+    combine: ``next_rows`` (a ``QuantizedRows``) receives the normalised bf16 rows, their FP4 codes and block
+    scales.  ``hidden_quantized`` feeds such rows to this layer in place of quantising ``hidden`` again."""
+    if hidden is None:
+        if hidden_quantized is None:
+            raise ValueError("hidden or hidden_quantized is required")
+        M, K = hidden_quantized.packed.shape[0], hidden_quantized.packed.shape[1] * 2
+    else:
+        _need(hidden, torch.bfloat16, "hidden")
+        M, K = hidden.shape
     if out is None:
-        out = torch.empty_like(hidden)
+        out = torch.empty(M, K, dtype=torch.bfloat16, device=(hidden if hidden is not None else hidden_quantized.packed).device)
     else:
         _need(out, torch.bfloat16, "out")
     extras = None
@@ -209,25 +220,64 @@ def fused_moe(hidden: torch.Tensor, weights: MoEWeights, ws: Workspace, *,
     elif gate_weight is not None and topk_ids is None:
         if gate_weight.dtype not in (torch.float32, torch.bfloat16) or not gate_weight.is_contiguous():
             raise TypeError("gate_weight must be a contiguous f32 or bf16 tensor [E, K]")
-        extras = VmoeExtras(gate_weight.data_ptr(), 0 if gate_weight.dtype == torch.float32 else 1, None)
+        extras = VmoeExtras()
+        extras.gate_weight = gate_weight.data_ptr()
+        extras.gate_dtype = 0 if gate_weight.dtype == torch.float32 else 1
     else:
         _need(topk_ids, torch.int32, "topk_ids")
         _need(topk_weights, torch.float32, "topk_weights")
     if residual is not None:
         _need(residual, torch.bfloat16, "residual")
         if extras is None:
-            extras = VmoeExtras(None, 0, None)
+            extras = VmoeExtras()
         extras.residual_bf16 = residual.data_ptr()
+    if hidden_quantized is not None:
+        if extras is None:
+            extras = VmoeExtras()
+        extras.hidden_q = _need(hidden_quantized.packed, torch.uint8, "hidden_quantized.packed").data_ptr()
+        extras.hidden_sf = _need(hidden_quantized.sf, torch.uint8, "hidden_quantized.sf").data_ptr()
+    if next_norm is not None:
+        if next_rows is None:
+            raise ValueError("next_norm needs next_rows to write to")
+        gamma, eps = next_norm
+        if extras is None:
+            extras = VmoeExtras()
+        extras.next_norm_weight = _need(gamma, torch.float32, "gamma").data_ptr()
+        extras.next_norm_eps = float(eps)
+        extras.next_normed_bf16 = _ptr(next_rows.normed)
+        extras.next_act_q = next_rows.packed.data_ptr()
+        extras.next_act_sf = next_rows.sf.data_ptr()
     if expert_map is not None:
         _need(expert_map, torch.int32, "expert_map")
     if ws.shape.has_shared and shared is None:
         raise ValueError("shape has a shared expert but no shared weights were given")
     check(lib.vmoe_forward_ex(C.byref(ws._cshape), C.byref(weights.cstruct()),
                               C.byref(shared.cstruct()) if shared is not None else None,
-                              hidden.data_ptr(), _ptr(router_logits), _ptr(topk_ids), _ptr(topk_weights),
+                              _ptr(hidden), _ptr(router_logits), _ptr(topk_ids), _ptr(topk_weights),
                               _ptr(expert_map), out.data_ptr(), M, ws.buf.data_ptr(), ws.nbytes,
                               C.byref(extras) if extras is not None else None, _stream()),
           "vmoe_forward_ex")
+    return out
+
+
+class QuantizedRows:
+    """Normalised activation rows as a layer's fused epilogue (or ``rmsnorm_quantize``) leaves them for the next
+    layer: bf16 rows ``[M, K]`` (optional), E2M1 codes ``[M, K/2]`` and E4M3 block scales ``[M, K/16]``."""
+
+    def __init__(self, rows: int, K: int, device="cuda", keep_bf16: bool = True):
+        self.normed = torch.empty(rows, K, dtype=torch.bfloat16, device=device) if keep_bf16 else None
+        self.packed = torch.empty(rows, K // 2, dtype=torch.uint8, device=device)
+        self.sf = torch.empty(rows, K // 16, dtype=torch.uint8, device=device)
+
+
+def rmsnorm_quantize(x: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6, out: QuantizedRows | None = None) -> QuantizedRows:
+    """``y = bf16(x * rsqrt(mean(x^2) + eps) * gamma)`` per row, then ``y`` quantised to NVFP4 (``vmoe_rmsnorm_quantize``)."""
+    _need(x, torch.bfloat16, "x")
+    _need(gamma, torch.float32, "gamma")
+    rows, K = x.shape
+    out = out or QuantizedRows(rows, K, x.device)
+    check(lib.vmoe_rmsnorm_quantize(x.data_ptr(), gamma.data_ptr(), float(eps), rows, K, _ptr(out.normed),
+                                    out.packed.data_ptr(), out.sf.data_ptr(), _stream()), "vmoe_rmsnorm_quantize")
     return out
 
 

@@ -123,3 +123,21 @@ def test_layer_tiny_self_consistency():
         half = omoe.ExpertWeights(*[t[r * 4:(r + 1) * 4].numpy() for t in layer["routed"]])
         parts.append(omoe.moe_layer(x, ids, w, half, expert_map=emap))
     assert np.abs(parts[0] + parts[1] - out64).max() <= 2 ** -7 * np.abs(out64).max()
+
+
+def test_rmsnorm_quantize_oracle_against_float64():
+    """oracle.moe.rmsnorm_quantize (fused-moe/csrc/megakernel_v1.cu:257-352 with a pinned summation order): the
+    normalised rows agree with a float64 evaluation to bf16 rounding, and the codes are the activation quantiser's."""
+    g = np.random.default_rng(5)
+    for K in (512, 4096, 7168):
+        x = nvfp4.bf16_round(g.standard_normal((4, K)).astype(np.float32) * 2.0)
+        gamma = (1.0 + 0.1 * g.standard_normal(K)).astype(np.float32)
+        y, packed, sf = omoe.rmsnorm_quantize(x, gamma, 1e-6)
+        ref = x.astype(np.float64) / np.sqrt((x.astype(np.float64) ** 2).mean(1, keepdims=True) + 1e-6) * gamma
+        assert np.all(np.abs(y - ref) <= np.abs(ref) * 2.0 ** -8 + 1e-6)
+        assert np.array_equal(y, nvfp4.bf16_round(y))
+        p2, s2 = nvfp4.quantize_act(y)
+        assert np.array_equal(packed, p2) and np.array_equal(sf, s2)
+    # an all-zero row stays zero and finite (eps keeps the reciprocal square root finite)
+    y, packed, sf = omoe.rmsnorm_quantize(np.zeros((1, 512), np.float32), np.ones(512, np.float32), 1e-6)
+    assert np.all(y == 0) and np.all(packed == 0)
