@@ -66,6 +66,10 @@ def parse():
                     help="expert parallel: groups of 6 tokens are the positions of one sequence and share this "
                          "fraction of their logits (0.98 gives the reference's ~71 %% adjacent-token expert reuse)")
     ap.add_argument("--layers", type=int, default=15)
+    ap.add_argument("--experts", type=int, default=None,
+                    help="prefill: number of routed experts (default 512).  8 experts, top-2 makes the grouped GEMM "
+                         "compute-bound: the case that shows the tensor pipe at work")
+    ap.add_argument("--topk", type=int, default=None, help="prefill: experts per token (default 10)")
     ap.add_argument("--path", default="tc", choices=["tc", "gemv"],
                     help="tc: tcgen05 block-scaled path (default); gemv: CUDA-core streaming GEMV path")
     return ap.parse_args()
@@ -263,11 +267,13 @@ def workload_config(tokens, gpus):
 class DecodeBench:
     """The config-2 layer on one GPU: weights once, one workspace and a few rotating input sets per batch size."""
 
-    def __init__(self, dev, path: str):
+    def __init__(self, dev, path: str, experts: int | None = None, topk: int | None = None):
         import sm120_moe_bench_b200 as vm
         from sm120_moe_bench_b200 import ops, synth
         self.vm, self.ops, self.synth, self.dev = vm, ops, synth, dev
         self.cfg = synth.CONFIG_LARGE
+        if experts or topk:         # same hidden / intermediate sizes, fewer experts: the compute-bound variant
+            self.cfg = synth.LayerConfig("few-experts", 4096, 1024, experts or 512, topk or 10, True)
         self.layer = synth.make_layer(self.cfg, seed=0, device=dev)
         self.routed = ops.MoEWeights(*self.layer["routed"]).prepare()
         self.shared = ops.MoEWeights(*self.layer["shared"]).prepare()
@@ -288,6 +294,25 @@ class DecodeBench:
             h, l = sets[i % len(sets)]
             vm.fused_moe(h, self.routed, ws, router_logits=l, shared=self.shared, out=out)
 
+        # Each step is replayed from a CUDA graph (one per input set, captured once): at small batches a step is a
+        # few tens of microseconds of device time, less than the host needs to issue its launches one by one.
+        eager_step, graphs = step, []
+        try:
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                for k in range(len(sets)):
+                    eager_step(k)
+                side.synchronize()
+                for k in range(len(sets)):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=side):
+                        eager_step(k)
+                    graphs.append(g)
+            torch.cuda.synchronize()
+            step = lambda i: graphs[i % len(graphs)].replay()
+        except Exception:  # noqa: BLE001
+            graphs = []
+            torch.cuda.synchronize()
         sampler = ClockSampler(self.dev.index or 0).start()
         for i in range(max(warmup, 3)):
             step(i)
@@ -324,6 +349,7 @@ class DecodeBench:
         layer_bytes = U * self.routed.nbytes_per_expert() + M * (K * 2 * 2 + cfg.num_experts * 4)
         gu_s, dn_s = statistics.median(gu) * 1e-3, statistics.median(dn) * 1e-3
         return {"tokens": M, "ms_per_step": ms_step, "tokens_per_s": M / (ms_step * 1e-3), "repeats": len(reps),
+                "launch": "one CUDA graph replay per step" if graphs else "eager launches",
                 "distinct_experts_per_step": U,
                 "layer_frac": layer_bytes / (ms_step * 1e-3) / 1e9 / self.peak, "layer_gbs": layer_bytes / (ms_step * 1e-3) / 1e9,
                 "layer_bytes": layer_bytes,
@@ -509,6 +535,7 @@ def run_ours(args):
         "timed_seconds": main["repeats"] * ms * 1e-3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4(w4a4)->f32",
         "data": "synthetic", "config": dict(workload_config(M, 1), kernel_path=args.path),
+        "launch": main["launch"],
         "roofline": roof, "clocks": main["clocks"],
         "e2e": {"value": M * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
                 "h2d_bytes_per_step": M * (cfg.hidden * 2 + cfg.num_experts * 4),
@@ -545,7 +572,7 @@ def run_ours(args):
 def run_prefill(args, dev):
     """BASELINE config 3: 8192 tokens through the same layer on one GPU; FP4 TFLOP/s of the whole layer
     (2 * M * (T + 1) * 3 * K * N flops) and of the two grouped GEMMs, event-timed."""
-    b = DecodeBench(dev, "tc")
+    b = DecodeBench(dev, "tc", args.experts, args.topk)
     M = args.tokens if args.tokens != 64 else 8192
     c = b.prefill_case(M, args.steps, args.warmup, args.zipf)
     cfg = b.cfg
@@ -553,7 +580,9 @@ def run_prefill(args, dev):
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": c["ms_per_step"], "repeats": c["repeats"],
             "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "nvfp4(w4a4)->f32", "data": "synthetic",
-            "config": {"workload": "single-GPU prefill MoE layer (BASELINE config 3)", "tokens": M, "zipf_s": args.zipf,
+            "config": {"workload": "single-GPU prefill MoE layer (BASELINE config 3)" if not (args.experts or args.topk) else
+                                   "single-GPU prefill MoE layer, config-3 sizes with fewer experts (compute-bound variant)",
+                       "tokens": M, "zipf_s": args.zipf,
                        "hidden": cfg.hidden, "inter": cfg.inter, "experts": cfg.num_experts, "topk": cfg.topk, "shared_experts": 1},
             "tokens_per_s": c["tokens_per_s"],
             "roofline": {"bound": "tensor", "kernel": "pf_kernel<1> (gate_up, tcgen05, 128-token x 256-row items)",

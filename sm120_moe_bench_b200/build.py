@@ -29,6 +29,8 @@ NVCC_FLAGS = [
 ]
 if os.environ.get("VMOE_PROFILE", "0") == "1":     # role cycle counters in the tcgen05 kernels (development aid)
     NVCC_FLAGS.append("-DVMOE_PROFILE")
+if os.environ.get("VMOE_TIMELINE", "0") == "1":    # %globaltimer marks in the small-batch kernels (development aid)
+    NVCC_FLAGS.append("-DVMOE_TIMELINE")
 
 
 def _sources():

@@ -4,6 +4,12 @@
 
 #include <string.h>
 
+#ifdef VMOE_TIMELINE
+namespace vmoe { unsigned long long* g_vmoe_timeline = nullptr; }
+// development builds only: 32 x u64 device buffer that the small-batch kernels write %globaltimer marks into
+extern "C" int vmoe_debug_set_timeline(void* device_buffer) { vmoe::g_vmoe_timeline = static_cast<unsigned long long*>(device_buffer); return 0; }
+#endif
+
 namespace vmoe {
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -131,6 +137,11 @@ int resolve_workspace(const vmoe_shape* s, void* base, Workspace* ws, int tc_uni
     ws->token_expect    = reinterpret_cast<int32_t*>(b + L.token_expect);
     ws->tc_unit_capacity = tc_units_override > 0 ? tc_units_override : max_tc_units(s);
     ws->small_tokens    = small_batch_tokens(s);
+#ifdef VMOE_TIMELINE
+    ws->timeline        = g_vmoe_timeline;
+#else
+    ws->timeline        = nullptr;
+#endif
     return VMOE_OK;
 }
 
@@ -361,9 +372,9 @@ int vmoe_forward_ex(const vmoe_shape* shape, const vmoe_weights* routed, const v
     __nv_bfloat16* out = static_cast<__nv_bfloat16*>(out_bf16);
     const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(hidden_bf16);
     // small batches: router + tables (+ quantiser) in one CTA
-    bool front = false, quantized = false;
+    bool front = false;
     if (path == VMOE_PATH_TC && cap == TC_UNIT_TOK_SMALL) {
-        if ((rc = launch_front(*shape, router_logits, topk_ids, topk_weights, expert_map, pre_q ? nullptr : x, M, ws, st, cap, &front, &quantized)))
+        if ((rc = launch_front(*shape, router_logits, topk_ids, topk_weights, expert_map, M, ws, st, cap, &front)))
             return rc;
         if (front && router_logits) { topk_ids = ws.topk_ids; topk_weights = ws.topk_weights; }
     }
@@ -377,10 +388,14 @@ int vmoe_forward_ex(const vmoe_shape* shape, const vmoe_weights* routed, const v
     }
     if (path == VMOE_PATH_TC) {
         const PreparedSet prep = to_prep(routed, shape->has_shared ? shared : nullptr);
-        if (!quantized && (rc = launch_permute_quantize(*shape, x, topk_ids, expert_map, M, ws, st, pre_q, pre_sf))) return rc;
+        // small batches: the permuting quantiser is the first work of the fused kernel; large ones: its own launch
+        const TcQuant quant{x, pre_q, pre_sf, topk_ids, expert_map};
+        const bool in_kernel = cap == TC_UNIT_TOK_SMALL && tuning("VMOE_FUSE_QUANT", 1) != 0 && tuning("VMOE_FUSE_PHASES", 1) != 0;
+        if (!in_kernel && (rc = launch_permute_quantize(*shape, x, topk_ids, expert_map, M, ws, st, pre_q, pre_sf))) return rc;
         bool combined = false;
         // with the next layer's RMSNorm behind it the combine runs as its own row-wide kernel
-        if ((rc = launch_tc(*shape, r, sh, prep, M, ws, st, TC_PHASE_GATE_UP | TC_PHASE_DOWN, norm_w ? nullptr : out, residual, &combined))) return rc;
+        if ((rc = launch_tc(*shape, r, sh, prep, M, ws, st, TC_PHASE_GATE_UP | TC_PHASE_DOWN, norm_w ? nullptr : out, residual, &combined,
+                            -1, -1, nullptr, in_kernel ? &quant : nullptr))) return rc;
         if (combined) return VMOE_OK;
     } else {
         if (pre_q) {

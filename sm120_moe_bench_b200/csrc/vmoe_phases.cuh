@@ -254,6 +254,11 @@ __device__ __forceinline__ void permute_quantize_block(long long b, const __nv_b
     const int bpr = K / SF_BLOCK;
     const int cap_shift = 31 - __clz(tc_cap);
     const int m = (int)(b / bpr), kb = (int)(b % bpr);
+    // the row's data is requested first: its latency then overlaps the table reads below
+    uint4 raw[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+    uint2 pre_c = make_uint2(0, 0); uint8_t pre_s = 0;
+    if (pre_q) { pre_c = reinterpret_cast<const uint2*>(pre_q)[b]; pre_s = pre_sf[b]; }
+    else { const uint4* src = reinterpret_cast<const uint4*>(x + b * SF_BLOCK); raw[0] = src[0]; raw[1] = src[1]; }
     // Destinations of the row: one per routed pair plus the shared expert.  BATCHED (small launches, bound by
     // load latency): all table reads of one level are issued together, three dependent round trips for the
     // whole row instead of four per pair.  Large launches walk the pairs one by one with fewer registers.
@@ -281,11 +286,8 @@ __device__ __forceinline__ void permute_quantize_block(long long b, const __nv_b
     uint8_t sb;
     if (pre_q) {
         // the row arrives quantised (a previous layer's fused RMSNorm + quantise epilogue)
-        const uint2 c = reinterpret_cast<const uint2*>(pre_q)[b];
-        lo = c.x; hi = c.y; sb = pre_sf[b];
+        lo = pre_c.x; hi = pre_c.y; sb = pre_s;
     } else {
-        const uint4* src = reinterpret_cast<const uint4*>(x + b * SF_BLOCK);
-        uint4 raw[2] = {src[0], src[1]};
         const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(raw);
         float v[SF_BLOCK];
         quantize_block16(h, v, lo, hi, sb);
@@ -324,6 +326,32 @@ __device__ __forceinline__ void permute_quantize_block(long long b, const __nv_b
 
 // out[m, 4c .. 4c+3] = bf16( sum_j pair_out[slot(m, j), :]  (ascending j, fp32)  + shared row ) [+ residual],
 // element i = m * (K / 4) + c.  BATCHED: slot numbers and then all rows requested at once (small launches).
+// The permuting half alone: an already quantised block (codes lo / hi, scale byte sb) of token-major block b goes to
+// every sorted slot of its token.  The tables are read one pair at a time (the one-CTA front keeps them in shared memory).
+__device__ __forceinline__ void permute_store_block(int b, uint32_t lo, uint32_t hi, uint8_t sb, int K, int T, int E, int has_shared,
+                                                    int tc_cap, const int32_t* topk_ids, const int32_t* expert_map, const Workspace& ws) {
+    const int bpr = K / SF_BLOCK;
+    const int cap_shift = 31 - __clz(tc_cap);
+    const int m = b / bpr, kb = b % bpr;
+    for (int j = 0; j <= T; ++j) {
+        int e, sl;
+        if (j < T) {
+            sl = ws.pair_slot[m * T + j];
+            if (sl < 0) continue;
+            e = topk_ids[m * T + j];
+            if (expert_map) e = expert_map[e];
+        } else {
+            if (!has_shared) break;
+            e = E;
+            sl = ws.expert_offsets[E] + m;
+        }
+        const int rank = sl - ws.expert_offsets[e];
+        const int unit = ws.tc_unit_base[e] + (rank >> cap_shift);
+        const int r = rank & (tc_cap - 1);
+        reinterpret_cast<uint2*>(ws.act_q_sorted + (size_t)sl * (K / 2))[kb] = make_uint2(lo, hi);
+        ws.act_sf_atoms[((size_t)unit * (K / 64) + (kb >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = sb;
+    }
+}
 template <bool BATCHED>
 __device__ __forceinline__ uint2 combine_value(long long i, const float* pair_out, const int32_t* pair_slot,
                                                const int32_t* expert_offsets, int K, int T, int E, int has_shared,

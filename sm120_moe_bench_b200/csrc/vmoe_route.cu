@@ -69,15 +69,12 @@ __global__ void tables_place_kernel(TableArgs a) { pdl_begin(); phase_place(a, b
 
 // ---------------------------------------------------------------------------------
 // Up to 4096 pairs: the front of the layer in ONE CTA.  Optionally the router (one warp per token), then the
-// permutation phases, optionally -- for the very smallest batches, one or two 16-element blocks per thread --
-// the permuting activation quantiser.  Everything a later phase of this CTA reads back (ids, weights, expert
+// permutation phases.  Everything a later phase of this CTA reads back (ids, weights, expert
 // offsets, first unit per expert, slot of each pair; bitmap and running popcounts when they fit) lives in
 // shared memory and is copied to the workspace at the end, so no phase waits for a round trip through L2.
 // ---------------------------------------------------------------------------------
-template <bool WITH_PQ>
-__global__ void __launch_bounds__(WITH_PQ ? TABLE_THREADS / 2 : TABLE_THREADS)
-front_kernel(const float* __restrict__ logits, int num_global, TableArgs a, int tables_in_smem,
-             const __nv_bfloat16* __restrict__ x, int K) {
+__global__ void __launch_bounds__(TABLE_THREADS)
+front_kernel(const float* __restrict__ logits, int num_global, TableArgs a, int tables_in_smem) {
     extern __shared__ int32_t s_mem[];
     const int tid = threadIdx.x, nthr = blockDim.x, warp = tid >> 5, lane = tid & 31, nwarps = nthr >> 5;
     const int P = a.M * a.T;
@@ -119,11 +116,6 @@ front_kernel(const float* __restrict__ logits, int num_global, TableArgs a, int 
     phase_scan(a, tid, nthr, s_count, s_scan); __syncthreads();
     phase_place(a, tid, nthr);
     __syncthreads();
-    if (WITH_PQ) {
-        const int nb = a.M * (K / SF_BLOCK);
-        for (int b = tid; b < nb; b += nthr)
-            permute_quantize_block<true>(b, x, a.M, K, a.T, a.E, a.has_shared, a.tc_cap, s_ids, a.expert_map, a.ws);
-    }
     for (int i = tid; i < a.E + 2; i += nthr) g_off[i] = s_off[i];
     if (g_ub) for (int i = tid; i < a.E + 1; i += nthr) g_ub[i] = s_ub[i];
     for (int p = tid; p < P; p += nthr) g_slot[p] = s_slot[p];
@@ -136,12 +128,12 @@ int tuning(const char* name, int dflt) {
 
 // Launches front_kernel when the problem fits one CTA; *done = false (and nothing launched) otherwise.
 static int launch_one_cta(const vmoe_shape& s, const float* logits, const int32_t* ids, const float* w,
-                          const int32_t* expert_map, const __nv_bfloat16* x, bool pq, int M, const Workspace& ws,
+                          const int32_t* expert_map, int M, const Workspace& ws,
                           cudaStream_t st, int tc_cap, bool gemv_units, bool* done) {
     *done = false;
     const long long P = (long long)M * s.topk;
     if (M <= 0 || P > 4096) return VMOE_OK;
-    const int nthr = pq ? TABLE_THREADS / 2 : TABLE_THREADS;
+    const int nthr = TABLE_THREADS;
     TableArgs a;
     a.tc_cap = tc_cap; a.gemv_units = gemv_units ? 1 : 0;
     a.ids = ids; a.w = w; a.expert_map = expert_map;
@@ -158,12 +150,10 @@ static int launch_one_cta(const vmoe_shape& s, const float* logits, const int32_
     if (smem > 200 * 1024) return VMOE_OK;
     static bool attr_done = false;
     if (!attr_done) {
-        cudaFuncSetAttribute(front_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        cudaFuncSetAttribute(front_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(front_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         attr_done = true;
     }
-    if (pq) launch_pdl(front_kernel<true>, 1u, (unsigned)nthr, smem, st, logits, s.num_global_experts, a, in_smem ? 1 : 0, x, s.hidden);
-    else    launch_pdl(front_kernel<false>, 1u, (unsigned)nthr, smem, st, logits, s.num_global_experts, a, in_smem ? 1 : 0, x, s.hidden);
+    launch_pdl(front_kernel, 1u, (unsigned)nthr, smem, st, logits, s.num_global_experts, a, in_smem ? 1 : 0);
     *done = true;
     return cuda_status(cudaGetLastError());
 }
@@ -171,7 +161,7 @@ static int launch_one_cta(const vmoe_shape& s, const float* logits, const int32_
 int launch_tables(const vmoe_shape& s, const int32_t* ids, const float* w, const int32_t* expert_map,
                   int M, const Workspace& ws, cudaStream_t st, int tc_cap, bool gemv_units) {
     bool done = false;
-    int rc = launch_one_cta(s, nullptr, ids, w, expert_map, nullptr, false, M, ws, st, tc_cap, gemv_units, &done);
+    int rc = launch_one_cta(s, nullptr, ids, w, expert_map, M, ws, st, tc_cap, gemv_units, &done);
     if (rc || done) return rc;
     // large problems: grid-wide phases as separate launches
     TableArgs a;
@@ -192,16 +182,11 @@ int launch_tables(const vmoe_shape& s, const int32_t* ids, const float* w, const
 }
 
 int launch_front(const vmoe_shape& s, const float* logits, const int32_t* ids, const float* w,
-                 const int32_t* expert_map, const __nv_bfloat16* x, int M, const Workspace& ws, cudaStream_t st,
-                 int tc_cap, bool* done, bool* quantized) {
+                 const int32_t* expert_map, int M, const Workspace& ws, cudaStream_t st, int tc_cap, bool* done) {
     const int max_tokens = tuning("VMOE_FRONT_TOKENS", 32);            // router inside the one-CTA front up to this batch
-    const int max_pq_tokens = tuning("VMOE_FRONT_PQ_TOKENS", 2);       // ... and the permuting quantiser up to this one
-    *done = false; *quantized = false;
+    *done = false;
     if (M <= 0 || M > max_tokens) return VMOE_OK;
-    const bool pq = x != nullptr && M <= max_pq_tokens && (long long)M * (s.hidden / SF_BLOCK) <= 2 * (TABLE_THREADS / 2);
-    const int rc = launch_one_cta(s, logits, ids, w, expert_map, x, pq, M, ws, st, tc_cap, false, done);
-    *quantized = *done && pq;
-    return rc;
+    return launch_one_cta(s, logits, ids, w, expert_map, M, ws, st, tc_cap, false, done);
 }
 
 }  // namespace vmoe

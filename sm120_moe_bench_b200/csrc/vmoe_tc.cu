@@ -72,6 +72,9 @@ struct FuParams {
     // combine inside the kernel (single-GPU forward); out == NULL: rows only
     __nv_bfloat16* out; const __nv_bfloat16* residual;
     int T, has_shared, M;
+    // permuting activation quantiser as the kernel's first work (pq_blocks = M * K / 16; 0 = done by the caller)
+    int pq_blocks, tc_cap;
+    TcQuant quant;
     int has_signal;
     TcEpSignal signal;
 };
@@ -106,6 +109,7 @@ struct FuShared {
     int abort_flag;
     int last_cta;
 };
+constexpr int FU_PQ_CHUNK = FU_EPI_SETS * 128;          // 16-element blocks per chunk: one per epilogue thread
 
 __device__ __forceinline__ void fu_timeout(const Workspace& ws, FuShared* sh) {
     atomicExch(&ws.counters[CNT_STATUS], VMOE_ERR_TIMEOUT);
@@ -131,7 +135,7 @@ struct FuItem { int kind, unit, tile; };
 // ---------------------------------------------------------------------------------
 template <int NA, int KS>
 __device__ __forceinline__ bool fu_produce_item(const FuParams& p, uint8_t* smem, FuShared* sh, bool leader, uint32_t& g,
-                                                const FuItem& it, const int4& u, float alpha, bool wait_unit) {
+                                                const FuItem& it, const int4& u, float alpha, bool wait_unit, bool& wait_quant) {
     constexpr bool DOWN = NA == 1;
     const bool shd = u.x >= p.E;
     const int e = shd ? 0 : u.x;
@@ -174,6 +178,13 @@ __device__ __forceinline__ bool fu_produce_item(const FuParams& p, uint8_t* smem
             const bool done = wait_counter(&p.ws.unit_done[it.unit], p.tiles_g * 4);
             if (!__all_sync(0xffffffffu, done)) return false;      // the stage never completes: consumers time out and unwind
         }
+        if (!DOWN && wait_quant) {
+            // the slot-ordered activation rows are written by this kernel's epilogue warps (all CTAs' together) while
+            // the first weight tiles above are in flight
+            const bool done = wait_counter(&p.ws.counters[CNT_PQ_DONE], (p.pq_blocks + FU_PQ_CHUNK - 1) / FU_PQ_CHUNK);
+            if (!__all_sync(0xffffffffu, done)) return false;
+            wait_quant = false;
+        }
         // tokens and their scale atoms
 #pragma unroll
         for (int kk = 0; kk < KS; ++kk)
@@ -198,6 +209,7 @@ __device__ __forceinline__ void fu_producer(const FuParams& p, uint8_t* smem, Fu
     const int num_units = min(p.ws.counters[CNT_TC_UNITS], p.ws.tc_unit_capacity);
     const long long total_g = do_g ? (long long)num_units * p.tiles_g : 0;
     const long long total = total_g + (do_d ? (long long)num_units * p.tiles_d : 0);
+    if (leader && num_units >= 0) VMOE_MARK_MIN(p.ws, 11);
     auto decode = [&](long long item) -> FuItem {
         if (item < total_g) return FuItem{ITEM_GATE_UP, (int)(item / p.tiles_g), (int)(item % p.tiles_g)};
         const long long i2 = item - total_g;
@@ -230,6 +242,7 @@ __device__ __forceinline__ void fu_producer(const FuParams& p, uint8_t* smem, Fu
     bool next_ready = (next < total) ? unit_ready(next_it) : true;
     uint32_t g = 0;
     bool ok = true;
+    bool wait_quant = p.pq_blocks > 0;
     while (ok) {
         if (next >= total) break;
         const FuItem it = next_it;
@@ -240,9 +253,9 @@ __device__ __forceinline__ void fu_producer(const FuParams& p, uint8_t* smem, Fu
         next = pop();
         next_it = decode(next < total ? next : 0);
         next_u = (next < total) ? p.ws.tc_units[next_it.unit] : make_int4(0, 0, 0, 8);
-        if (it.kind == ITEM_GATE_UP) ok = fu_produce_item<2, 1>(p, smem, sh, leader, g, it, u, alpha, false);
-        else if (p.ks_d == 2)        ok = fu_produce_item<1, 2>(p, smem, sh, leader, g, it, u, alpha, !ready);
-        else                         ok = fu_produce_item<1, 1>(p, smem, sh, leader, g, it, u, alpha, !ready);
+        if (it.kind == ITEM_GATE_UP) ok = fu_produce_item<2, 1>(p, smem, sh, leader, g, it, u, alpha, false, wait_quant);
+        else if (p.ks_d == 2)        ok = fu_produce_item<1, 2>(p, smem, sh, leader, g, it, u, alpha, !ready, wait_quant);
+        else                         ok = fu_produce_item<1, 1>(p, smem, sh, leader, g, it, u, alpha, !ready, wait_quant);
         if (next < total) { next_alpha = alpha_of(next_it, next_u); next_ready = unit_ready(next_it); }
     }
     if (!ok && leader) fu_timeout(p.ws, sh);
@@ -311,6 +324,9 @@ __device__ __forceinline__ void fu_mma(uint8_t* smem, FuShared* sh, uint32_t tme
             if (!__all_sync(0xffffffffu, mbar_wait(&sh->full[slot], (g / FU_STAGES) & 1))) { ok = false; break; }
             tc_fence_after();
             const TcStageInfo inf = ld_info(&sh->info[slot]);
+            if (leader && g == 0) VMOE_MARK_MIN(ws, 12);
+            if (leader && inf.pad[0] == ITEM_DOWN && inf.expert >= 0) VMOE_MARK_MIN(ws, 13);
+            if (leader && inf.pad[0] == ITEM_GATE_UP && inf.expert >= 0) VMOE_MARK_MAX(ws, 14);
             if (first) {
                 // the accumulator buffer must have been drained by the epilogue FU_NBUF items ago
                 bool w = true;
@@ -367,6 +383,25 @@ __device__ __forceinline__ void fu_epilogue(const FuParams& p, FuShared* sh, uin
     const int wq = (warp - 2) & 3;                    // warp inside the set
     const int row = quad * 32 + lane;                 // row of the 128-row tile
     const bool combine = p.out != nullptr;
+    if (p.pq_blocks > 0) {
+        // The permuting activation quantiser: chunks of 256 blocks (one per epilogue thread), chunk c on CTA
+        // c mod gridDim.x; the producers meanwhile stream the first weight tiles and only wait for the count of
+        // finished chunks before their first token-tile copy.
+        const int et = (warp - 2) * 32 + lane;                // epilogue thread index, 0 .. 255
+        const int chunks = (p.pq_blocks + FU_PQ_CHUNK - 1) / FU_PQ_CHUNK;
+        int done = 0;
+        for (int c = blockIdx.x; c < chunks; c += gridDim.x, ++done) {
+            const int b = c * FU_PQ_CHUNK + et;
+            if (b < p.pq_blocks)
+                permute_quantize_block<true>(b, p.quant.x, p.M, p.hidden, p.T, p.E, p.has_shared, p.tc_cap, p.quant.topk_ids,
+                                             p.quant.expert_map, p.ws, p.quant.pre_q, p.quant.pre_sf);
+        }
+        if (done) {
+            fence_proxy_async();          // the rows are read by bulk copies (async proxy)
+            asm volatile("bar.sync 1, %0;" ::"r"(FU_PQ_CHUNK) : "memory");
+            if (et == 0) red_release_add(&p.ws.counters[CNT_PQ_DONE], done);
+        }
+    }
     if (combine) {
         // tokens that receive no row at all (no local expert, no shared expert): zeros (+ residual)
         for (int m = blockIdx.x; m < p.M; m += gridDim.x)
@@ -480,6 +515,7 @@ tc_fused_kernel(const __grid_constant__ FuParams p) {
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     FuShared* sh = reinterpret_cast<FuShared*>(smem + (size_t)FU_STAGES * FU_STAGE_BYTES);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) VMOE_MARK_MIN(p.ws, 8);
 
     if (tid == 0) {
         for (int i = 0; i < FU_STAGES; ++i) { mbar_init(&sh->full[i], 1); mbar_init(&sh->empty[i], 1); }
@@ -493,11 +529,19 @@ tc_fused_kernel(const __grid_constant__ FuParams p) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)), "r"(TC_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    if (warp == 0 && lane < 8) {
+        // the descriptors of the first copies: fetched while the previous kernel is still running
+        const CUtensorMap* maps[8] = {&p.map_w13_routed, &p.map_w13_shared, &p.map_w2_routed, &p.map_w2_shared,
+                                      &p.map_act[0], &p.map_act[1], &p.map_inter[0], &p.map_inter[1]};
+        asm volatile("prefetch.tensormap [%0];" ::"l"(maps[lane]) : "memory");
+    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = sh->tmem_base;
+    if (tid == 0) VMOE_MARK_MIN(p.ws, 9);
     pdl_begin();
+    if (tid == 0) VMOE_MARK_MIN(p.ws, 10);
 
     if (warp == 0) fu_producer(p, smem, sh);
     else if (warp == 1) fu_mma(smem, sh, tmem, p.ws);
@@ -505,10 +549,12 @@ tc_fused_kernel(const __grid_constant__ FuParams p) {
 
     tc_fence_before();
     __syncthreads();
+    if (tid == 0) VMOE_MARK_MAX(p.ws, 15);
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_TMEM_COLS) : "memory");
     }
+    if (tid == 32) VMOE_MARK_MAX(p.ws, 16);
     if (p.has_signal) {
         // expert parallelism: the last CTA to leave tells every rank that this rank's rows are in place;
         // the value carries the call number and, in its lowest bit, whether this rank hit an error
@@ -677,8 +723,9 @@ static int fill_fu_params(const vmoe_shape& s, const WeightSet& routed, const We
 
 int launch_tc(const vmoe_shape& s, const WeightSet& routed, const WeightSet& shared, const PreparedSet& prep,
               int M, const Workspace& ws, cudaStream_t st, int phases, __nv_bfloat16* out, const __nv_bfloat16* residual,
-              bool* combined, int unit_cap, long long b_rows, const TcEpSignal* signal) {
+              bool* combined, int unit_cap, long long b_rows, const TcEpSignal* signal, const TcQuant* quant, bool* quantized) {
     if (combined) *combined = false;
+    if (quantized) *quantized = false;
     if (M == 0 && !signal) return VMOE_OK;
     const int cap = unit_cap > 0 ? unit_cap : tc_unit_cap(s, M);
     if (cap == TC_UNIT_TOK_PREFILL) {
@@ -699,7 +746,12 @@ int launch_tc(const vmoe_shape& s, const WeightSet& routed, const WeightSet& sha
     // the step is latency-bound.
     const bool fuse_combine = out != nullptr && phases == (TC_PHASE_GATE_UP | TC_PHASE_DOWN) && ws.row_dst == nullptr &&
                               M <= ws.small_tokens && M <= tuning("VMOE_FUSE_COMBINE_TOKENS", 2);
-    if (fuse_combine) { p.out = out; p.residual = residual; p.M = M; }
+    if (fuse_combine) { p.out = out; p.residual = residual; }
+    p.M = M;
+    if (quant && phases == (TC_PHASE_GATE_UP | TC_PHASE_DOWN)) {
+        p.quant = *quant; p.pq_blocks = M * (s.hidden / SF_BLOCK); p.tc_cap = cap;
+        if (quantized) *quantized = true;
+    }
     if (combined) *combined = fuse_combine;
     if (signal) { p.has_signal = 1; p.signal = *signal; }
     const size_t smem = (size_t)FU_STAGES * FU_STAGE_BYTES + sizeof(FuShared) + 1024;
