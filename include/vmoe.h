@@ -228,6 +228,11 @@ int vmoe_stage_down(const vmoe_shape* shape, const vmoe_weights* routed,
                     const vmoe_weights* shared, int32_t M, void* workspace, void* stream);
 int vmoe_stage_combine(const vmoe_shape* shape, int32_t M, void* workspace,
                        void* out_bf16, void* stream);
+/* gate_up and down projection as the forward runs them on the tensor-core path -- one launch of the fused kernel for
+ * small batches, the two token-major kernels for large ones -- without quantiser and combine: the dominant kernel(s)
+ * alone, for the roofline figure.  VMOE_ERR_SHAPE on the streaming GEMV path. */
+int vmoe_stage_experts(const vmoe_shape* shape, const vmoe_weights* routed,
+                       const vmoe_weights* shared, int32_t M, void* workspace, void* stream);
 
 /* Reads (and clears) the device status word of a workspace after the caller has
  * synchronised the stream: VMOE_OK or VMOE_ERR_TIMEOUT.  The reference has no

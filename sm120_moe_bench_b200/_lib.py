@@ -70,6 +70,8 @@ SIGNATURES = {
                                      C.c_int32, _P, _P]),
     "vmoe_stage_down": (C.c_int, [C.POINTER(VmoeShape), C.POINTER(VmoeWeights), C.POINTER(VmoeWeights),
                                   C.c_int32, _P, _P]),
+    "vmoe_stage_experts": (C.c_int, [C.POINTER(VmoeShape), C.POINTER(VmoeWeights), C.POINTER(VmoeWeights),
+                                     C.c_int32, _P, _P]),
     "vmoe_stage_combine": (C.c_int, [C.POINTER(VmoeShape), C.c_int32, _P, _P, _P]),
     "vmoe_read_status": (C.c_int, [_P, C.POINTER(VmoeShape), _P]),
     "vmoe_ep_slab_bytes": (C.c_size_t, [C.POINTER(VmoeEpCtx), C.POINTER(VmoeShape)]),

@@ -304,6 +304,20 @@ int vmoe_stage_down(const vmoe_shape* shape, const vmoe_weights* routed, const v
     return launch_down(*shape, r, sh, M, ws, static_cast<cudaStream_t>(stream));
 }
 
+int vmoe_stage_experts(const vmoe_shape* shape, const vmoe_weights* routed, const vmoe_weights* shared,
+                       int32_t M, void* workspace, void* stream) {
+    int rc = check_call(shape, routed, shared, M, workspace);
+    if (rc) return rc;
+    Workspace ws;
+    if ((rc = resolve_workspace(shape, workspace, &ws))) return rc;
+    int path;
+    if ((rc = pick_path(shape, routed, shared, &path))) return rc;
+    if (path != VMOE_PATH_TC) return VMOE_ERR_SHAPE;
+    const WeightSet r = to_set(routed), sh = to_set(shape->has_shared ? shared : nullptr);
+    return launch_tc(*shape, r, sh, to_prep(routed, shape->has_shared ? shared : nullptr), M, ws,
+                     static_cast<cudaStream_t>(stream), TC_PHASE_GATE_UP | TC_PHASE_DOWN);
+}
+
 int vmoe_stage_combine(const vmoe_shape* shape, int32_t M, void* workspace, void* out_bf16, void* stream) {
     int rc = check_shape(shape);
     if (rc) return rc;

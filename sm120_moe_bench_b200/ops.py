@@ -296,7 +296,8 @@ def router_gemv(hidden: torch.Tensor, gate_weight: torch.Tensor) -> torch.Tensor
 
 def run_stage(name: str, ws: Workspace, weights: MoEWeights, shared: MoEWeights | None, M: int,
               out: torch.Tensor | None = None) -> None:
-    """Run one stage (``gate_up`` / ``down`` / ``combine``) over an already built workspace."""
+    """Run one stage (``gate_up`` / ``down`` / ``experts`` = both in the forward's own launch(es) / ``combine``) over
+    an already built workspace."""
     sh = C.byref(shared.cstruct()) if shared is not None else None
     if name == "gate_up":
         check(lib.vmoe_stage_gate_up(C.byref(ws._cshape), C.byref(weights.cstruct()), sh, M,
@@ -304,6 +305,9 @@ def run_stage(name: str, ws: Workspace, weights: MoEWeights, shared: MoEWeights 
     elif name == "down":
         check(lib.vmoe_stage_down(C.byref(ws._cshape), C.byref(weights.cstruct()), sh, M,
                                   ws.buf.data_ptr(), _stream()), "vmoe_stage_down")
+    elif name == "experts":
+        check(lib.vmoe_stage_experts(C.byref(ws._cshape), C.byref(weights.cstruct()), sh, M,
+                                     ws.buf.data_ptr(), _stream()), "vmoe_stage_experts")
     elif name == "combine":
         check(lib.vmoe_stage_combine(C.byref(ws._cshape), M, ws.buf.data_ptr(), out.data_ptr(), _stream()),
               "vmoe_stage_combine")

@@ -24,6 +24,7 @@ read the reference project itself.
 from __future__ import annotations
 
 import importlib.util
+import os
 import sys
 from pathlib import Path
 
@@ -135,4 +136,7 @@ def main(ref_root: str):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("VMOE_REFERENCE_ROOT")
+    if not root:
+        raise SystemExit("usage: make_golden.py <reference checkout>   (or set VMOE_REFERENCE_ROOT)")
+    main(root)

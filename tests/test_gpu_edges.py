@@ -54,7 +54,7 @@ def test_empty_batch(path):
 @pytest.mark.parametrize("M", [5, 70, 200, 600])
 def test_every_token_on_the_same_experts(path, M):
     """All tokens pick experts 3 and 7 (in that order): two experts with M tokens each, the others empty.
-    M = 70 / 200 / 600 takes the 64-token-unit and the 128-token-unit kernels with several units per expert."""
+    M = 70 / 200 / 600 takes the token-major kernels (128-token units) with several units per expert."""
     from sm120_moe_bench_b200 import synth
     cfg = synth.LayerConfig("skew", 512, 256, 12, 2, True)
     vm, layer, routed, shared = _setup(cfg, 2, path)
