@@ -70,6 +70,9 @@ def parse():
                     help="prefill: number of routed experts (default 512).  8 experts, top-2 makes the grouped GEMM "
                          "compute-bound: the case that shows the tensor pipe at work")
     ap.add_argument("--topk", type=int, default=None, help="prefill: experts per token (default 10)")
+    ap.add_argument("--norm", action="store_true",
+                    help="stack (one GPU): pre-norm blocks x <- x + moe(rmsnorm(x)); every layer's combine also normalises "
+                         "and quantises the next layer's input (vmoe_extras.next_norm_*), which the next layer takes as codes")
     ap.add_argument("--path", default="tc", choices=["tc", "gemv"],
                     help="tc: tcgen05 block-scaled path (default); gemv: CUDA-core streaming GEMV path")
     return ap.parse_args()
@@ -634,11 +637,26 @@ def run_stack(args, dev):
     logits = [synth.make_inputs(cfg, M, seed=1000 + li, device=dev)[1] for li in range(L)]
     x = x0.clone()
 
-    def one_pass():
-        x.copy_(x0)
-        for li in range(L):
-            # residual add fused into the combine, in place: x <- x + moe(x)
-            vm.fused_moe(x, layers[li][0], ws, router_logits=logits[li], shared=layers[li][1], out=x, residual=x)
+    if args.norm:
+        gen = torch.Generator(device=dev).manual_seed(77)
+        gammas = [(1.0 + 0.05 * torch.randn(cfg.hidden, generator=gen, device=dev)).float() for _ in range(L)]
+        rows = [ops.QuantizedRows(M, cfg.hidden, dev), ops.QuantizedRows(M, cfg.hidden, dev)]
+
+        def one_pass():
+            x.copy_(x0)
+            ops.rmsnorm_quantize(x, gammas[0], 1e-6, out=rows[0])            # the first block's input
+            for li in range(L):
+                cur, nxt = rows[li % 2], rows[(li + 1) % 2]
+                # x <- x + moe(norm(x)); the same kernel leaves norm(x) for the next block as bf16 rows + FP4 codes
+                vm.fused_moe(cur.normed, layers[li][0], ws, router_logits=logits[li], shared=layers[li][1], out=x, residual=x,
+                             hidden_quantized=cur, next_norm=(gammas[li + 1], 1e-6) if li + 1 < L else None,
+                             next_rows=nxt if li + 1 < L else None)
+    else:
+        def one_pass():
+            x.copy_(x0)
+            for li in range(L):
+                # residual add fused into the combine, in place: x <- x + moe(x)
+                vm.fused_moe(x, layers[li][0], ws, router_logits=logits[li], shared=layers[li][1], out=x, residual=x)
 
     one_pass()                                          # warm: tensor maps, attributes
     torch.cuda.synchronize()
@@ -664,7 +682,8 @@ def run_stack(args, dev):
     line = {"metric": "moe_stack_latency_ms", "value": ms_graph, "unit": "ms per pass (per-token latency)", "n_gpus": 1,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_graph, "repeats": len(reps), "higher_is_better": False,
             "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4(w4a4)->f32", "data": "synthetic",
-            "config": {"workload": "stack of MoE layers, config-2 shape, residual add, one CUDA graph (BASELINE config 5 on one GPU)",
+            "config": {"workload": "stack of MoE layers, config-2 shape, residual add, one CUDA graph (BASELINE config 5 on one GPU)" +
+                                   (", pre-norm blocks with RMSNorm + next-layer quantisation fused behind every combine" if args.norm else ""),
                        "layers": L, "tokens": M},
             "us_per_layer": ms_graph * 1e3 / L, "tokens_per_s": M / (ms_graph * 1e-3),
             "eager_ms_per_pass": ms_eager, "graph_equals_eager": same, "clocks": clocks, "device_status": ws.status()}

@@ -36,7 +36,7 @@ namespace vmoe {
 
 constexpr int EP_MAX_RANKS = 16;
 constexpr int EP_FRONT_THREADS = 1024;
-constexpr int EP_FRONT_ROUTE_TOKENS = 64;      // above this the router runs as its own grid-wide launch
+constexpr int EP_FRONT_ROUTE_TOKENS = 32;      // above this the router runs as its own grid-wide launch
 
 struct EpFlags {            // lives at the start of every rank's slab; written by peers
     int32_t dispatch_flag[EP_MAX_RANKS];    // [src] 2 * call + error bit of the last completed dispatch from src

@@ -7,19 +7,25 @@
 // inside the tensor core instead of on the conversion (XU) pipe, which a CUDA-core GEMV saturates long before
 // HBM does.
 //
-// Work items, in queue order:
+// Work of one launch:
+//   first, on the epilogue warps: the permuting activation quantiser (a6) -- chunks of 256 sixteen-element blocks,
+//     chunk c on CTA c mod gridDim.x -- while the producers already stream the first weight tiles; a producer waits
+//     (bounded) for the count of finished chunks before its first token-tile copy;
 //   gate_up item (unit u, row tile t): 128 gate rows + the matching 128 up rows of the unit's expert over all
 //     of K; epilogue = x alpha1, SiLU * up, FP4 re-quantisation of the intermediate (a8 + a9), then one
 //     release-increment of unit_done[u] per epilogue warp;
 //   down item (unit u, row tile t): 128 rows of w2 over all of N; its producer first streams the weight tiles
-//     into the ring, then waits (bounded) until all gate_up tiles of unit u are done before it loads the
-//     intermediate; epilogue = x (router weight x alpha2) -> fp32 row segment (a10), then -- single-GPU
-//     forward -- one increment of token_done[token, t] per token of the unit; whoever completes a token's
-//     count sums that token's rows for these 128 columns in the fixed pair order and writes bf16 (a11).
+//     into the ring, then makes sure (bounded wait; normally seen complete one item earlier) that all gate_up
+//     tiles of unit u are done before it loads the intermediate; epilogue = x (router weight x alpha2) -> fp32
+//     row segment (a10), then -- smallest batches of the single-GPU forward -- one increment of
+//     token_done[token, t] per token of the unit; whoever completes a token's count sums that token's rows for
+//     these 128 columns in the fixed pair order and writes bf16 (a11).
 // All gate_up items precede all down items in the queue and a gate_up item never waits, so a down item only
-// ever waits for items that running CTAs already hold: no co-residency assumption, no grid barrier, and the
-// tail of one projection overlaps the head of the next.  Used alone (stage entry points) a phase mask selects
-// one kind of item and nothing waits.
+// ever waits for items that running CTAs already hold: no grid barrier, and the tail of one projection overlaps
+// the head of the next.  The first item of a CTA is its block index and the quantiser chunks are assigned by block
+// index too, so -- like any grid sized to the SM count -- the launch assumes that every CTA gets an SM; if a
+// foreign kernel keeps one away for longer than the wait limit the call ends with VMOE_ERR_TIMEOUT, never in a
+// hang.  Used alone (stage entry points) a phase mask selects one kind of item and nothing waits.
 //
 // Math follows fused-moe/csrc/verdict_fused_cooperative_tma_ext.cu:323-563 of the reference; its structure
 // (one cooperative kernel, four grid barriers, partial sums per K group) is not reproduced.
