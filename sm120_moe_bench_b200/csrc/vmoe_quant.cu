@@ -128,7 +128,7 @@ norm_quant_kernel(const __nv_bfloat16* x, const float* __restrict__ pair_out, co
         if (FROM_COMBINE) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                q[i] = combine_value<false>((long long)m * (K / 4) + b * 4 + i, pair_out, pair_slot, expert_offsets, K, T, E, has_shared, residual);
+                q[i] = combine_value<true>((long long)m * (K / 4) + b * 4 + i, pair_out, pair_slot, expert_offsets, K, T, E, has_shared, residual);
                 reinterpret_cast<uint2*>(out + (size_t)m * K)[b * 4 + i] = q[i];
             }
         } else {
