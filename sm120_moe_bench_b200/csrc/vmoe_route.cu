@@ -109,8 +109,8 @@ front_kernel(const float* __restrict__ logits, int num_global, TableArgs a, int 
     int32_t* g_off = a.ws.expert_offsets; int32_t* g_ub = a.ws.tc_unit_base; int32_t* g_slot = a.ws.pair_slot;
     a.ids = s_ids; a.w = s_w;
     a.ws.expert_offsets = s_off; a.ws.tc_unit_base = s_ub; a.ws.pair_slot = s_slot;
+    phase_clear(a, tid, nthr);       // touches nothing the router reads or writes: runs beside it on the other warps
     __syncthreads();
-    phase_clear(a, tid, nthr);       __syncthreads();
     phase_mark(a, tid, nthr);        __syncthreads();
     phase_count(a, warp, nwarps, lane, s_count); __syncthreads();
     phase_scan(a, tid, nthr, s_count, s_scan); __syncthreads();

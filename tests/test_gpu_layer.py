@@ -127,6 +127,22 @@ def test_small_shapes_with_shared(vm, M, path):
     _run_and_check(vm, cfg, layer, hidden, logits, M, expert_subset=False, path=path)
 
 
+@pytest.mark.parametrize("hidden,inter,E,T,shared,M", [
+    (768, 768, 5, 1, True, 9),        # odd k-block counts: one k-block per stage in the down items
+    (768, 256, 5, 5, False, 2),       # every expert on every token, no shared expert
+    (1024, 768, 20, 16, True, 3),     # the largest top-k
+    (512, 512, 33, 4, True, 33),      # expert and token counts that are not multiples of anything
+    (2048, 256, 7, 2, False, 100),    # token-major kernels, no shared expert
+    (768, 768, 6, 3, True, 130),      # token-major kernels with an odd k-block count
+])
+def test_assorted_shapes_on_the_tensor_core_path(vm, hidden, inter, E, T, shared, M):
+    from sm120_moe_bench_b200 import synth
+    cfg = synth.LayerConfig("odd", hidden, inter, E, T, shared)
+    layer = synth.make_layer(cfg, seed=hidden + E)
+    hid, logits = synth.make_inputs(cfg, M, seed=M + T)
+    _run_and_check(vm, cfg, layer, hid, logits, M, expert_subset=False, path=TC)
+
+
 def test_prepared_scale_layout(vm):
     """vmoe_prepare_sf: linear [rows, K/16] -> [rows/128][K/64][32][4][4] atoms, NaN bytes -> 0."""
     from sm120_moe_bench_b200._lib import lib
