@@ -9,17 +9,19 @@
 // pair, already quantised (2304 bytes at K = 4096), and each weighted output row crosses once
 // (fp32, so the owner's fixed-order sum is bit-identical to the single-GPU result).
 //
-// Per forward call on rank r (one stream, no host synchronisation, six launches):
-//   1 front     one CTA: route the local tokens, then the plan (destination rank and position inside the
-//               (source -> destination) slab of every pair, in pair order: deterministic)
-//   2 dispatch  quantise each 16-block once, store it into the slab of every destination of the token
-//               (16-byte peer stores); the last CTA publishes row counts and the call flag on every peer
+// Per forward call on rank r (one stream, no host synchronisation, five launches; seven around the token-major kernels):
+//   1 router    one warp per local token
+//   2 dispatch  one CTA per token: the plan (destination rank and position inside the (source -> destination)
+//               slab of every pair, in pair order: deterministic), then each 16-block quantised once and stored
+//               into the slab of every destination of the token (16-byte peer stores); the last CTA publishes
+//               row counts and the call flag on every peer
 //   3 gather    one CTA: bounded acquire-wait on every source's flag, dense list of the rows that actually
 //               arrived (prefix over the sources' counts), permutation tables over exactly those rows
-//   4 permute   received rows into sorted-slot order + scale atoms, destination pointer of every output row
+//   4 permute   received rows into sorted-slot order + scale atoms, destination pointer of every output row: the
+//               first work of the weights-as-rows kernel (a launch of its own in front of the token-major kernels)
 //   5 experts   the tcgen05 kernels of the single-GPU layer; the down projection's epilogue stores each
 //               weighted row straight into the token owner's combine slab over NVLink; the last CTA
-//               publishes the "rows are in place" flag on every peer
+//               publishes the "rows are in place" flag on every peer (a one-warp launch behind the token-major kernels)
 //   6 combine   bounded wait on every rank's flag, fixed-order sum (+ residual) -> bf16; the last CTA
 //               advances the call counter
 // The call number lives in device memory (a counter in the workspace, advanced by step 6), so the chain has
@@ -35,8 +37,6 @@
 namespace vmoe {
 
 constexpr int EP_MAX_RANKS = 16;
-constexpr int EP_FRONT_THREADS = 1024;
-constexpr int EP_FRONT_ROUTE_TOKENS = 32;      // above this the router runs as its own grid-wide launch
 
 struct EpFlags {            // lives at the start of every rank's slab; written by peers
     int32_t dispatch_flag[EP_MAX_RANKS];    // [src] 2 * call + error bit of the last completed dispatch from src
@@ -70,7 +70,6 @@ struct EpState {
     int32_t ticket_dispatch, ticket_experts, ticket_combine;
     int32_t recv_rows;          // rows that arrived for this call
     int32_t src_base[EP_MAX_RANKS + 1];   // exclusive prefix of the rows per source
-    int32_t send_count[EP_MAX_RANKS];
 };
 
 struct EpDev {              // by value into kernels
@@ -79,9 +78,16 @@ struct EpDev {              // by value into kernels
     uint8_t* slab[EP_MAX_RANKS];            // every rank's slab as mapped into this process
     EpLayout L;
     EpState* state;
-    int32_t* plan_dest; int32_t* plan_pos;
     int32_t* flat_ids; float* flat_w; float** row_dst;
+    unsigned long long* timeline;           // development builds (-DVMOE_TIMELINE) only
 };
+#ifdef VMOE_TIMELINE
+#define EP_MARK_MIN(ep, slot) do { if ((ep).timeline) atomicMin(&(ep).timeline[slot], global_timer_ns()); } while (0)
+#define EP_MARK_MAX(ep, slot) do { if ((ep).timeline) atomicMax(&(ep).timeline[slot], global_timer_ns()); } while (0)
+#else
+#define EP_MARK_MIN(ep, slot) ((void)0)
+#define EP_MARK_MAX(ep, slot) ((void)0)
+#endif
 
 __device__ __forceinline__ void st_release_sys(int32_t* p, int32_t v) {
     asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -105,128 +111,96 @@ __device__ __forceinline__ int32_t wait_flag(const int32_t* p, int32_t call, uns
 }
 
 // ---------------------------------------------------------------------------------
-// 1 front: router (one warp per token, several rounds) + plan.  Pair index p = m*T + j for routed pairs,
-// M*T + m for the shared expert, which stays on the owner.  One CTA.
-// ---------------------------------------------------------------------------------
-__global__ void __launch_bounds__(EP_FRONT_THREADS)
-ep_front_kernel(const float* __restrict__ logits, int num_global, int32_t* __restrict__ topk_ids, float* __restrict__ topk_w,
-                int M, int T, int has_shared, EpDev ep) {
-    __shared__ int32_t s_cnt[32][EP_MAX_RANKS];     // pairs per (warp, destination) in the current chunk
-    __shared__ int32_t s_base[EP_MAX_RANKS];        // pairs per destination in earlier chunks
-    extern __shared__ float s_prob[];               // [warps][num_global]
-    pdl_begin();
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
-    if (logits) {
-        for (int m = warp; m < M; m += nwarps)
-            route_token(logits + (size_t)m * num_global, s_prob + (size_t)warp * num_global, num_global, T, lane,
-                        topk_ids + (size_t)m * T, topk_w + (size_t)m * T);
-    }
-    const int P = M * T + (has_shared ? M : 0);
-    if (tid < ep.world) s_base[tid] = 0;
-    __syncthreads();
-    for (int p0 = 0; p0 < P; p0 += blockDim.x) {
-        const int p = p0 + tid;
-        int dest = -1;
-        if (p < P) dest = (p < M * T) ? min(max(topk_ids[p] / ep.e_local, 0), ep.world - 1) : ep.rank;
-        int wrank = 0;
-        for (int d = 0; d < ep.world; ++d) {
-            const unsigned bal = __ballot_sync(0xffffffffu, dest == d);
-            if (lane == 0) s_cnt[warp][d] = __popc(bal);
-            if (dest == d) wrank = __popc(bal & ((1u << lane) - 1u));
-        }
-        __syncthreads();
-        if (dest >= 0) {
-            int wbase = 0;
-            for (int w = 0; w < warp; ++w) wbase += s_cnt[w][dest];
-            ep.plan_dest[p] = dest;
-            ep.plan_pos[p] = s_base[dest] + wbase + wrank;
-        }
-        __syncthreads();
-        if (tid < ep.world) {
-            int total = 0;
-            for (int w = 0; w < nwarps; ++w) total += s_cnt[w][tid];
-            s_base[tid] += total;
-        }
-        __syncthreads();
-    }
-    if (tid < ep.world) ep.state->send_count[tid] = s_base[tid];
-}
-
-// ---------------------------------------------------------------------------------
-// 2 dispatch: quantise each 16-block once (same arithmetic as quantize_kernel), store it into the
-// slab of every destination of the token, then release the per-source flag on every peer.
+// 2 dispatch: one CTA per local token.  The CTA first works out where the token's rows go -- destination rank of
+// every pair and its position inside the (this rank -> destination) slab, which is the number of earlier pairs, in pair
+// order, with the same destination: pair p = m*T + j for routed pairs, M*T + m for the shared expert, which stays
+// on the owner (deterministic: a count over the ids in front, no atomics on the result) -- then quantises each
+// 16-block of the row once (same arithmetic as quantize_kernel) and stores it into the slab of every destination
+// (16-byte peer stores).  The last CTA to finish releases the row counts and the call flag on every peer.
 // ---------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ topk_ids,
                    const float* __restrict__ topk_w, int M, int K, int T, int has_shared, EpDev ep,
                    int32_t* status) {
+    __shared__ int32_t s_before[EP_MAX_RANKS];      // routed pairs of earlier tokens per destination
+    __shared__ int32_t s_total[EP_MAX_RANKS];       // routed pairs of all tokens per destination
+    __shared__ int32_t s_dst[MAX_TOPK + 1], s_pos[MAX_TOPK + 1];
+    __shared__ int s_last;
+    if (threadIdx.x == 0) EP_MARK_MIN(ep, 20);
     pdl_begin();
-    const int bpr = K / SF_BLOCK;
-    const long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (b < (long long)M * bpr) {
-        const int m = (int)(b / bpr), kb = (int)(b % bpr);
-        // destinations of the row: all plan entries are requested at once, ahead of the arithmetic
-        constexpr int MAXJ = MAX_TOPK + 1;
-        int dst[MAXJ], pos[MAXJ];
-#pragma unroll
-        for (int j = 0; j < MAXJ; ++j) {
-            dst[j] = -1; pos[j] = 0;
-            if (j < T || (j == T && has_shared)) {
-                const int p = (j < T) ? m * T + j : M * T + m;
-                dst[j] = ep.plan_dest[p]; pos[j] = ep.plan_pos[p];
-            }
-        }
-        const uint4* src = reinterpret_cast<const uint4*>(x + b * SF_BLOCK);
-        uint4 raw[2] = {src[0], src[1]};
-        const __nv_bfloat16* h = reinterpret_cast<const __nv_bfloat16*>(raw);
-        float v[SF_BLOCK];
-        float amax = 0.f;
-#pragma unroll
-        for (int i = 0; i < SF_BLOCK; ++i) { v[i] = __bfloat162float(h[i]); amax = fmaxf(amax, fabsf(v[i])); }
-        const uint8_t sb = e4m3_encode(fmaxf(amax / 6.0f, 1e-30f));
-        float scale = e4m3_decode(sb);
-        if (scale < 1e-30f) scale = 1e-30f;
-        uint32_t lo = 0, hi = 0;
-        const ScaleDivider div_scale(scale);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) lo |= e2m1_encode(div_scale(v[i])) << (4 * i);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) hi |= e2m1_encode(div_scale(v[8 + i])) << (4 * i);
-#pragma unroll
-        for (int j = 0; j < MAXJ; ++j) {
-            if (dst[j] < 0) continue;
-            if (pos[j] >= ep.capacity) { if (kb == 0) atomicExch(status, VMOE_ERR_LIMIT); continue; }
-            const int p = (j < T) ? m * T + j : M * T + m;
-            uint8_t* slab = ep.slab[dst[j]];
-            const size_t row = (size_t)ep.rank * ep.capacity + pos[j];
-            reinterpret_cast<uint2*>(slab + ep.L.recv_q + row * (K / 2))[kb] = make_uint2(lo, hi);
-            (slab + ep.L.recv_sf + row * (K / 16))[kb] = sb;
-            if (kb == 0) {
-                const int id = (j < T) ? topk_ids[p] : 0;
-                const int le = (j < T) ? id - (id / ep.e_local) * ep.e_local : ep.e_local;     // shared expert = local id E_local
-                const float w = (j < T) ? topk_w[p] : 1.0f;
-                reinterpret_cast<int4*>(slab + ep.L.recv_meta)[row] = make_int4(le, p, __float_as_int(w), 0);
+    if (threadIdx.x == 0) EP_MARK_MIN(ep, 21);
+    const int tid = threadIdx.x, m = blockIdx.x;
+    if (tid < EP_MAX_RANKS) { s_before[tid] = 0; s_total[tid] = 0; }
+    __syncthreads();
+    const int P = M * T;
+    for (int p0 = 0; p0 < P; p0 += blockDim.x) {            // counted by ballots: one shared-memory atomic per warp and destination
+        const int p = p0 + tid;
+        const int d = p < P ? min(max(topk_ids[p] / ep.e_local, 0), ep.world - 1) : -1;
+        for (int dd = 0; dd < ep.world; ++dd) {
+            const unsigned all = __ballot_sync(0xffffffffu, d == dd);
+            const unsigned before = __ballot_sync(0xffffffffu, d == dd && p < m * T);
+            if ((tid & 31) == 0 && all) {
+                atomicAdd(&s_total[dd], __popc(all));
+                if (before) atomicAdd(&s_before[dd], __popc(before));
             }
         }
     }
-    // last CTA to finish publishes the counts and the call flag on every peer
-    __threadfence_system();
     __syncthreads();
-    __shared__ int s_last;
-    if (threadIdx.x == 0) s_last = (atomicAdd(&ep.state->ticket_dispatch, 1) == (int)gridDim.x - 1);
+    if (m < M && tid <= T) {
+        int d, pos;
+        if (tid < T) {
+            d = min(max(topk_ids[m * T + tid] / ep.e_local, 0), ep.world - 1);
+            pos = s_before[d];
+            for (int j = 0; j < tid; ++j) pos += (min(max(topk_ids[m * T + j] / ep.e_local, 0), ep.world - 1) == d);
+        } else {
+            d = has_shared ? ep.rank : -1;
+            pos = s_total[ep.rank] + m;                 // behind every routed pair that stays on this rank
+        }
+        s_dst[tid] = d; s_pos[tid] = pos;
+        if (d >= 0 && pos >= ep.capacity) atomicExch(status, VMOE_ERR_LIMIT);
+    }
     __syncthreads();
-    if (s_last && threadIdx.x < ep.world) {
-        __threadfence_system();
-        const int d = threadIdx.x;
+    if (m < M) {
+        const int bpr = K / SF_BLOCK;
+        for (int kb = tid; kb < bpr; kb += blockDim.x) {
+            const uint4* src = reinterpret_cast<const uint4*>(x + ((size_t)m * bpr + kb) * SF_BLOCK);
+            uint4 raw[2] = {src[0], src[1]};
+            float v[SF_BLOCK]; uint32_t lo, hi; uint8_t sb;
+            quantize_block16(reinterpret_cast<const __nv_bfloat16*>(raw), v, lo, hi, sb);
+            for (int j = 0; j <= T; ++j) {
+                const int d = s_dst[j], pos = s_pos[j];
+                if (d < 0 || pos >= ep.capacity) continue;
+                const int p = (j < T) ? m * T + j : M * T + m;
+                uint8_t* slab = ep.slab[d];
+                const size_t row = (size_t)ep.rank * ep.capacity + pos;
+                reinterpret_cast<uint2*>(slab + ep.L.recv_q + row * (K / 2))[kb] = make_uint2(lo, hi);
+                (slab + ep.L.recv_sf + row * (K / 16))[kb] = sb;
+                if (kb == 0) {
+                    const int id = (j < T) ? topk_ids[p] : 0;
+                    const int le = (j < T) ? id - (id / ep.e_local) * ep.e_local : ep.e_local;     // shared expert = local id E_local
+                    const float w = (j < T) ? topk_w[p] : 1.0f;
+                    reinterpret_cast<int4*>(slab + ep.L.recv_meta)[row] = make_int4(le, p, __float_as_int(w), 0);
+                }
+            }
+        }
+    }
+    // Last CTA to finish publishes the counts and the call flag on every peer.  The ticket orders memory at GPU scope
+    // (release: this CTA's peer stores, seen through the barrier; acquire: the other CTAs'); the one system-scope release
+    // is the flag store, cumulative over all of that and over the count stored just before it by the same thread.
+    __syncthreads();
+    if (tid == 0) s_last = (atom_acq_rel_add(&ep.state->ticket_dispatch, 1) == (int)gridDim.x - 1);
+    __syncthreads();
+    if (s_last && tid < ep.world) {
+        const int d = tid;
         EpFlags* f = reinterpret_cast<EpFlags*>(ep.slab[d] + ep.L.flags);
-        const int c = min(ep.state->send_count[d], ep.capacity);
+        const int sent = s_total[d] + ((has_shared && d == ep.rank) ? M : 0);
         const int32_t call = ep.state->epoch + 1;
         const int32_t bad = (*(volatile int32_t*)status) != 0;
-        f->dispatch_count[ep.rank] = c;
-        __threadfence_system();
+        f->dispatch_count[ep.rank] = min(sent, ep.capacity);
         st_release_sys(&f->dispatch_flag[ep.rank], call * 2 + bad);
     }
-    if (s_last && threadIdx.x == 0) ep.state->ticket_dispatch = 0;
+    if (s_last && tid == 0) ep.state->ticket_dispatch = 0;
+    if (tid == 0) EP_MARK_MAX(ep, 22);
 }
 
 // ---------------------------------------------------------------------------------
@@ -248,6 +222,7 @@ ep_gather_tables_kernel(EpDev ep, TableArgs a, int smem_table_words) {
     const int tid = threadIdx.x, nthr = blockDim.x;
     int32_t* s_count = s_mem; int32_t* s_scan = s_mem + a.E;
     pdl_begin();
+    if (tid == 0) EP_MARK_MIN(ep, 23);
     int32_t* status = a.ws.counters + CNT_STATUS;
     const EpFlags* f = reinterpret_cast<const EpFlags*>(ep.slab[ep.rank] + ep.L.flags);
     const int32_t call = ep.state->epoch + 1;
@@ -272,23 +247,47 @@ ep_gather_tables_kernel(EpDev ep, TableArgs a, int smem_table_words) {
     __syncthreads();
     const int R = s_base[ep.world];
     const int4* meta = reinterpret_cast<const int4*>(ep.slab[ep.rank] + ep.L.recv_meta);
+    a.M = R; a.words = (R + 31) / 32;
+    // Everything a later phase of this CTA reads back lives in shared memory when it fits (ids, weights, expert
+    // offsets, unit bases, slots, bitmap, running popcounts) and is copied out at the end; otherwise only the bitmap
+    // and its popcounts do, or nothing does (the workspace holds room for all of it).
+    int32_t* s_free = s_scan + 3 * nthr;
+    const long long need_tables = 2LL * a.E * a.words, need_rest = 2LL * (a.E + 2) + 3LL * R;
+    const bool shadow = need_tables + need_rest <= smem_table_words;
+    int32_t* g_off = a.ws.expert_offsets; int32_t* g_ub = a.ws.tc_unit_base; int32_t* g_slot = a.ws.pair_slot;
+    int32_t* ids = ep.flat_ids; float* wts = ep.flat_w;
+    if (shadow) {
+        a.ws.expert_offsets = s_free; a.ws.tc_unit_base = s_free + a.E + 2; a.ws.pair_slot = s_free + 2 * (a.E + 2);
+        ids = a.ws.pair_slot + R; wts = reinterpret_cast<float*>(ids + R);
+        s_free = ids + 2 * R;
+        for (int i = tid; i < a.E + 2; i += nthr) a.ws.tc_unit_base[i] = 0;
+    }
+    if (shadow || need_tables <= smem_table_words) {
+        a.ws.bitmap = reinterpret_cast<uint32_t*>(s_free);
+        a.ws.word_prefix = reinterpret_cast<int32_t*>(a.ws.bitmap + (size_t)a.E * a.words);
+    }
     for (int i = tid; i < R; i += nthr) {
         const int s = ep_source_of(s_base, ep.world, i);
         const int4 mt = meta[(size_t)s * ep.capacity + (i - s_base[s])];
-        ep.flat_ids[i] = mt.x;
-        ep.flat_w[i] = __int_as_float(mt.z);
+        ids[i] = mt.x;
+        wts[i] = __int_as_float(mt.z);
+        if (shadow) { ep.flat_ids[i] = mt.x; ep.flat_w[i] = __int_as_float(mt.z); }     // the permutation of the rows reads them
     }
+    a.ids = ids; a.w = wts;
+    phase_clear(a, tid, nthr);
     __syncthreads();
-    a.M = R; a.words = (R + 31) / 32;
-    if ((long long)a.E * a.words * 2 <= smem_table_words) {
-        a.ws.bitmap = reinterpret_cast<uint32_t*>(s_scan + 3 * nthr);
-        a.ws.word_prefix = reinterpret_cast<int32_t*>(a.ws.bitmap + (size_t)a.E * a.words);
-    }
-    phase_clear(a, tid, nthr);       __syncthreads();
+    if (tid == 0) EP_MARK_MAX(ep, 24);
     phase_mark(a, tid, nthr);        __syncthreads();
     phase_count(a, tid >> 5, nthr >> 5, tid & 31, s_count); __syncthreads();
     phase_scan(a, tid, nthr, s_count, s_scan); __syncthreads();
     phase_place(a, tid, nthr);
+    __syncthreads();
+    if (shadow) {
+        for (int i = tid; i < a.E + 2; i += nthr) g_off[i] = a.ws.expert_offsets[i];
+        for (int i = tid; i < a.E + 1; i += nthr) g_ub[i] = a.ws.tc_unit_base[i];
+        for (int i = tid; i < R; i += nthr) g_slot[i] = a.ws.pair_slot[i];
+    }
+    if (tid == 0) EP_MARK_MAX(ep, 25);
 }
 
 // ---------------------------------------------------------------------------------
@@ -297,41 +296,23 @@ ep_gather_tables_kernel(EpDev ep, TableArgs a, int smem_table_words) {
 // arrived (their number is only known on the device).
 // ---------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
-ep_permute_kernel(EpDev ep, int K, int tc_cap, Workspace ws) {
-    __shared__ int32_t s_base[EP_MAX_RANKS + 1];
+ep_permute_kernel(TcEpPermute e, int K, int tc_cap, Workspace ws) {
     pdl_begin();
-    if (threadIdx.x <= ep.world) s_base[threadIdx.x] = ep.state->src_base[threadIdx.x];
-    __syncthreads();
     const int bpr = K / SF_BLOCK;
-    const long long total = (long long)s_base[ep.world] * bpr;
-    const uint8_t* slab = ep.slab[ep.rank];
-    const int cap_shift = 31 - __clz(tc_cap);                     // tc_cap is 16 or 128
-    for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < total; b += (long long)gridDim.x * blockDim.x) {
-        const int i = (int)(b / bpr), kb = (int)(b % bpr);
-        const int slot = ws.pair_slot[i];
-        if (slot < 0) continue;
-        const int src = ep_source_of(s_base, ep.world, i);
-        const size_t row = (size_t)src * ep.capacity + (i - s_base[src]);
-        const uint2 q = reinterpret_cast<const uint2*>(slab + ep.L.recv_q + row * (K / 2))[kb];
-        const uint8_t sb = (slab + ep.L.recv_sf + row * (K / 16))[kb];
-        const int e = ep.flat_ids[i];
-        const int rank_in_e = slot - ws.expert_offsets[e];
-        const int unit = ws.tc_unit_base[e] + (rank_in_e >> cap_shift);
-        const int r = rank_in_e & (tc_cap - 1);
-        reinterpret_cast<uint2*>(ws.act_q_sorted + (size_t)slot * (K / 2))[kb] = q;
-        if (unit < ws.tc_unit_capacity)
-            ws.act_sf_atoms[((size_t)unit * (K / 64) + (kb >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = sb;
-        if (kb == 0) {
-            const int4 mt = reinterpret_cast<const int4*>(slab + ep.L.recv_meta)[row];
-            ep.row_dst[slot] = reinterpret_cast<float*>(ep.slab[src] + ep.L.comb) + (size_t)mt.y * K;   // row of pair id mt.y
-        }
+    const long long total = (long long)e.src_base[e.world] * bpr;
+    constexpr int NB = 4;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long b0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; b0 < total; b0 += NB * stride) {
+        long long bs[NB];
+#pragma unroll
+        for (int n = 0; n < NB; ++n) bs[n] = (b0 + n * stride < total) ? b0 + n * stride : -1;
+        ep_permute_blocks<NB>(e, bs, K, tc_cap, ws);
     }
 }
 
 // 5b: the "rows are in place" flag when the token-major kernels ran (the weights-as-rows kernel publishes it itself)
 __global__ void ep_signal_kernel(EpDev ep, const int32_t* status) {
-    pdl_begin();
-    __threadfence_system();
+    pdl_begin();                   // the down projection's peer stores are complete and visible to this grid
     if (threadIdx.x < ep.world) {
         EpFlags* f = reinterpret_cast<EpFlags*>(ep.slab[threadIdx.x] + ep.L.flags);
         const int32_t bad = (*(volatile const int32_t*)status) != 0;
@@ -349,6 +330,7 @@ ep_combine_kernel(EpDev ep, int M, int K, int T, int has_shared, const __nv_bflo
                   int32_t* status) {
     __shared__ int s_ok;
     pdl_begin();
+    if (threadIdx.x == 0) EP_MARK_MIN(ep, 26);
     const EpFlags* f = reinterpret_cast<const EpFlags*>(ep.slab[ep.rank] + ep.L.flags);
     const int32_t call = ep.state->epoch + 1;
     if (threadIdx.x == 0) s_ok = 1;
@@ -366,15 +348,18 @@ ep_combine_kernel(EpDev ep, int M, int K, int T, int has_shared, const __nv_bflo
         const int k4 = K / 4;
         for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)M * k4; i += (long long)gridDim.x * blockDim.x) {
             const int m = (int)(i / k4), c = (int)(i % k4);
+            // all rows of the token are requested at once (the loop below would otherwise wait for each load in turn)
+            float4 v[MAX_TOPK + 1];
+#pragma unroll
+            for (int j = 0; j <= MAX_TOPK; ++j) {
+                const bool live = j < T || (j == MAX_TOPK && has_shared);
+                const size_t row = j < T ? (size_t)(m * T + j) : (size_t)(M * T + m);
+                v[j] = live ? __ldcg(reinterpret_cast<const float4*>(comb + row * K) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int j = 0; j < T; ++j) {
-                const float4 v = reinterpret_cast<const float4*>(comb + (size_t)(m * T + j) * K)[c];
-                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-            }
-            if (has_shared) {
-                const float4 v = reinterpret_cast<const float4*>(comb + (size_t)(M * T + m) * K)[c];
-                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-            }
+#pragma unroll
+            for (int j = 0; j <= MAX_TOPK; ++j)        // ascending pair order, shared expert last
+                if (j < T || (j == MAX_TOPK && has_shared)) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
             __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
             if (residual) {
                 // x + moe(x) with the layer output rounded to bf16 first: the same bits as a separate bf16 add
@@ -388,6 +373,7 @@ ep_combine_kernel(EpDev ep, int M, int K, int T, int has_shared, const __nv_bflo
         }
     }
     __syncthreads();
+    if (threadIdx.x == 0) EP_MARK_MAX(ep, 27);
     if (threadIdx.x == 0) {
         __threadfence();
         if (atomicAdd(&ep.state->ticket_combine, 1) == (int)gridDim.x - 1) {
@@ -435,8 +421,8 @@ static int ep_tc_units(const vmoe_ep_ctx* c) {
 static size_t ep_extra_bytes(const vmoe_ep_ctx* c, const vmoe_shape* s) {
     const size_t rows = (size_t)c->world * c->capacity;
     const size_t P = (size_t)c->max_local_tokens * (s->topk + 1);
-    // state, plan_dest, plan_pos [P], flat_ids, flat_w [rows], row_dst [rows], local topk ids / weights [P]
-    return ep_align(sizeof(EpState)) + ep_align(P * 4) * 2 + ep_align(rows * 4) * 2 + ep_align(rows * 8) + ep_align(P * 4) * 2;
+    // state, flat_ids, flat_w [rows], row_dst [rows], local topk ids / weights [P]
+    return ep_align(sizeof(EpState)) + ep_align(rows * 4) * 2 + ep_align(rows * 8) + ep_align(P * 4) * 2;
 }
 
 extern "C" {
@@ -507,10 +493,9 @@ int vmoe_ep_forward(const vmoe_ep_ctx* ctx, const vmoe_shape* shape, const vmoe_
     ep.wait_ns = ctx->wait_limit_us > 0 ? (unsigned long long)ctx->wait_limit_us * 1000ull : MBAR_WAIT_LIMIT_NS;
     for (int i = 0; i < ctx->world; ++i) ep.slab[i] = static_cast<uint8_t*>(ctx->slab[i]);
     ep.L = ep_layout(ctx->world, ctx->capacity, ctx->max_local_tokens, K, T);
+    ep.timeline = ws.timeline;
     auto take = [&](size_t b) { uint8_t* p = extra; extra += ep_align(b); return p; };
     ep.state = reinterpret_cast<EpState*>(take(sizeof(EpState)));
-    ep.plan_dest = reinterpret_cast<int32_t*>(take(P * 4));
-    ep.plan_pos = reinterpret_cast<int32_t*>(take(P * 4));
     ep.flat_ids = reinterpret_cast<int32_t*>(take(rows * 4));
     ep.flat_w = reinterpret_cast<float*>(take(rows * 4));
     ep.row_dst = reinterpret_cast<float**>(take(rows * 8));
@@ -520,29 +505,18 @@ int vmoe_ep_forward(const vmoe_ep_ctx* ctx, const vmoe_shape* shape, const vmoe_
     const int has_shared = shape->has_shared ? 1 : 0;
     const int Eg = shape->num_global_experts;
 
-    // 1 front
+    // 1 router
+    if ((rc = launch_route(router_logits, M, Eg, T, loc_ids, loc_w, st))) return rc;
     {
-        const float* lg = router_logits;
-        size_t smem = (size_t)(EP_FRONT_THREADS / 32) * Eg * sizeof(float);
-        if (M > EP_FRONT_ROUTE_TOKENS || smem > 160 * 1024) {
-            if ((rc = launch_route(router_logits, M, Eg, T, loc_ids, loc_w, st))) return rc;
-            lg = nullptr; smem = 0;
-        }
         static bool attr_done = false;
         if (!attr_done) {
-            cudaFuncSetAttribute(ep_front_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
             cudaFuncSetAttribute(ep_gather_tables_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
             attr_done = true;
         }
-        launch_pdl(ep_front_kernel, 1u, (unsigned)EP_FRONT_THREADS, smem, st, lg, Eg, loc_ids, loc_w, M, T, has_shared, ep);
     }
-    // 2 dispatch
-    {
-        const long long nb = (long long)M * (K / SF_BLOCK);
-        const unsigned grid = (unsigned)((nb + 255) / 256 > 0 ? (nb + 255) / 256 : 1);
-        launch_pdl(ep_dispatch_kernel, grid, 256u, 0, st, static_cast<const __nv_bfloat16*>(hidden_bf16), loc_ids, loc_w,
-                   M, K, T, has_shared, ep, status);
-    }
+    // 2 dispatch (+ plan): one CTA per local token; a rank without tokens still publishes its (empty) counts
+    launch_pdl(ep_dispatch_kernel, (unsigned)(M > 0 ? M : 1), 256u, 0, st, static_cast<const __nv_bfloat16*>(hidden_bf16),
+               loc_ids, loc_w, M, K, T, has_shared, ep, status);
     // Tokens per work unit and with them the kernel: chosen from the rows a rank receives under balanced routing
     // (about its own M * (T + 1)); any other row count is still computed correctly, only not by the faster kernel.
     vmoe_shape est = lt;
@@ -561,30 +535,43 @@ int vmoe_ep_forward(const vmoe_ep_ctx* ctx, const vmoe_shape* shape, const vmoe_
         const size_t smem = 200 * 1024;
         launch_pdl(ep_gather_tables_kernel, 1u, nthr, smem, st, ep, a, (int)((smem - fixed) / 4));
     }
-    // 4 permute
-    launch_pdl(ep_permute_kernel, (unsigned)(2 * 148), 256u, 0, st, ep, K, cap, ws);
-    // 5 experts
+    // 4 permute + 5 experts.  The weights-as-rows kernel permutes the received rows as its first work and publishes
+    // the "rows are in place" flags from its last CTA; around the token-major kernels both are launches of their own.
     const WeightSet r{routed->w13, routed->w13_sf, routed->w13_gs, routed->w2, routed->w2_sf, routed->w2_gs};
     const WeightSet sh = shape->has_shared ? WeightSet{shared->w13, shared->w13_sf, shared->w13_gs, shared->w2, shared->w2_sf, shared->w2_gs}
                                            : r;
     PreparedSet prep{routed->w13_sf_atoms, routed->w2_sf_atoms,
                      shape->has_shared ? shared->w13_sf_atoms : routed->w13_sf_atoms,
                      shape->has_shared ? shared->w2_sf_atoms : routed->w2_sf_atoms};
+    TcEpPermute perm;
+    memset(&perm, 0, sizeof(perm));
+    perm.recv_q = ep.slab[ctx->rank] + ep.L.recv_q; perm.recv_sf = ep.slab[ctx->rank] + ep.L.recv_sf;
+    perm.recv_meta = reinterpret_cast<const int4*>(ep.slab[ctx->rank] + ep.L.recv_meta);
+    for (int i = 0; i < ctx->world; ++i) perm.comb[i] = reinterpret_cast<float*>(ep.slab[i] + ep.L.comb);
+    perm.src_base = ep.state->src_base; perm.flat_ids = ep.flat_ids; perm.row_dst = ep.row_dst;
+    perm.world = ctx->world; perm.capacity = ctx->capacity;
     ws.row_dst = ep.row_dst;
     const int Mr = (int)rows;
-    if (cap == TC_UNIT_TOK_SMALL) {
+    const bool in_kernel = cap == TC_UNIT_TOK_SMALL;
+    if (in_kernel) {
         TcEpSignal sig;
         memset(&sig, 0, sizeof(sig));
         for (int i = 0; i < ctx->world; ++i)
             sig.flag[i] = &reinterpret_cast<EpFlags*>(ep.slab[i] + ep.L.flags)->combine_flag[ctx->rank];
         sig.world = ctx->world; sig.epoch = &ep.state->epoch; sig.ticket = &ep.state->ticket_experts;
-        if ((rc = launch_tc(lk, r, sh, prep, Mr, ws, st, TC_PHASE_GATE_UP | TC_PHASE_DOWN, nullptr, nullptr, nullptr, cap, Mr, &sig))) return rc;
+        if ((rc = launch_tc(lk, r, sh, prep, Mr, ws, st, TC_PHASE_GATE_UP | TC_PHASE_DOWN, nullptr, nullptr, nullptr, cap, Mr, &sig,
+                            nullptr, nullptr, &perm))) return rc;
     } else {
-        if ((rc = launch_tc(lk, r, sh, prep, Mr, ws, st, TC_PHASE_GATE_UP | TC_PHASE_DOWN, nullptr, nullptr, nullptr, cap, Mr, nullptr))) return rc;
+        launch_pdl(ep_permute_kernel, (unsigned)(2 * 148), 256u, 0, st, perm, K, cap, ws);
+        if ((rc = launch_tc(lk, r, sh, prep, Mr, ws, st, TC_PHASE_GATE_UP | TC_PHASE_DOWN, nullptr, nullptr, nullptr, cap, Mr))) return rc;
         launch_pdl(ep_signal_kernel, 1u, 32u, 0, st, ep, static_cast<const int32_t*>(status));
     }
     // 6 combine
-    launch_pdl(ep_combine_kernel, 148u, 256u, 0, st, ep, M, K, T, has_shared, static_cast<const __nv_bfloat16*>(residual_bf16),
+    // one output element (four columns) per thread, like the single-GPU combine; at least one CTA (a rank without
+    // tokens still waits for the flags and advances the call counter)
+    const long long cn = (long long)M * (K / 4);
+    const unsigned cgrid = (unsigned)(cn > 0 ? (cn + 255) / 256 < 65535 ? (cn + 255) / 256 : 65535 : 1);
+    launch_pdl(ep_combine_kernel, cgrid, 256u, 0, st, ep, M, K, T, has_shared, static_cast<const __nv_bfloat16*>(residual_bf16),
                static_cast<__nv_bfloat16*>(out_bf16), status);
     return cuda_status(cudaGetLastError());
 }

@@ -352,6 +352,43 @@ __device__ __forceinline__ void permute_store_block(int b, uint32_t lo, uint32_t
         ws.act_sf_atoms[((size_t)unit * (K / 64) + (kb >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = sb;
     }
 }
+// Expert parallelism: NB 16-element blocks (block b = received row b / bpr of the dense list, k-block b % bpr; b < 0 =
+// none) go to their sorted slots + scale atoms; a block with k-block 0 also records where its slot's output row goes:
+// the row of the pair in its owner's combine area.  Row i of the dense list = source s, position i - src_base[s].
+// The table reads of all NB blocks are issued level by level (three dependent round trips for the batch, not per block).
+template <int NB>
+__device__ __forceinline__ void ep_permute_blocks(const TcEpPermute& e, const long long (&b)[NB], int K, int tc_cap, const Workspace& ws) {
+    const int bpr = K / SF_BLOCK;
+    const int cap_shift = 31 - __clz(tc_cap);                     // tc_cap is 16 or 128
+    int row_i[NB], kb[NB], slot[NB], ex[NB], src[NB];
+#pragma unroll
+    for (int n = 0; n < NB; ++n) {
+        slot[n] = -1; ex[n] = 0; row_i[n] = 0; kb[n] = 0;
+        if (b[n] >= 0) { row_i[n] = (int)(b[n] / bpr); kb[n] = (int)(b[n] % bpr); slot[n] = ws.pair_slot[row_i[n]]; ex[n] = e.flat_ids[row_i[n]]; }
+    }
+    uint2 q[NB]; uint8_t sb[NB]; int off[NB], ub[NB]; size_t row[NB];
+#pragma unroll
+    for (int n = 0; n < NB; ++n) {
+        src[n] = 0; row[n] = 0; off[n] = 0; ub[n] = 0; q[n] = make_uint2(0, 0); sb[n] = 0;
+        if (slot[n] < 0) continue;
+        while (src[n] + 1 < e.world && row_i[n] >= e.src_base[src[n] + 1]) ++src[n];
+        row[n] = (size_t)src[n] * e.capacity + (row_i[n] - e.src_base[src[n]]);
+        q[n] = reinterpret_cast<const uint2*>(e.recv_q + row[n] * (K / 2))[kb[n]];
+        sb[n] = (e.recv_sf + row[n] * (K / 16))[kb[n]];
+        off[n] = ws.expert_offsets[ex[n]]; ub[n] = ws.tc_unit_base[ex[n]];
+    }
+#pragma unroll
+    for (int n = 0; n < NB; ++n) {
+        if (slot[n] < 0) continue;
+        const int rank_in_e = slot[n] - off[n];
+        const int unit = ub[n] + (rank_in_e >> cap_shift);
+        const int r = rank_in_e & (tc_cap - 1);
+        reinterpret_cast<uint2*>(ws.act_q_sorted + (size_t)slot[n] * (K / 2))[kb[n]] = q[n];
+        if (unit < ws.tc_unit_capacity)
+            ws.act_sf_atoms[((size_t)unit * (K / 64) + (kb[n] >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb[n] & 3)] = sb[n];
+        if (kb[n] == 0) e.row_dst[slot[n]] = e.comb[src[n]] + (size_t)e.recv_meta[row[n]].y * K;     // row of the pair in its owner's slab
+    }
+}
 template <bool BATCHED>
 __device__ __forceinline__ uint2 combine_value(long long i, const float* pair_out, const int32_t* pair_slot,
                                                const int32_t* expert_offsets, int K, int T, int E, int has_shared,

@@ -81,6 +81,8 @@ struct FuParams {
     // permuting activation quantiser as the kernel's first work (pq_blocks = M * K / 16; 0 = done by the caller)
     int pq_blocks, tc_cap;
     TcQuant quant;
+    int has_ep_permute;        // expert parallelism: the first work is the permutation of the received rows instead
+    TcEpPermute ep_permute;
     int has_signal;
     TcEpSignal signal;
 };
@@ -121,15 +123,6 @@ __device__ __forceinline__ void fu_timeout(const Workspace& ws, FuShared* sh) {
     atomicExch(&ws.counters[CNT_STATUS], VMOE_ERR_TIMEOUT);
     atomicExch(&sh->abort_flag, 1);
 }
-__device__ __forceinline__ void red_release_add(int32_t* p, int32_t v) {
-    asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ int32_t atom_acq_rel_add(int32_t* p, int32_t v) {
-    int32_t old;
-    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
-    return old;
-}
-
 // kind of a stage record: TcStageInfo::pad[0]; k-blocks per stage: pad[1]
 enum { ITEM_GATE_UP = 0, ITEM_DOWN = 1 };
 
@@ -187,7 +180,8 @@ __device__ __forceinline__ bool fu_produce_item(const FuParams& p, uint8_t* smem
         if (!DOWN && wait_quant) {
             // the slot-ordered activation rows are written by this kernel's epilogue warps (all CTAs' together) while
             // the first weight tiles above are in flight
-            const bool done = wait_counter(&p.ws.counters[CNT_PQ_DONE], (p.pq_blocks + FU_PQ_CHUNK - 1) / FU_PQ_CHUNK);
+            const int nblk = p.has_ep_permute ? p.ep_permute.src_base[p.ep_permute.world] * (p.hidden / SF_BLOCK) : p.pq_blocks;
+            const bool done = wait_counter(&p.ws.counters[CNT_PQ_DONE], (nblk + FU_PQ_CHUNK - 1) / FU_PQ_CHUNK);
             if (!__all_sync(0xffffffffu, done)) return false;
             wait_quant = false;
         }
@@ -248,7 +242,7 @@ __device__ __forceinline__ void fu_producer(const FuParams& p, uint8_t* smem, Fu
     bool next_ready = (next < total) ? unit_ready(next_it) : true;
     uint32_t g = 0;
     bool ok = true;
-    bool wait_quant = p.pq_blocks > 0;
+    bool wait_quant = p.pq_blocks > 0 || p.has_ep_permute;
     while (ok) {
         if (next >= total) break;
         const FuItem it = next_it;
@@ -389,18 +383,35 @@ __device__ __forceinline__ void fu_epilogue(const FuParams& p, FuShared* sh, uin
     const int wq = (warp - 2) & 3;                    // warp inside the set
     const int row = quad * 32 + lane;                 // row of the 128-row tile
     const bool combine = p.out != nullptr;
-    if (p.pq_blocks > 0) {
-        // The permuting activation quantiser: chunks of 256 blocks (one per epilogue thread), chunk c on CTA
-        // c mod gridDim.x; the producers meanwhile stream the first weight tiles and only wait for the count of
-        // finished chunks before their first token-tile copy.
+    if (p.pq_blocks > 0 || p.has_ep_permute) {
+        // The permuting activation quantiser (expert parallelism: the permutation of the rows that arrived): chunks of
+        // 256 blocks (one per epilogue thread), chunk c on CTA c mod gridDim.x; the producers meanwhile stream the
+        // first weight tiles and only wait for the count of finished chunks before their first token-tile copy.
         const int et = (warp - 2) * 32 + lane;                // epilogue thread index, 0 .. 255
-        const int chunks = (p.pq_blocks + FU_PQ_CHUNK - 1) / FU_PQ_CHUNK;
+        const int bpr = p.hidden / SF_BLOCK;
+        const int nblk = p.has_ep_permute ? p.ep_permute.src_base[p.ep_permute.world] * bpr : p.pq_blocks;
+        const int chunks = (nblk + FU_PQ_CHUNK - 1) / FU_PQ_CHUNK;
         int done = 0;
-        for (int c = blockIdx.x; c < chunks; c += gridDim.x, ++done) {
-            const int b = c * FU_PQ_CHUNK + et;
-            if (b < p.pq_blocks)
-                permute_quantize_block<true>(b, p.quant.x, p.M, p.hidden, p.T, p.E, p.has_shared, p.tc_cap, p.quant.topk_ids,
-                                             p.quant.expert_map, p.ws, p.quant.pre_q, p.quant.pre_sf);
+        if (p.has_ep_permute) {
+            constexpr int NB = 4;                             // chunks a thread handles per batch of table reads
+            for (int c = blockIdx.x; c < chunks; c += NB * gridDim.x) {
+                long long bs[NB];
+#pragma unroll
+                for (int n = 0; n < NB; ++n) {
+                    const int cn = c + n * gridDim.x;
+                    const long long b = (long long)cn * FU_PQ_CHUNK + et;
+                    bs[n] = (cn < chunks && b < nblk) ? b : -1;
+                    if (cn < chunks) ++done;
+                }
+                ep_permute_blocks<NB>(p.ep_permute, bs, p.hidden, p.tc_cap, p.ws);
+            }
+        } else {
+            for (int c = blockIdx.x; c < chunks; c += gridDim.x, ++done) {
+                const int b = c * FU_PQ_CHUNK + et;
+                if (b < nblk)
+                    permute_quantize_block<true>(b, p.quant.x, p.M, p.hidden, p.T, p.E, p.has_shared, p.tc_cap, p.quant.topk_ids,
+                                                 p.quant.expert_map, p.ws, p.quant.pre_q, p.quant.pre_sf);
+            }
         }
         if (done) {
             fence_proxy_async();          // the rows are read by bulk copies (async proxy)
@@ -512,7 +523,6 @@ __device__ __forceinline__ void fu_epilogue(const FuParams& p, FuShared* sh, uin
             }
         }
     }
-    if (p.has_signal) __threadfence_system();     // this thread's peer stores, before the CTA reports its exit
 }
 
 __global__ void __launch_bounds__(FU_THREADS, 1)
@@ -564,13 +574,12 @@ tc_fused_kernel(const __grid_constant__ FuParams p) {
     if (p.has_signal) {
         // expert parallelism: the last CTA to leave tells every rank that this rank's rows are in place;
         // the value carries the call number and, in its lowest bit, whether this rank hit an error
-        if (tid == 0) {
-            __threadfence_system();
-            sh->last_cta = (atomicAdd(p.signal.ticket, 1) == (int)gridDim.x - 1);
-        }
+        // The ticket orders memory at GPU scope (release: this CTA's peer stores, seen through the barrier above;
+        // acquire: the other CTAs'); the one system-scope release is the flag store of the last CTA, which is cumulative
+        // over all of that.  (A system-scope fence in every CTA cost ~9 us at the end of every call.)
+        if (tid == 0) sh->last_cta = (atom_acq_rel_add(p.signal.ticket, 1) == (int)gridDim.x - 1);
         __syncthreads();
         if (sh->last_cta && tid < p.signal.world) {
-            __threadfence_system();
             const int32_t call = *p.signal.epoch + 1;
             const int32_t bad = (*(volatile int32_t*)&p.ws.counters[CNT_STATUS]) != 0;
             asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.signal.flag[tid]), "r"(call * 2 + bad) : "memory");
@@ -729,9 +738,11 @@ static int fill_fu_params(const vmoe_shape& s, const WeightSet& routed, const We
 
 int launch_tc(const vmoe_shape& s, const WeightSet& routed, const WeightSet& shared, const PreparedSet& prep,
               int M, const Workspace& ws, cudaStream_t st, int phases, __nv_bfloat16* out, const __nv_bfloat16* residual,
-              bool* combined, int unit_cap, long long b_rows, const TcEpSignal* signal, const TcQuant* quant, bool* quantized) {
+              bool* combined, int unit_cap, long long b_rows, const TcEpSignal* signal, const TcQuant* quant, bool* quantized,
+              const TcEpPermute* ep_permute, bool* ep_done) {
     if (combined) *combined = false;
     if (quantized) *quantized = false;
+    if (ep_done) *ep_done = false;
     if (M == 0 && !signal) return VMOE_OK;
     const int cap = unit_cap > 0 ? unit_cap : tc_unit_cap(s, M);
     if (cap == TC_UNIT_TOK_PREFILL) {
@@ -760,6 +771,8 @@ int launch_tc(const vmoe_shape& s, const WeightSet& routed, const WeightSet& sha
     }
     if (combined) *combined = fuse_combine;
     if (signal) { p.has_signal = 1; p.signal = *signal; }
+    if (ep_permute) { p.has_ep_permute = 1; p.ep_permute = *ep_permute; p.tc_cap = cap; }
+    if (ep_done) *ep_done = signal != nullptr && ep_permute != nullptr;
     const size_t smem = (size_t)FU_STAGES * FU_STAGE_BYTES + sizeof(FuShared) + 1024;
     static bool attr_set[64] = {false};       // per device
     int dev = 0;
