@@ -976,7 +976,10 @@ def run_expert_parallel(args, world, rank, local, dev):
             "e2e": {"value": tokens_total / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": M * (cfg.hidden * 2 + cfg.num_experts * 4) * world,
                     "d2h_bytes_per_step": M * cfg.hidden * 2 * world, "ms_per_step": e2e_ms / args.steps},
-            "gpu_launches": 6 * args.steps * world,   # front, dispatch, gather + tables, permute, experts, combine
+            # router, dispatch (+ plan), gather + tables, experts, combine; above the small-batch threshold the
+            # received-row permutation, the second expert kernel and the flag kernel are launches of their own
+            "gpu_launches": (5 if M * cfg.topk <= min(int(os.environ.get("VMOE_SMALL_PER_EXPERT", "10")), 16) * per else 8)
+                            * args.steps * world,
             "device_status": int(st.item()),
         }
         print(json.dumps(line), flush=True)

@@ -70,7 +70,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
         log.append(out)
         if p.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src.name}:\n{out}")
-    subprocess.run([nvcc, "-shared", "-o", str(LIB), *objs, "-lcudart"], check=True)
+    subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", str(LIB), *objs, "-lcudart"], check=True)
     (objdir / "ptxas.log").write_text("\n".join(log))
     STAMP.write_text(digest)
     if verbose:

@@ -517,11 +517,10 @@ int vmoe_ep_forward(const vmoe_ep_ctx* ctx, const vmoe_shape* shape, const vmoe_
     // 2 dispatch (+ plan): one CTA per local token; a rank without tokens still publishes its (empty) counts
     launch_pdl(ep_dispatch_kernel, (unsigned)(M > 0 ? M : 1), 256u, 0, st, static_cast<const __nv_bfloat16*>(hidden_bf16),
                loc_ids, loc_w, M, K, T, has_shared, ep, status);
-    // Tokens per work unit and with them the kernel: chosen from the rows a rank receives under balanced routing
-    // (about its own M * (T + 1)); any other row count is still computed correctly, only not by the faster kernel.
-    vmoe_shape est = lt;
-    est.topk = 1;
-    const int cap = tc_unit_cap(est, M * (T + 1));
+    // Tokens per work unit and with them the kernel: chosen by the single-GPU rule (routed pairs per routed expert)
+    // from the rows a rank receives under balanced routing, about its own M * T; any other row count is still
+    // computed correctly, only not by the faster kernel.
+    const int cap = tc_unit_cap(lk, M * T);
     // 3 gather + tables
     {
         TableArgs a;

@@ -675,6 +675,27 @@ int make_map(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t ro
     return VMOE_OK;
 }
 
+// Scale atoms as a 2-D tensor: rows of one 512-byte atom (128 words), box = the four atoms of one 256-element k-step.
+int make_sf_map(CUtensorMap* map, const void* base, uint64_t atoms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const MapKey key{dev, base, 512, atoms, 0x80000004u};
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    auto it = g_map_cache.find(key);
+    if (it != g_map_cache.end()) { *map = it->second; return VMOE_OK; }
+    const cuuint64_t dims[2] = {128, atoms};
+    const cuuint64_t strides[1] = {512};
+    const cuuint32_t box[2] = {128, 4};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return VMOE_ERR_CUDA;
+    if (g_map_cache.size() >= 65536) g_map_cache.clear();
+    g_map_cache.emplace(key, *map);
+    return VMOE_OK;
+}
+
 int tc_sm_count() {
     static int n = 0;
     if (n == 0) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev); if (n <= 0) n = 148; }
@@ -746,9 +767,21 @@ int launch_tc(const vmoe_shape& s, const WeightSet& routed, const WeightSet& sha
     if (M == 0 && !signal) return VMOE_OK;
     const int cap = unit_cap > 0 ? unit_cap : tc_unit_cap(s, M);
     if (cap == TC_UNIT_TOK_PREFILL) {
+        // VMOE_PF_PAIR=1 runs the projections on CTA pairs (cta_group::2, vmoe_tc_pair.cu).  Off by default: measured on
+        // the 8192-token layer under the power cap the pairs tie on gate_up (655 against 660 us) and lose on the down
+        // projection (754 against 638 us: short items, and the single accumulator is handed over across two CTAs).
         int rc = VMOE_OK;
-        if (phases & TC_PHASE_GATE_UP) rc = launch_pf_gate_up(s, routed, shared, prep, M, ws, st, b_rows);
-        if (!rc && (phases & TC_PHASE_DOWN)) rc = launch_pf_down(s, routed, shared, prep, M, ws, st, b_rows);
+        const bool pairs = tuning("VMOE_PF_PAIR", 0) != 0;
+        if (phases & TC_PHASE_GATE_UP) {
+            bool done = false;
+            if (pairs) rc = launch_pair_gate_up(s, routed, shared, prep, M, ws, st, b_rows, &done);
+            if (!rc && !done) rc = launch_pf_gate_up(s, routed, shared, prep, M, ws, st, b_rows);
+        }
+        if (!rc && (phases & TC_PHASE_DOWN)) {
+            bool done = false;
+            if (pairs) rc = launch_pair_down(s, routed, shared, prep, M, ws, st, b_rows, &done);
+            if (!rc && !done) rc = launch_pf_down(s, routed, shared, prep, M, ws, st, b_rows);
+        }
         return rc;
     }
     FuParams p;

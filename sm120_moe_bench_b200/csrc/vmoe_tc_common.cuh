@@ -91,6 +91,13 @@ __device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t (&r)[8]) {
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                  : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // shared-memory matrix descriptors (sm_100 format: version 1 in bits 46-47)
@@ -126,6 +133,7 @@ __device__ __forceinline__ void tc_timeout(const Workspace& ws, TcShared* sh) {
 // host: cached cuTensorMapEncodeTiled of a 2-D byte tensor [rows, row_bytes], box [box_rows, 128 B], 128-byte swizzle
 int get_encoder();
 int make_map(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows);
+int make_sf_map(CUtensorMap* map, const void* base, uint64_t atoms);   // scale atoms [atoms, 512 B], box = 4 atoms
 int tc_sm_count();
 
 }  // namespace vmoe

@@ -54,14 +54,6 @@ struct PfParams {
     int K, N, hidden, E, tiles, queue;
 };
 
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr) : "memory");
-}
-
 // Cycle counters per role, summed over CTAs (development builds with -DVMOE_PROFILE only; read and cleared by
 // vmoe_debug_read_profile of csrc/vmoe_debug.h):
 // [0] MMA warp: waiting for a full stage, [1] MMA warp: waiting for the accumulator, [2] MMA warp: issuing,
