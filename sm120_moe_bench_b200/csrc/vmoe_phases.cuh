@@ -324,34 +324,6 @@ __device__ __forceinline__ void permute_quantize_block(long long b, const __nv_b
     }
 }
 
-// out[m, 4c .. 4c+3] = bf16( sum_j pair_out[slot(m, j), :]  (ascending j, fp32)  + shared row ) [+ residual],
-// element i = m * (K / 4) + c.  BATCHED: slot numbers and then all rows requested at once (small launches).
-// The permuting half alone: an already quantised block (codes lo / hi, scale byte sb) of token-major block b goes to
-// every sorted slot of its token.  The tables are read one pair at a time (the one-CTA front keeps them in shared memory).
-__device__ __forceinline__ void permute_store_block(int b, uint32_t lo, uint32_t hi, uint8_t sb, int K, int T, int E, int has_shared,
-                                                    int tc_cap, const int32_t* topk_ids, const int32_t* expert_map, const Workspace& ws) {
-    const int bpr = K / SF_BLOCK;
-    const int cap_shift = 31 - __clz(tc_cap);
-    const int m = b / bpr, kb = b % bpr;
-    for (int j = 0; j <= T; ++j) {
-        int e, sl;
-        if (j < T) {
-            sl = ws.pair_slot[m * T + j];
-            if (sl < 0) continue;
-            e = topk_ids[m * T + j];
-            if (expert_map) e = expert_map[e];
-        } else {
-            if (!has_shared) break;
-            e = E;
-            sl = ws.expert_offsets[E] + m;
-        }
-        const int rank = sl - ws.expert_offsets[e];
-        const int unit = ws.tc_unit_base[e] + (rank >> cap_shift);
-        const int r = rank & (tc_cap - 1);
-        reinterpret_cast<uint2*>(ws.act_q_sorted + (size_t)sl * (K / 2))[kb] = make_uint2(lo, hi);
-        ws.act_sf_atoms[((size_t)unit * (K / 64) + (kb >> 2)) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = sb;
-    }
-}
 // Expert parallelism: NB 16-element blocks (block b = received row b / bpr of the dense list, k-block b % bpr; b < 0 =
 // none) go to their sorted slots + scale atoms; a block with k-block 0 also records where its slot's output row goes:
 // the row of the pair in its owner's combine area.  Row i of the dense list = source s, position i - src_base[s].
@@ -389,6 +361,8 @@ __device__ __forceinline__ void ep_permute_blocks(const TcEpPermute& e, const lo
         if (kb[n] == 0) e.row_dst[slot[n]] = e.comb[src[n]] + (size_t)e.recv_meta[row[n]].y * K;     // row of the pair in its owner's slab
     }
 }
+// out[m, 4c .. 4c+3] = bf16( sum_j pair_out[slot(m, j), :]  (ascending j, fp32)  + shared row ) [+ residual],
+// element i = m * (K / 4) + c.  BATCHED: slot numbers and then all rows requested at once (small launches).
 template <bool BATCHED>
 __device__ __forceinline__ uint2 combine_value(long long i, const float* pair_out, const int32_t* pair_slot,
                                                const int32_t* expert_offsets, int K, int T, int E, int has_shared,
