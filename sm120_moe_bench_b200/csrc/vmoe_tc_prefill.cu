@@ -52,6 +52,7 @@ struct PfParams {
     const float* gs_routed; const float* gs_shared;
     Workspace ws;
     int K, N, hidden, E, tiles, queue;
+    int wide_rows;                               // down epilogue: exchange row pieces between lanes for 128-byte stores
 };
 
 // Cycle counters per role, summed over CTAs (development builds with -DVMOE_PROFILE only; read and cleared by
@@ -303,7 +304,6 @@ pf_kernel(const __grid_constant__ PfParams p) {
                 pe_math += prof_clock() - q1;
             } else {
                 const float scale = valid ? p.ws.scatter_weights[srow] * alpha : 0.f;
-                float* orow = (p.ws.row_dst ? p.ws.row_dst[srow] : p.ws.pair_out + srow * p.hidden) + inf.tile * PF_N + sub * 64;
                 uint32_t yr[4][16];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) tc_ld16(tacc + sub * 64 + c * 16, yr[c]);
@@ -313,19 +313,68 @@ pf_kernel(const __grid_constant__ PfParams p) {
                 if (lane == 0) mbar_arrive(&sh->tmem_empty[0]);
                 const long long q1 = prof_clock();
                 pe_ld += q1 - c1;
-                if (valid) {
-                    // 32-byte stores: every lane writes whole sectors of its own row
+                if (!p.wide_rows) {
+                    float* orow = (p.ws.row_dst ? p.ws.row_dst[srow] : p.ws.pair_out + srow * p.hidden) + inf.tile * PF_N + sub * 64;
+                    if (valid) {
+                        // 32-byte stores: every lane writes whole sectors of its own row
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+#pragma unroll
+                            for (int i = 0; i < 16; i += 8)
+                                asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                                             ::"l"(orow + c * 16 + i),
+                                               "f"(scale * __uint_as_float(yr[c][i])), "f"(scale * __uint_as_float(yr[c][i + 1])),
+                                               "f"(scale * __uint_as_float(yr[c][i + 2])), "f"(scale * __uint_as_float(yr[c][i + 3])),
+                                               "f"(scale * __uint_as_float(yr[c][i + 4])), "f"(scale * __uint_as_float(yr[c][i + 5])),
+                                               "f"(scale * __uint_as_float(yr[c][i + 6])), "f"(scale * __uint_as_float(yr[c][i + 7]))
+                                             : "memory");
+                    }
+                } else {
+                    // Expert parallelism: the rows go to their owners' memory, most of them over NVLink, where a
+                    // 32-byte store per lane makes 32-byte packets.  The four lanes of a group exchange their rows'
+                    // 32-byte pieces (a 4 x 4 transpose of 16-float blocks, two shuffle stages) so that every store
+                    // instruction writes 128 contiguous bytes of one row per group: lane i of the group ends up with
+                    // pieces i and 4 + i (of the row's eight) of all four rows.
+                    float d[64];
 #pragma unroll
                     for (int c = 0; c < 4; ++c)
 #pragma unroll
-                        for (int i = 0; i < 16; i += 8)
+                        for (int i = 0; i < 16; ++i) d[c * 16 + i] = scale * __uint_as_float(yr[c][i]);
+                    const int li = lane & 3;
+                    // block j (j = 0..3) of a lane = floats [8j, 8j + 8) and [32 + 8j, 32 + 8j + 8)
+#pragma unroll
+                    for (int bit = 1; bit <= 2; bit <<= 1) {
+                        const bool up = (li & bit) != 0;
+#pragma unroll
+                        for (int j0 = 0; j0 < 4; ++j0) {
+                            if (j0 & bit) continue;
+                            const int j1 = j0 | bit;            // lanes with the bit clear pass block j1 and keep j0, the others the reverse
+#pragma unroll
+                            for (int f = 0; f < 16; ++f) {
+                                const int a0 = (f < 8) ? 8 * j0 + f : 32 + 8 * j0 + (f - 8);
+                                const int a1 = (f < 8) ? 8 * j1 + f : 32 + 8 * j1 + (f - 8);
+                                const float send = up ? d[a0] : d[a1];
+                                const float recv = __shfl_xor_sync(0xffffffffu, send, bit);
+                                if (up) d[a0] = recv; else d[a1] = recv;
+                            }
+                        }
+                    }
+                    // block r now holds pieces li and 4 + li of row (lane & ~3) + r
+                    const int t0 = quad * 32 + (lane & ~3);
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        if (t0 + r >= inf.ntok) continue;
+                        float* orow = p.ws.row_dst[(size_t)inf.slot0 + t0 + r] + inf.tile * PF_N + sub * 64;
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int a = h ? 32 + 8 * r : 8 * r;
                             asm volatile("st.global.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
-                                         ::"l"(orow + c * 16 + i),
-                                           "f"(scale * __uint_as_float(yr[c][i])), "f"(scale * __uint_as_float(yr[c][i + 1])),
-                                           "f"(scale * __uint_as_float(yr[c][i + 2])), "f"(scale * __uint_as_float(yr[c][i + 3])),
-                                           "f"(scale * __uint_as_float(yr[c][i + 4])), "f"(scale * __uint_as_float(yr[c][i + 5])),
-                                           "f"(scale * __uint_as_float(yr[c][i + 6])), "f"(scale * __uint_as_float(yr[c][i + 7]))
+                                         ::"l"(orow + (4 * h + li) * 8),
+                                           "f"(d[a]), "f"(d[a + 1]), "f"(d[a + 2]), "f"(d[a + 3]),
+                                           "f"(d[a + 4]), "f"(d[a + 5]), "f"(d[a + 6]), "f"(d[a + 7])
                                          : "memory");
+                        }
+                    }
                 }
                 pe_st += prof_clock() - q1;
             }
@@ -372,6 +421,7 @@ static int launch_pf(const vmoe_shape& s, const WeightSet& routed, const WeightS
     p.ws = ws; p.K = K; p.N = s.inter; p.hidden = s.hidden; p.E = s.num_experts;
     p.tiles = GU ? s.inter / TC_ROWS : s.hidden / PF_N;
     p.queue = GU ? CNT_QUEUE1 : CNT_QUEUE2;
+    p.wide_rows = (!GU && ws.row_dst && tuning("VMOE_EP_WIDE_STORES", 1)) ? 1 : 0;
     const size_t smem = (size_t)Cfg::STAGES * Cfg::STAGE_BYTES + sizeof(TcShared) + 1024;
     static bool attr_set[64] = {false};
     int dev = 0;
