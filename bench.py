@@ -647,7 +647,9 @@ def run_prefill(args, dev):
                        "tokens": M, "zipf_s": args.zipf,
                        "hidden": cfg.hidden, "inter": cfg.inter, "experts": cfg.num_experts, "topk": cfg.topk, "shared_experts": 1},
             "tokens_per_s": c["tokens_per_s"],
-            "roofline": {"bound": "tensor", "kernel": "pf_kernel<1> (gate_up, tcgen05, 128-token x 256-row items)",
+            "roofline": {"bound": "tensor", "kernel": ("pair_kernel<1> (gate_up, tcgen05 cta_group::2, 256-token x 256-row items on CTA pairs)"
+                                                        if os.environ.get("VMOE_PF_PAIR", "0") not in ("", "0")
+                                                        else "pf_kernel<1> (gate_up, tcgen05, 128-token x 256-row items)"),
                          "achieved": c["gate_up_tflops"], "peak": NOMINAL_FP4_TFLOPS,
                          "peak_source": "nominal dense FP4 (MEASURED_PEAKS.json holds no FP4 figure)", "unit": "TFLOP/s",
                          "frac": c["gate_up_tflops"] / NOMINAL_FP4_TFLOPS, "traffic": None,
