@@ -23,11 +23,12 @@ def main():
     shared = ops.MoEWeights(*[t.cuda() for t in layer["shared"]]).prepare()
     first, per = ep.expert_partition(cfg.num_experts, world, rank)
     mine = ops.MoEWeights(*[t[first:first + per].contiguous().cuda() for t in layer["routed"]]).prepare()
-    max_tok = 40
+    max_tok = 96
     moe = ep.ExpertParallelMoE(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, mine, shared, max_local_tokens=max_tok)
     ws = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, max_tok, has_shared=True, path=2))
     ok = True
-    for it, M in enumerate([40, 7 + rank, 0 if rank == 0 else 3, 33]):     # ragged and empty batches
+    # ragged and empty batches; 96 tokens take the token-major kernels at every world size
+    for it, M in enumerate([96, 40, 7 + rank, 0 if rank == 0 else 3, 33]):
         hidden, logits = synth.make_inputs(cfg, max(M, 1), seed=100 * it + rank)
         hidden, logits = hidden[:M].cuda().contiguous(), logits[:M].cuda().contiguous()
         out = moe.forward(hidden, logits)

@@ -23,10 +23,12 @@ def test_single_rank_matches_fused_layer():
     layer = synth.make_layer(cfg, seed=5)
     routed = ops.MoEWeights(*[t.cuda() for t in layer["routed"]]).prepare()
     shared = ops.MoEWeights(*[t.cuda() for t in layer["shared"]]).prepare()
-    moe = ep.ExpertParallelMoE(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, routed, shared, max_local_tokens=48)
-    ws = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, 48, has_shared=True, path=2))
+    moe = ep.ExpertParallelMoE(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, routed, shared, max_local_tokens=301)
+    ws = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, 301, has_shared=True, path=2))
     try:
-        for M in (48, 5, 0, 17):                       # several calls: epochs advance, slabs are reused
+        # several calls: epochs advance, slabs are reused; 301 and 48 tokens take the token-major kernels (several units
+        # per expert, unit sizes that are no multiple of four), the others the weights-as-rows kernel
+        for M in (301, 48, 5, 0, 17):
             hidden, logits = synth.make_inputs(cfg, max(M, 1), seed=M)
             hidden, logits = hidden[:M].cuda().contiguous(), logits[:M].cuda().contiguous()
             out = moe.forward(hidden, logits)
