@@ -125,6 +125,7 @@ ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restric
     __shared__ int32_t s_before[EP_MAX_RANKS];      // routed pairs of earlier tokens per destination
     __shared__ int32_t s_total[EP_MAX_RANKS];       // routed pairs of all tokens per destination
     __shared__ int32_t s_dst[MAX_TOPK + 1], s_pos[MAX_TOPK + 1];
+    __shared__ __align__(16) uint8_t s_sf[256];        // block scales of one chunk of 256 blocks
     __shared__ int s_last;
     if (threadIdx.x == 0) EP_MARK_MIN(ep, 20);
     pdl_begin();
@@ -162,26 +163,40 @@ ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restric
     __syncthreads();
     if (m < M) {
         const int bpr = K / SF_BLOCK;
-        for (int kb = tid; kb < bpr; kb += blockDim.x) {
-            const uint4* src = reinterpret_cast<const uint4*>(x + ((size_t)m * bpr + kb) * SF_BLOCK);
-            uint4 raw[2] = {src[0], src[1]};
-            float v[SF_BLOCK]; uint32_t lo, hi; uint8_t sb;
-            quantize_block16(reinterpret_cast<const __nv_bfloat16*>(raw), v, lo, hi, sb);
-            for (int j = 0; j <= T; ++j) {
-                const int d = s_dst[j], pos = s_pos[j];
-                if (d < 0 || pos >= ep.capacity) continue;
-                const int p = (j < T) ? m * T + j : M * T + m;
-                uint8_t* slab = ep.slab[d];
-                const size_t row = (size_t)ep.rank * ep.capacity + pos;
-                reinterpret_cast<uint2*>(slab + ep.L.recv_q + row * (K / 2))[kb] = make_uint2(lo, hi);
-                (slab + ep.L.recv_sf + row * (K / 16))[kb] = sb;
-                if (kb == 0) {
-                    const int id = (j < T) ? topk_ids[p] : 0;
-                    const int le = (j < T) ? id - (id / ep.e_local) * ep.e_local : ep.e_local;     // shared expert = local id E_local
-                    const float w = (j < T) ? topk_w[p] : 1.0f;
-                    reinterpret_cast<int4*>(slab + ep.L.recv_meta)[row] = make_int4(le, p, __float_as_int(w), 0);
+        for (int kb0 = 0; kb0 < bpr; kb0 += blockDim.x) {           // uniform trip count: the CTA meets at barriers inside
+            const int kb = kb0 + tid;
+            if (kb < bpr) {
+                const uint4* src = reinterpret_cast<const uint4*>(x + ((size_t)m * bpr + kb) * SF_BLOCK);
+                uint4 raw[2] = {src[0], src[1]};
+                float v[SF_BLOCK]; uint32_t lo, hi; uint8_t sb;
+                quantize_block16(reinterpret_cast<const __nv_bfloat16*>(raw), v, lo, hi, sb);
+                s_sf[tid] = sb;
+                for (int j = 0; j <= T; ++j) {
+                    const int d = s_dst[j], pos = s_pos[j];
+                    if (d < 0 || pos >= ep.capacity) continue;
+                    const int p = (j < T) ? m * T + j : M * T + m;
+                    uint8_t* slab = ep.slab[d];
+                    const size_t row = (size_t)ep.rank * ep.capacity + pos;
+                    reinterpret_cast<uint2*>(slab + ep.L.recv_q + row * (K / 2))[kb] = make_uint2(lo, hi);
+                    if (kb == 0) {
+                        const int id = (j < T) ? topk_ids[p] : 0;
+                        const int le = (j < T) ? id - (id / ep.e_local) * ep.e_local : ep.e_local;     // shared expert = local id E_local
+                        const float w = (j < T) ? topk_w[p] : 1.0f;
+                        reinterpret_cast<int4*>(slab + ep.L.recv_meta)[row] = make_int4(le, p, __float_as_int(w), 0);
+                    }
                 }
             }
+            __syncthreads();
+            // the chunk's block scales leave as 16-byte stores (K is a multiple of 256: 16 scales never straddle a chunk)
+            const int parts = min((int)blockDim.x, bpr - kb0) / 16;
+            for (int i = tid; i < (T + 1) * parts; i += blockDim.x) {
+                const int j = i / parts, part = i - j * parts;
+                const int d = s_dst[j], pos = s_pos[j];
+                if (d < 0 || pos >= ep.capacity) continue;
+                const size_t row = (size_t)ep.rank * ep.capacity + pos;
+                reinterpret_cast<uint4*>(ep.slab[d] + ep.L.recv_sf + row * (K / 16) + kb0)[part] = reinterpret_cast<const uint4*>(s_sf)[part];
+            }
+            __syncthreads();
         }
     }
     // Last CTA to finish publishes the counts and the call flag on every peer.  The ticket orders memory at GPU scope
