@@ -304,13 +304,15 @@ class DecodeBench:
         self.path = 2 if path == "tc" else 1
         self.peak, self.peak_kind = measured_peak_gbs()
 
-    def case(self, M, steps, warmup, rotate, seed0=0, zipf=None, stage_steps=None):
+    def case(self, M, steps, warmup, rotate, seed0=0, zipf=None, stage_steps=None, mtp_corr=0.0):
         """Times the layer (and its two GEMM kernels alone) at batch M.  Returns a dict of figures."""
         import numpy as np
         import torch
         vm, ops, cfg = self.vm, self.ops, self.cfg
         ws = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, max(M, 1), has_shared=True, path=self.path), self.dev)
-        sets = [self.synth.make_inputs(cfg, M, seed=seed0 + i, device=self.dev, zipf_s=zipf) for i in range(max(rotate, 1))]
+        group = 6 if (mtp_corr > 0 and M % 6 == 0) else None      # 1 verified + 5 draft positions per sequence
+        sets = [self.synth.make_inputs(cfg, M, seed=seed0 + i, device=self.dev, zipf_s=zipf, mtp_group=group, mtp_corr=mtp_corr if group else 0.0)
+                for i in range(max(rotate, 1))]
         out = torch.empty(M, cfg.hidden, dtype=torch.bfloat16, device=self.dev)
 
         def step(i):
@@ -484,7 +486,7 @@ def run_ours(args):
     b = DecodeBench(dev, args.path)
     cfg, routed, shared = b.cfg, b.routed, b.shared
     M = args.tokens
-    main = b.case(M, args.steps, args.warmup, args.rotate, seed0=0, zipf=args.zipf)
+    main = b.case(M, args.steps, args.warmup, args.rotate, seed0=0, zipf=args.zipf, mtp_corr=args.mtp_corr)
     parity = b.parity_rows(main, [0, M // 2, M - 1] if M >= 3 else list(range(M)))
     if b.path == 2:
         kname, kb, kus, kfrac = ("tc_fused_kernel: gate_up + down items of the step in one launch (tcgen05)",
@@ -596,7 +598,9 @@ def run_ours(args):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": main["ms_per_step"], "repeats": main["repeats"],
         "timed_seconds": main["repeats"] * ms * 1e-3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4(w4a4)->f32",
-        "data": "synthetic", "config": dict(workload_config(M, 1), kernel_path=args.path),
+        "data": "synthetic", "config": dict(workload_config(M, 1), kernel_path=args.path,
+                                            **({"mtp": {"positions_per_sequence": 6, "logit_correlation": args.mtp_corr}}
+                                               if args.mtp_corr > 0 and M % 6 == 0 else {})),
         "launch": main["launch"],
         "roofline": roof, "clocks": main["clocks"],
         "e2e": {"value": M * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
