@@ -6,8 +6,8 @@
 // cta_group::2, issued by the even CTA, multiplies both CTAs' token tiles with both halves of the weight
 // tile and accumulates into each CTA's own tensor memory (128 lanes x 256 columns).  A weight byte therefore
 // crosses L2 -> shared memory once per 256 tokens instead of once per 128, and a CTA's stage shrinks from
-// 54 KB to 38 KB for the same MMA work: the single-CTA kernel is bound by exactly that traffic (shared-memory
-// fill + operand reads of 200 bytes per clock at full tensor rate against 128 available).
+// 54 KB to 38 KB for the same MMA work: the single-CTA kernel is bound by that traffic (at 64 bytes per clock an
+// SM takes 864 cycles to ingest a 54 KB stage whose four MMAs need 540).
 //
 //   pair_kernel<1> gate_up: even CTA loads the 128 gate rows, odd CTA the matching 128 up rows.
 //   pair_kernel<0> down:    even CTA loads rows [0, 128) of the 256-row w2 tile, odd CTA rows [128, 256).
