@@ -692,7 +692,7 @@ def run_prefill(args, dev):
                        "hidden": cfg.hidden, "inter": cfg.inter, "experts": cfg.num_experts, "topk": cfg.topk, "shared_experts": 1},
             "tokens_per_s": c["tokens_per_s"],
             "roofline": {"bound": "tensor", "kernel": ("pair_kernel<1> (gate_up, tcgen05 cta_group::2, 256-token x 256-row items on CTA pairs)"
-                                                        if os.environ.get("VMOE_PF_PAIR", "0") not in ("", "0")
+                                                        if int(os.environ.get("VMOE_PF_PAIR", "0") or 0) & 1
                                                         else "pf_kernel<1> (gate_up, tcgen05, 128-token x 256-row items)"),
                          "achieved": c["gate_up_tflops"], "peak": fp4_peak,
                          "peak_source": ("measured in this run: dense NVFP4 GEMM 8192^3 of the vendor library (torch._scaled_mm); "

@@ -767,19 +767,18 @@ int launch_tc(const vmoe_shape& s, const WeightSet& routed, const WeightSet& sha
     if (M == 0 && !signal) return VMOE_OK;
     const int cap = unit_cap > 0 ? unit_cap : tc_unit_cap(s, M);
     if (cap == TC_UNIT_TOK_PREFILL) {
-        // VMOE_PF_PAIR=1 runs the projections on CTA pairs (cta_group::2, vmoe_tc_pair.cu).  Off by default: measured on
-        // the 8192-token layer under the power cap the pairs tie on gate_up (655 against 660 us) and lose on the down
-        // projection (754 against 638 us: short items, and the single accumulator is handed over across two CTAs).
+        // VMOE_PF_PAIR: bit 0 runs the gate_up projection on CTA pairs (cta_group::2, vmoe_tc_pair.cu), bit 1 the down
+        // projection.
         int rc = VMOE_OK;
-        const bool pairs = tuning("VMOE_PF_PAIR", 0) != 0;
+        const int pairs = tuning("VMOE_PF_PAIR", 0);
         if (phases & TC_PHASE_GATE_UP) {
             bool done = false;
-            if (pairs) rc = launch_pair_gate_up(s, routed, shared, prep, M, ws, st, b_rows, &done);
+            if (pairs & 1) rc = launch_pair_gate_up(s, routed, shared, prep, M, ws, st, b_rows, &done);
             if (!rc && !done) rc = launch_pf_gate_up(s, routed, shared, prep, M, ws, st, b_rows);
         }
         if (!rc && (phases & TC_PHASE_DOWN)) {
             bool done = false;
-            if (pairs) rc = launch_pair_down(s, routed, shared, prep, M, ws, st, b_rows, &done);
+            if (pairs & 2) rc = launch_pair_down(s, routed, shared, prep, M, ws, st, b_rows, &done);
             if (!rc && !done) rc = launch_pf_down(s, routed, shared, prep, M, ws, st, b_rows);
         }
         return rc;

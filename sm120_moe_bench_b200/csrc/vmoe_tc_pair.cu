@@ -77,25 +77,14 @@ __device__ __forceinline__ uint32_t cluster_addr(uint32_t addr, uint32_t rank) {
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
     return r;
 }
+// Arrival on a barrier of either CTA.  Default semantics (release at CTA scope): what the barrier orders here is
+// tensor-memory traffic, fenced by tcgen05.fence, not global stores -- a cluster-scope release would make every
+// arrival wait for the warp's earlier global stores.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n selp.b32 %0, 1, 0, p;\n}\n"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait on a barrier that threads of the other CTA arrive on.
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    const unsigned long long t0 = global_timer_ns();
-    for (uint32_t i = 1;; ++i) {
-        if (mbar_try_wait_cluster(bar, parity)) return true;
-        if ((i & 63u) == 0 && global_timer_ns() - t0 > MBAR_WAIT_LIMIT_NS) return false;
-    }
-}
+// Bounded wait on a barrier that the other CTA's threads, copies or commits arrive on.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity) { return mbar_wait(bar, parity); }
 // Tensor copy into this CTA's shared memory whose bytes are counted on a barrier of either CTA of the pair.
 __device__ __forceinline__ void tma2_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint32_t bar_cluster_addr) {
     asm volatile(
@@ -103,8 +92,11 @@ __device__ __forceinline__ void tma2_load_2d(void* dst, const CUtensorMap* map, 
         ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(bar_cluster_addr) : "memory");
 }
 // tcgen05 forms of the CTA pair: issued by one thread of the even CTA, carried out in both
-__device__ __forceinline__ void tc2_commit(uint32_t bar_cluster_addr) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
+// One arrival on the barrier at this address in BOTH CTAs of the pair once the MMAs issued so far have completed.
+__device__ __forceinline__ void tc2_commit_both(uint32_t bar_addr) {
+    const uint16_t both = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar_addr), "h"(both) : "memory");
 }
 __device__ __forceinline__ void tc2_cp_sf(uint32_t taddr, uint64_t sdesc) {
     asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
@@ -271,13 +263,12 @@ pair_kernel(const __grid_constant__ P2Params p) {
         bool ok = true;
         if (rank == 0) {
             // ------------------------------------------------------------- MMA issuer of the pair (warp-uniform
-            // loop, one elected lane issues).  Each completion is committed twice: to this CTA's barrier and to
-            // the barrier at the same place in the odd CTA.
+            // loop, one elected lane issues).  Each completion is committed to the barrier at the same place in
+            // both CTAs.
             uint32_t it = 0;
             const uint32_t smem16 = smem_u32(smem) >> 4;
             const uint32_t idesc = idesc_nvf4_pair(P2_N);
-            const uint32_t empty_here = smem_u32(&sh->empty[0]), empty_there = cluster_addr(empty_here, 1);
-            const uint32_t tfull_here = smem_u32(&sh->tmem_full), tfull_there = cluster_addr(tfull_here, 1);
+            const uint32_t empty_here = smem_u32(&sh->empty[0]), tfull_here = smem_u32(&sh->tmem_full);
             long long pw_full = 0, pw_peer = 0, pw_acc = 0, p_issue = 0;
             const long long t_begin = prof_clock();
             for (long long item = pair_id; item < total && ok; item += npairs_grid) {
@@ -316,12 +307,12 @@ pair_kernel(const __grid_constant__ P2Params p) {
                         const uint32_t acc = (kb > 0 || j > 0) ? 1u : 0u;
                         if (leader) tc2_mma(tmem, da, db, idesc, sfcol + j * 4, sfcol + 16 + j * 8, acc);
                     }
-                    if (leader) { tc2_commit(empty_here + slot * 8); tc2_commit(empty_there + slot * 8); }
+                    if (leader) tc2_commit_both(empty_here + slot * 8);
                     p_issue += prof_clock() - c3;
                     ++g;
                 }
                 if (!ok) break;
-                if (leader) { tc2_commit(tfull_here); tc2_commit(tfull_there); }
+                if (leader) tc2_commit_both(tfull_here);
                 ++it;
             }
             if (leader) {

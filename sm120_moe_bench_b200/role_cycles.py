@@ -49,7 +49,7 @@ def main():
     hidden, logits = synth.make_inputs(cfg, M, seed=1, device="cuda")
     sms = torch.cuda.get_device_properties(0).multi_processor_count
     for pair in (0, 1):
-        os.environ["VMOE_PF_PAIR"] = str(pair)
+        os.environ["VMOE_PF_PAIR"] = "3" if pair else "0"          # bit 0: gate_up on pairs, bit 1: down on pairs
         vm.fused_moe(hidden, routed, ws, router_logits=logits, shared=shared)
         torch.cuda.synchronize()
         ids = ws.view("topk_ids", torch.int32, M * cfg.topk).view(M, cfg.topk).clone()

@@ -295,7 +295,7 @@ def test_config_large_prefill_oracle_rows(vm, large_layer, zipf):
     pytest.param((1024, 512, 16, 4, 2048, 1.2), id="16experts-zipf"),     # hot experts with many pairs, cold ones with one unit
 ])
 def test_cta_pair_kernels_match_single_cta_kernels(vm, monkeypatch, case):
-    """The token-major projections on CTA pairs (tcgen05 cta_group::2, opted into with VMOE_PF_PAIR=1) against the
+    """The token-major projections on CTA pairs (tcgen05 cta_group::2, opted into with VMOE_PF_PAIR) against the
     single-CTA kernels on the same inputs: the same products accumulated in the same order, so bit for bit; three
     rows of the pair run against the oracle as well."""
     from sm120_moe_bench_b200 import synth
@@ -306,17 +306,17 @@ def test_cta_pair_kernels_match_single_cta_kernels(vm, monkeypatch, case):
     ws = vm.Workspace(vm.MoEShape(K, N, E, T, M, has_shared=True, path=TC))
     hidden, logits = synth.make_inputs(cfg, M, seed=9, device="cuda", zipf_s=zipf)
     outs = {}
-    for pair in ("0", "1"):
+    for pair in ("0", "3"):                                  # bit 0: gate_up on pairs, bit 1: down on pairs
         monkeypatch.setenv("VMOE_PF_PAIR", pair)
         outs[pair] = vm.fused_moe(hidden, routed, ws, router_logits=logits, shared=shared).clone()
         torch.cuda.synchronize()
         assert ws.status() == 0
-    assert torch.equal(outs["0"], outs["1"])
+    assert torch.equal(outs["0"], outs["3"])
     ids_dev = ws.view("topk_ids", torch.int32, M * T).view(M, T).clone()
     w_dev = ws.view("topk_weights", torch.float32, M * T).view(M, T).clone()
     rows = [0, M // 2 + 1, M - 1]
     ref = _oracle_rows(cfg, layer, hidden, ids_dev, w_dev, rows)
-    util.assert_output_close(outs["1"][rows].float().cpu().numpy(), ref)
+    util.assert_output_close(outs["3"][rows].float().cpu().numpy(), ref)
 
 
 def test_wide_shape_on_the_tensor_core_path(vm):
