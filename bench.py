@@ -261,27 +261,35 @@ def run_reference_arm(args):
     value = sample_tokens * len(times) / total
     sample = (f"each step = {sample_tokens} token of the {args.tokens}-token decode batch "
               f"({problem[5]} routed experts + 1 shared), through {what}")
-    config = workload_config(args.tokens, args.gpus)
-    config["tokens_timed_per_step"] = sample_tokens
+    config = workload_config(args.tokens, args.gpus, args.zipf, args.mtp_corr)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": len(times), "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4(w4a4)->f32",
         "data": "synthetic",
-        "config": config,
+        "config": config, "tokens_timed_per_step": sample_tokens,
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
-def workload_config(tokens, gpus):
-    return {"workload": "single-GPU decode MoE layer, large-MoE shape (BASELINE config 2)" if gpus == 1 else
-            f"decode MoE layer, large-MoE shape (BASELINE config 2 layer), expert parallel over {gpus} GPUs",
-            "hidden": 4096, "inter": 1024, "experts": 512, "topk": 10, "shared_experts": 1,
-            "tokens_per_gpu": tokens, "weights": "NVFP4 (E2M1 + E4M3 per-16 + fp32 global), N(0,0.02), seed 0",
-            "parallelism": "single GPU" if gpus == 1 else f"expert parallel over {gpus} GPUs",
-            "l2": "inputs larger than L2: every step streams > 126 MB of expert weights; input sets rotate"}
+def workload_config(tokens, gpus, zipf=None, mtp_corr=0.0):
+    """What names the workload -- the same dict from both arms (this build and ``--impl reference``); what names an
+    implementation (kernel path, measured reuse) is kept out of it."""
+    per = 512 // max(gpus, 1)
+    c = {"workload": "single-GPU decode MoE layer, large-MoE shape (BASELINE config 2)" if gpus == 1 else
+                     f"decode MoE layer, large-MoE shape (BASELINE config 2 layer), expert parallel over {gpus} GPUs",
+         "hidden": 4096, "inter": 1024, "experts": 512, "topk": 10, "shared_experts": 1,
+         "tokens_per_gpu": tokens, "weights": "NVFP4 (E2M1 + E4M3 per-16 + fp32 global), N(0,0.02), seed 0",
+         "parallelism": "single GPU" if gpus == 1 else
+                        f"expert parallel over {gpus} GPUs ({per} routed experts per GPU, shared expert replicated)",
+         "l2": "inputs larger than L2: every step streams > 126 MB of expert weights; input sets rotate"}
+    if zipf is not None:
+        c["zipf_s"] = zipf
+    if mtp_corr > 0 and tokens % 6 == 0:
+        c["mtp"] = {"positions_per_sequence": 6, "logit_correlation": mtp_corr}
+    return c
 
 
 # ---------------------------------------------------------------------------------------------
@@ -598,9 +606,7 @@ def run_ours(args):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": main["ms_per_step"], "repeats": main["repeats"],
         "timed_seconds": main["repeats"] * ms * 1e-3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4(w4a4)->f32",
-        "data": "synthetic", "config": dict(workload_config(M, 1), kernel_path=args.path,
-                                            **({"mtp": {"positions_per_sequence": 6, "logit_correlation": args.mtp_corr}}
-                                               if args.mtp_corr > 0 and M % 6 == 0 else {})),
+        "data": "synthetic", "config": workload_config(M, 1, args.zipf, args.mtp_corr), "kernel_path": args.path,
         "launch": main["launch"],
         "roofline": roof, "clocks": main["clocks"],
         "e2e": {"value": M * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
@@ -1000,18 +1006,14 @@ def run_expert_parallel(args, world, rank, local, dev):
         peak, peak_kind = measured_peak_gbs()
         step_s = ms / args.steps * 1e-3
         tokens_total = M * world * args.steps
-        config = workload_config(M, world)
-        config["parallelism"] = f"expert parallel over {world} GPUs ({per} routed experts per GPU, shared expert replicated), dispatch/combine as NVLink peer-memory kernels"
-        config["kernel_path"] = "tc"
-        config["zipf_s"] = args.zipf
-        if group:
-            config["mtp"] = {"positions_per_sequence": group, "logit_correlation": args.mtp_corr,
-                             "adjacent_expert_reuse": float(np.mean(reuse))}
+        config = workload_config(M, world, args.zipf, args.mtp_corr)
         line = {
             "metric": METRIC, "value": tokens_total / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, len(sets), 3), "ms_per_step": ms / args.steps, "repeats": len(reps),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "nvfp4(w4a4)->f32",
-            "data": "synthetic", "config": config,
+            "data": "synthetic", "config": config, "kernel_path": "tc",
+            "exchange": "dispatch/combine as NVLink peer-memory kernels (no NCCL on the data path)",
+            "adjacent_expert_reuse": float(np.mean(reuse)) if group else None,
             "roofline": {"bound": "hbm", "kernel": "expert-parallel layer (all kernels of one step, per GPU)",
                          "achieved": total_bytes / world / step_s / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": total_bytes / world / step_s / 1e9 / peak, "traffic": None,
