@@ -137,6 +137,7 @@ int resolve_workspace(const vmoe_shape* s, void* base, Workspace* ws, int tc_uni
     ws->token_expect    = reinterpret_cast<int32_t*>(b + L.token_expect);
     ws->tc_unit_capacity = tc_units_override > 0 ? tc_units_override : max_tc_units(s);
     ws->small_tokens    = small_batch_tokens(s);
+    ws->pair_rows_bf16  = 0;
 #ifdef VMOE_TIMELINE
     ws->timeline        = g_vmoe_timeline;
 #else
@@ -407,6 +408,10 @@ int vmoe_forward_ex(const vmoe_shape* shape, const vmoe_weights* routed, const v
         const bool in_kernel = cap == TC_UNIT_TOK_SMALL && tuning("VMOE_FUSE_QUANT", 1) != 0 && tuning("VMOE_FUSE_PHASES", 1) != 0;
         if (!in_kernel && (rc = launch_permute_quantize(*shape, x, topk_ids, expert_map, M, ws, st, pre_q, pre_sf))) return rc;
         bool combined = false;
+        // VMOE_PAIR_ROWS_BF16=1 (large batches, plain combine only): the down projection stores its per-pair rows as
+        // bf16 and the combine sums them in fp32 in the same fixed order -- half the bytes of that round trip for a
+        // second rounding per pair.  Off by default: the default path keeps fp32 rows.
+        if (cap == TC_UNIT_TOK_PREFILL && !norm_w && tuning("VMOE_PAIR_ROWS_BF16", 0) != 0) ws.pair_rows_bf16 = 1;
         // with the next layer's RMSNorm behind it the combine runs as its own row-wide kernel
         if ((rc = launch_tc(*shape, r, sh, prep, M, ws, st, TC_PHASE_GATE_UP | TC_PHASE_DOWN, norm_w ? nullptr : out, residual, &combined,
                             -1, -1, nullptr, in_kernel ? &quant : nullptr))) return rc;

@@ -363,7 +363,17 @@ __device__ __forceinline__ void ep_permute_blocks(const TcEpPermute& e, const lo
 }
 // out[m, 4c .. 4c+3] = bf16( sum_j pair_out[slot(m, j), :]  (ascending j, fp32)  + shared row ) [+ residual],
 // element i = m * (K / 4) + c.  BATCHED: slot numbers and then all rows requested at once (small launches).
-template <bool BATCHED>
+// Four consecutive values of one per-pair row: fp32 as stored, or bf16 widened (ROWS16).
+template <bool ROWS16>
+__device__ __forceinline__ float4 pair_row_load(const float* pair_out, size_t slot, int K, int c) {
+    if (ROWS16) {
+        const uint2 u = __ldcg(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(pair_out) + slot * K) + c);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+        return make_float4(__bfloat162float(a.x), __bfloat162float(a.y), __bfloat162float(b.x), __bfloat162float(b.y));
+    }
+    return __ldcg(reinterpret_cast<const float4*>(pair_out + slot * K) + c);       // L2: rows written by other SMs
+}
+template <bool BATCHED, bool ROWS16 = false>
 __device__ __forceinline__ uint2 combine_value(long long i, const float* pair_out, const int32_t* pair_slot,
                                                const int32_t* expert_offsets, int K, int T, int E, int has_shared,
                                                const __nv_bfloat16* residual) {
@@ -378,7 +388,7 @@ __device__ __forceinline__ uint2 combine_value(long long i, const float* pair_ou
         float4 v[MAX_TOPK + 1];
 #pragma unroll
         for (int j = 0; j <= MAX_TOPK; ++j)
-            if (slot[j] >= 0) v[j] = __ldcg(reinterpret_cast<const float4*>(pair_out + (size_t)slot[j] * K) + c);   // L2: rows written by other SMs
+            if (slot[j] >= 0) v[j] = pair_row_load<ROWS16>(pair_out, (size_t)slot[j], K, c);
 #pragma unroll
         for (int j = 0; j <= MAX_TOPK; ++j)        // ascending pair order, shared expert last
             if (slot[j] >= 0) { acc.x += v[j].x; acc.y += v[j].y; acc.z += v[j].z; acc.w += v[j].w; }
@@ -386,13 +396,13 @@ __device__ __forceinline__ uint2 combine_value(long long i, const float* pair_ou
         for (int j = 0; j < T; ++j) {
             const int slot = pair_slot[m * T + j];
             if (slot >= 0) {
-                const float4 v = __ldcg(reinterpret_cast<const float4*>(pair_out + (size_t)slot * K) + c);
+                const float4 v = pair_row_load<ROWS16>(pair_out, (size_t)slot, K, c);
                 acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
             }
         }
         if (has_shared) {
             const int slot = expert_offsets[E] + m;
-            const float4 v = __ldcg(reinterpret_cast<const float4*>(pair_out + (size_t)slot * K) + c);
+            const float4 v = pair_row_load<ROWS16>(pair_out, (size_t)slot, K, c);
             acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
         }
     }
@@ -407,12 +417,12 @@ __device__ __forceinline__ uint2 combine_value(long long i, const float* pair_ou
     uint2 o; o.x = *reinterpret_cast<uint32_t*>(&lo); o.y = *reinterpret_cast<uint32_t*>(&hi);
     return o;                       // four bf16 values
 }
-template <bool BATCHED>
+template <bool BATCHED, bool ROWS16 = false>
 __device__ __forceinline__ void combine_element(long long i, const float* pair_out, const int32_t* pair_slot,
                                                 const int32_t* expert_offsets, int M, int K, int T, int E, int has_shared,
                                                 const __nv_bfloat16* residual, __nv_bfloat16* out) {
     (void)M;
-    reinterpret_cast<uint2*>(out)[i] = combine_value<BATCHED>(i, pair_out, pair_slot, expert_offsets, K, T, E, has_shared, residual);
+    reinterpret_cast<uint2*>(out)[i] = combine_value<BATCHED, ROWS16>(i, pair_out, pair_slot, expert_offsets, K, T, E, has_shared, residual);
 }
 
 }  // namespace vmoe

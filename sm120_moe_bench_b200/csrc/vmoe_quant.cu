@@ -72,7 +72,7 @@ int launch_dequantize(const uint8_t* packed, const uint8_t* sf, const float* gs,
 // out[m, :] = bf16( sum_j pair_out[slot(m, j), :]  (ascending j, fp32)  + shared row )
 // one thread per 4 consecutive columns.  BATCHED (small launches, bound by load latency): the slot numbers and
 // then all rows of a token are requested at once; otherwise (large launches, bound by bandwidth) row by row.
-template <bool BATCHED>
+template <bool BATCHED, bool ROWS16>
 __global__ void __launch_bounds__(256)
 combine_kernel(const float* __restrict__ pair_out, const int32_t* __restrict__ pair_slot,
                const int32_t* __restrict__ expert_offsets, int M, int K, int T, int E, int has_shared,
@@ -80,7 +80,7 @@ combine_kernel(const float* __restrict__ pair_out, const int32_t* __restrict__ p
     pdl_begin();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (long long)M * (K / 4)) return;
-    combine_element<BATCHED>(i, pair_out, pair_slot, expert_offsets, M, K, T, E, has_shared, residual, out);
+    combine_element<BATCHED, ROWS16>(i, pair_out, pair_slot, expert_offsets, M, K, T, E, has_shared, residual, out);
 }
 
 int launch_combine(const vmoe_shape& s, int M, const Workspace& ws, __nv_bfloat16* out, cudaStream_t st,
@@ -88,11 +88,14 @@ int launch_combine(const vmoe_shape& s, int M, const Workspace& ws, __nv_bfloat1
     const long long n = (long long)M * (s.hidden / 4);
     if (n == 0) return VMOE_OK;
     const unsigned blocks = (unsigned)((n + 255) / 256);
-    if (blocks <= 1024)
-        launch_pdl(combine_kernel<true>, blocks, 256u, 0, st,
+    if (ws.pair_rows_bf16)
+        launch_pdl(combine_kernel<false, true>, blocks, 256u, 0, st,
+            ws.pair_out, ws.pair_slot, ws.expert_offsets, M, s.hidden, s.topk, s.num_experts, s.has_shared, residual, out);
+    else if (blocks <= 1024)
+        launch_pdl(combine_kernel<true, false>, blocks, 256u, 0, st,
             ws.pair_out, ws.pair_slot, ws.expert_offsets, M, s.hidden, s.topk, s.num_experts, s.has_shared, residual, out);
     else
-        launch_pdl(combine_kernel<false>, blocks, 256u, 0, st,
+        launch_pdl(combine_kernel<false, false>, blocks, 256u, 0, st,
             ws.pair_out, ws.pair_slot, ws.expert_offsets, M, s.hidden, s.topk, s.num_experts, s.has_shared, residual, out);
     return cuda_status(cudaGetLastError());
 }

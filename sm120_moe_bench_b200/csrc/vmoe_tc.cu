@@ -778,7 +778,7 @@ int launch_tc(const vmoe_shape& s, const WeightSet& routed, const WeightSet& sha
         }
         if (!rc && (phases & TC_PHASE_DOWN)) {
             bool done = false;
-            if (pairs & 2) rc = launch_pair_down(s, routed, shared, prep, M, ws, st, b_rows, &done);
+            if ((pairs & 2) && !ws.pair_rows_bf16) rc = launch_pair_down(s, routed, shared, prep, M, ws, st, b_rows, &done);
             if (!rc && !done) rc = launch_pf_down(s, routed, shared, prep, M, ws, st, b_rows);
         }
         return rc;

@@ -313,7 +313,29 @@ pf_kernel(const __grid_constant__ PfParams p) {
                 if (lane == 0) mbar_arrive(&sh->tmem_empty[0]);
                 const long long q1 = prof_clock();
                 pe_ld += q1 - c1;
-                if (!p.wide_rows) {
+                if (p.ws.pair_rows_bf16 && !p.ws.row_dst) {
+                    // opt-in: the row leaves as bf16 (64 values = four 32-byte stores), summed in fp32 by the combine
+                    __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.ws.pair_out) + srow * p.hidden + inf.tile * PF_N + sub * 64;
+                    if (valid) {
+#pragma unroll
+                        for (int c = 0; c < 4; c += 2) {
+                            uint32_t w[16];
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                const int cc = c + (i >> 3), e0 = (i & 7) * 2;
+                                const __nv_bfloat162 v = __floats2bfloat162_rn(scale * __uint_as_float(yr[cc][e0]), scale * __uint_as_float(yr[cc][e0 + 1]));
+                                w[i] = *reinterpret_cast<const uint32_t*>(&v);
+                            }
+#pragma unroll
+                            for (int h = 0; h < 2; ++h)
+                                asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                                             ::"l"(orow + c * 16 + h * 16),
+                                               "r"(w[h * 8]), "r"(w[h * 8 + 1]), "r"(w[h * 8 + 2]), "r"(w[h * 8 + 3]),
+                                               "r"(w[h * 8 + 4]), "r"(w[h * 8 + 5]), "r"(w[h * 8 + 6]), "r"(w[h * 8 + 7])
+                                             : "memory");
+                        }
+                    }
+                } else if (!p.wide_rows) {
                     float* orow = (p.ws.row_dst ? p.ws.row_dst[srow] : p.ws.pair_out + srow * p.hidden) + inf.tile * PF_N + sub * 64;
                     if (valid) {
                         // 32-byte stores: every lane writes whole sectors of its own row

@@ -319,6 +319,34 @@ def test_cta_pair_kernels_match_single_cta_kernels(vm, monkeypatch, case):
     util.assert_output_close(outs["3"][rows].float().cpu().numpy(), ref)
 
 
+def test_bf16_pair_rows_option_stays_within_its_stated_error(vm, monkeypatch):
+    """VMOE_PAIR_ROWS_BF16=1 (large batches): the down projection leaves its per-pair rows as bf16, the combine still
+    sums them in fp32 in the fixed order.  A second rounding per pair: not bit-exact, measured at 2.7e-3 relative L2 on
+    the 8192-token layer; here the bound the option is documented with (5e-3, cosine >= 0.9999) against the oracle, and
+    the default path on the same inputs within the ordinary tolerance."""
+    from sm120_moe_bench_b200 import synth
+    cfg = synth.LayerConfig("rows16", 1024, 512, 16, 4, True)
+    M = 2048
+    layer = synth.make_layer(cfg, seed=11, device="cuda")
+    routed, shared = _device_layer(vm, layer)
+    ws = vm.Workspace(vm.MoEShape(cfg.hidden, cfg.inter, cfg.num_experts, cfg.topk, M, has_shared=True, path=TC))
+    hidden, logits = synth.make_inputs(cfg, M, seed=12, device="cuda")
+    outs = {}
+    for flag in ("0", "1"):
+        monkeypatch.setenv("VMOE_PAIR_ROWS_BF16", flag)
+        outs[flag] = vm.fused_moe(hidden, routed, ws, router_logits=logits, shared=shared).clone()
+        torch.cuda.synchronize()
+        assert ws.status() == 0
+    ids_dev = ws.view("topk_ids", torch.int32, M * cfg.topk).view(M, cfg.topk).clone()
+    w_dev = ws.view("topk_weights", torch.float32, M * cfg.topk).view(M, cfg.topk).clone()
+    rows = [0, 5, M // 2 + 1, M - 1]
+    ref = _oracle_rows(cfg, layer, hidden, ids_dev, w_dev, rows)
+    util.assert_output_close(outs["0"][rows].float().cpu().numpy(), ref)
+    got = outs["1"][rows].float().cpu().numpy()
+    assert util.cosine(got, ref) >= 0.9999 and util.rel_l2(got, ref) <= 5e-3
+    assert not torch.equal(outs["0"], outs["1"])          # the option really took the other path
+
+
 def test_wide_shape_on_the_tensor_core_path(vm):
     """Hidden 7168, intermediate 2048 (beyond what the streaming GEMV kernels take): the tensor-core path has no
     such cap.  Four experts, top-2 + shared; decode (weights-as-rows kernel) and a 160-token batch (token-major)."""
