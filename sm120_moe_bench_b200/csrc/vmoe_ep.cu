@@ -9,7 +9,7 @@
 // pair, already quantised (2304 bytes at K = 4096), and each weighted output row crosses once
 // (fp32, so the owner's fixed-order sum is bit-identical to the single-GPU result).
 //
-// Per forward call on rank r (one stream, no host synchronisation, five launches; seven around the token-major kernels):
+// Per forward call on rank r (one stream, no host synchronisation, five launches; eight around the token-major kernels):
 //   1 router    one warp per local token
 //   2 dispatch  one CTA per token: the plan (destination rank and position inside the (source -> destination)
 //               slab of every pair, in pair order: deterministic), then each 16-block quantised once and stored
@@ -20,7 +20,8 @@
 //   4 permute   received rows into sorted-slot order + scale atoms, destination pointer of every output row: the
 //               first work of the weights-as-rows kernel (a launch of its own in front of the token-major kernels)
 //   5 experts   the tcgen05 kernels of the single-GPU layer; the down projection's epilogue stores each
-//               weighted row straight into the token owner's combine slab over NVLink; the last CTA
+//               weighted row straight into the token owner's combine slab over NVLink (128 contiguous bytes of
+//               a row per store instruction); the last CTA
 //               publishes the "rows are in place" flag on every peer (a one-warp launch behind the token-major kernels)
 //   6 combine   bounded wait on every rank's flag, fixed-order sum (+ residual) -> bf16; the last CTA
 //               advances the call counter
